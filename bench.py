@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the FRAC chunked-scan forward at the 135M layer shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: the composed
+frac_scan forward (u, c, kappa, rho -> h) followed by the skip-mix + gated-RMSNorm epilogue.
+Workload at every N: batch 8 x 24 heads (192 sequences), L 8192, R 64, M 128, chunk 256,
+bf16 u/c/kappa/z, fp32 rho, per GPU (weak scaling: every rank owns one such batch; the scan
+partitions by batch x head, so there is no data-path collective).
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of the
+reference's pure-PyTorch scan (oracle/frac_oracle.py) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "frac-ssm-kernels_b200"))
+
+import torch  # noqa: E402
+
+CFG = dict(batch=8, L=8192, H=24, R=64, M=128, T=256)
+METRIC = "frac_scan fwd tokens/s (all GPUs) at the 135M layer shape"
+
+
+def algorithmic_bytes(BH, L, R, M, with_init=False):
+    """Scan-level bytes the problem must move: bf16 u, c, kappa, h; fp32 rho; fp32 final state
+    (the reference's own accounting, benchmarks/benchmark_frac_scan.py:52-61)."""
+    return BH * L * (2 * R + 2 * M + 2 * M + 4 * M + 2 * R) + BH * R * M * 4 * (2 if with_init else 1)
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def device_inputs(dev, seed):
+    """Layer-level synthetic inputs with the stated distributions, generated on the device:
+    x, Bt, Ct, z ~ N(0,1) bf16; dt = softplus(N(0,1) - 4); A = -exp(U[0, ln 16]); D ~ N(0,1);
+    alpha ~ U(0.3, 0.9) per head; mapped to (u, c, kappa, rho) as oracle.layer_inputs does."""
+    b, L, H, R, M = CFG["batch"], CFG["L"], CFG["H"], CFG["R"], CFG["M"]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    x = rn(b, L, H, R).bfloat16()
+    z = rn(b, L, H * R).bfloat16()
+    dt = torch.nn.functional.softplus(rn(b, L, H) - 4.0)
+    A = -torch.exp(torch.rand(H, device=dev, generator=g) * math.log(16.0))
+    D = rn(H)
+    alpha = 0.3 + 0.6 * torch.rand(H, device=dev, generator=g)
+    log_tau = torch.linspace(0.0, math.log(65536.0), M, device=dev)
+    rate = (-A) ** (1.0 / alpha)
+    prior = -alpha[:, None] * log_tau[None, :]                      # [H, M]
+    u = x.permute(0, 2, 1, 3).reshape(b * H, L, R).contiguous()
+    c = torch.empty(b * H, L, M, device=dev, dtype=torch.bfloat16)
+    kappa = torch.empty_like(c)
+    rho = torch.empty(b * H, L, M, device=dev, dtype=torch.float32)
+    for bi in range(b):                                             # bound the float32 temporaries
+        Bt = rn(L, 1, M).bfloat16().float()
+        Ct = rn(L, 1, M).bfloat16().float()
+        r = torch.exp(-dt[bi][..., None] * rate[None, :, None] / log_tau.exp()).clamp(1e-6, 1 - 1e-6)
+        cw = torch.softmax(prior + Ct, dim=-1)
+        ww = torch.softmax(prior + Bt, dim=-1)
+        sl = slice(bi * H, (bi + 1) * H)
+        rho[sl] = r.permute(1, 0, 2)
+        c[sl] = cw.permute(1, 0, 2).bfloat16()
+        kappa[sl] = ((1 - r) * ww).permute(1, 0, 2).bfloat16()
+    Dhr = D[:, None].expand(H, R).contiguous()
+    w = torch.ones(H * R, device=dev, dtype=torch.bfloat16)
+    return dict(u=u, c=c, kappa=kappa, rho=rho, x_conv=x.reshape(b, L, H * R), z=z, D=Dhr, w=w)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline_sample(slabs, threads=None):
+    """Time the CPU restatement of the reference scan on `slabs` (batch, head) rows of the workload
+    (working precision: bf16 inputs, as the reference's upcast=False).  Returns tokens/s and a note."""
+    from oracle import frac_oracle as O
+
+    if threads:
+        torch.set_num_threads(threads)
+    H, L, R, M, T = CFG["H"], CFG["L"], CFG["R"], CFG["M"], CFG["T"]
+    u, c, kappa, rho, _ = O.scan_inputs(slabs, L, R, M, dtype=torch.bfloat16, gen="model_like", seed=0)
+    O.frac_scan_slabs(u[:1, :1024], c[:1, :1024], kappa[:1, :1024], rho[:1, :1024], T, None, True)  # warm
+    t0 = time.perf_counter()
+    O.frac_scan_slabs(u, c, kappa, rho, T, None, True, exact=False, slab=1)
+    dt = time.perf_counter() - t0
+    tokens = slabs * L / H
+    return tokens / dt, dt
+
+
+def run_reference(args, rank):
+    """The reference arm: the oracle port on the host cores, one bounded sample per step."""
+    if rank != 0:
+        return
+    from oracle import frac_oracle as O
+
+    H, L, R, M, T = CFG["H"], CFG["L"], CFG["R"], CFG["M"], CFG["T"]
+    slabs = 2
+    cores = torch.get_num_threads()
+    u, c, kappa, rho, _ = O.scan_inputs(slabs, L, R, M, dtype=torch.bfloat16, gen="model_like", seed=0)
+    for _ in range(args.warmup):
+        O.frac_scan_slabs(u[:1], c[:1], kappa[:1], rho[:1], T, None, True, exact=False, slab=1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.frac_scan_slabs(u, c, kappa, rho, T, None, True, exact=False, slab=1)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = slabs * L / H / dt
+    sample = (f"{slabs} of the {CFG['batch'] * H} (batch, head) rows per step, L {L}, "
+              f"working precision (bf16 inputs), torch {torch.__version__}, "
+              f"{os.cpu_count()} logical cpus, {cores} torch threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "config 1: single-layer frac_scan forward + skip-mix/gated-RMSNorm epilogue, "
+                        "batch 8 x 24 heads, L 8192, R 64, M 128, chunk 256, per GPU",
+            "batch_per_gpu": CFG["batch"], "seq_len": CFG["L"], "nheads": CFG["H"], "headdim": CFG["R"],
+            "d_state": CFG["M"], "chunk_size": CFG["T"], "sharding": f"batch x head over {n} GPU(s), no collective",
+            "l2": "inputs (2.2 GB per step) exceed the 126 MB L2; no flush needed"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="auto", choices=["auto", "staged", "fused"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    args.warmup = max(args.warmup, 3)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from frac_ssm_b200 import _cabi
+    from frac_ssm_b200.layers import scan_epilogue
+    from frac_ssm_b200.ops.b200 import frac_scan
+
+    _cabi.lib()
+    d = device_inputs(dev, seed=rank)
+    H, R, T = CFG["H"], CFG["R"], CFG["T"]
+    BH, L, M = d["u"].shape[0], CFG["L"], CFG["M"]
+    fused = bool(_cabi.lib().fracssm_scan_fused_supported(BH, L, R, M, T, _cabi.BF16, _cabi.BF16))
+    use_fused = fused and args.path != "staged"
+    launches_per_step = (1 if use_fused else 4) + 1
+
+    def step():
+        h = frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path)
+        return scan_epilogue(h, d["x_conv"], d["z"], d["D"], d["w"], H, R, 1e-6)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    scan_evs = []
+    e0.record()
+    for _ in range(args.steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        h = frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path)
+        b.record()
+        scan_evs.append((a, b))
+        y = scan_epilogue(h, d["x_conv"], d["z"], d["D"], d["w"], H, R, 1e-6)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1) / args.steps
+    scan_ms = statistics.mean(a.elapsed_time(b) for a, b in scan_evs)
+    if dist is not None:
+        t = torch.tensor([ms, scan_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, scan_ms = t.tolist()
+    tokens = CFG["batch"] * L * world
+    value = tokens / (ms * 1e-3)
+
+    # end to end: pinned host buffers in, result out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        names = ("u", "c", "kappa", "rho", "x_conv", "z")
+        host = {k: torch.empty(d[k].shape, dtype=d[k].dtype, pin_memory=True).copy_(d[k]) for k in names}
+        y_host = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+        h2d = sum(host[k].numel() * host[k].element_size() for k in names)
+        d2h = y_host.numel() * y_host.element_size()
+
+        def e2e_step():
+            t = {k: host[k].to(dev, non_blocking=True) for k in names}
+            hh = frac_scan(t["u"], t["c"], t["kappa"], t["rho"], T, None, False, path=args.path)
+            yy = scan_epilogue(hh, t["x_conv"], t["z"], d["D"], d["w"], H, R, 1e-6)
+            y_host.copy_(yy, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        k2 = max(2, min(args.steps, 5))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(k2):
+            e2e_step()
+        s1.record()
+        barrier()
+        ems = s0.elapsed_time(s1) / k2
+        if dist is not None:
+            t = torch.tensor([ems], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = t.item()
+        e2e = {"value": tokens / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ems, "steps": k2}
+        del host, y_host
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        alg = algorithmic_bytes(BH, L, R, M)
+        achieved = alg / (scan_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                    "kernel": "scan_fused_kernel" if use_fused else
+                              "staged scan (chunk_cumsum + chunk_state + state_passing + chunk_readout<fused>)",
+                    "kernel_ms": scan_ms, "algorithmic_bytes": alg}
+        cpu = None
+        if not args.no_cpu_baseline:
+            slabs = 8
+            v, secs = cpu_baseline_sample(slabs)
+            cpu = {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": f"{slabs} of {BH} (batch, head) rows of the workload, {secs:.1f} s, "
+                             f"working precision, {os.cpu_count()} logical cpus"}
+        line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+                "tokens_per_s_per_gpu": value / world, "roofline": roofline, "cpu_baseline": cpu,
+                "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+                "scan_path": "fused" if use_fused else "staged"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,253 @@
+// Bandwidth-bound layer stages around the scan: parameter prep, skip-mix, gated RMSNorm,
+// and the skip-mix + gated-RMSNorm epilogue in one pass.
+#include "common.cuh"
+
+namespace fracssm {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+struct ParamArgs {
+  const void *dyn; int dyn_dt; int64_t dyn_sb, dyn_sl;
+  const void *rw; int rw_dt; int64_t rw_sb, rw_sl;
+  const void *x; int x_dt; int64_t x_sb, x_sl;
+  const float *mask; int64_t m_sb, m_sl;
+  const float *dt_bias, *log_tau;
+  float read_gate, write_gate, inv_read_temp, dt_min, dt_max, a_min, a_max, l_min, l_max;
+  void *u; float *c, *kappa, *rho;
+  int64_t L, H, R, M;
+};
+
+// One warp per (bh, token): lanes stride over the M modes; two softmaxes by warp shuffles.
+__global__ void __launch_bounds__(128) compute_params_kernel(const ParamArgs a) {
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int64_t l = (int64_t)blockIdx.x * 4 + warp;
+  const int64_t bh = blockIdx.y;
+  if (l >= a.L) return;
+  const int64_t b = bh / a.H, h = bh % a.H;
+  const int64_t H = a.H, M = a.M, R = a.R;
+
+  const int64_t dbase = b * a.dyn_sb + l * a.dyn_sl;
+  float dt = softplusf_(ld_f32(a.dyn, dbase + h, a.dyn_dt) + a.dt_bias[h]);
+  dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
+  const float alpha = a.a_min + sigmoidf_(ld_f32(a.dyn, dbase + H + h, a.dyn_dt)) * (a.a_max - a.a_min);
+  const float lam = a.l_min + sigmoidf_(ld_f32(a.dyn, dbase + 2 * H + h, a.dyn_dt)) * (a.l_max - a.l_min);
+  const float rate = powf(fmaxf(lam, 1e-4f), 1.f / fmaxf(alpha, 1e-4f));
+  const float keep = a.mask ? a.mask[b * a.m_sb + l * a.m_sl] : 1.f;
+
+  const int64_t rbase = b * a.rw_sb + l * a.rw_sl + h * M;       // read residuals
+  const int64_t wbase = rbase + H * M;                            // write residuals
+  float rmax = -INFINITY, wmax = -INFINITY;
+  for (int64_t m = lane; m < M; m += 32) {
+    const float prior = -alpha * a.log_tau[m];
+    rmax = fmaxf(rmax, (prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp);
+    wmax = fmaxf(wmax, prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt));
+  }
+  rmax = warp_max(rmax);
+  wmax = warp_max(wmax);
+  float rsum = 0.f, wsum = 0.f;
+  for (int64_t m = lane; m < M; m += 32) {
+    const float prior = -alpha * a.log_tau[m];
+    rsum += __expf((prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax);
+    wsum += __expf(prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax);
+  }
+  const float rinv = 1.f / warp_sum(rsum), winv = 1.f / warp_sum(wsum);
+  const int64_t obase = (bh * a.L + l) * M;
+  for (int64_t m = lane; m < M; m += 32) {
+    const float lt = a.log_tau[m];
+    const float prior = -alpha * lt;
+    const float cw = __expf((prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax) * rinv;
+    const float ww = __expf(prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax) * winv;
+    float rho = expf(-dt * (rate / fmaxf(expf(lt), 1e-6f)));
+    rho = fminf(fmaxf(rho, 1e-6f), 1.f - 1e-6f);
+    float kap = (1.f - rho) * ww;
+    if (a.mask) { kap *= keep; rho = rho * keep + (1.f - keep); }
+    a.c[obase + m] = cw;
+    a.kappa[obase + m] = kap;
+    a.rho[obase + m] = rho;
+  }
+  const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
+  for (int64_t r = lane; r < R; r += 32)
+    st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+}
+
+__global__ void __launch_bounds__(256)
+skip_mix_kernel(const void *__restrict__ mf, int mf_dt, int64_t mf_sb, int64_t mf_sl,
+                const void *__restrict__ x, int x_dt, int64_t x_sb, int64_t x_sl,
+                const float *__restrict__ D, void *__restrict__ out, int o_dt, int64_t L, int64_t H,
+                int64_t R) {
+  const int64_t HR = H * R;
+  const int64_t row = blockIdx.x;  // b * L + l
+  const int64_t b = row / L, l = row % L;
+  for (int64_t j = threadIdx.x; j < HR; j += blockDim.x) {
+    const int64_t h = j / R, r = j % R;
+    const float v = ld_f32(mf, (b * H + h) * mf_sb + l * mf_sl + r, mf_dt) +
+                    ld_f32(x, b * x_sb + l * x_sl + j, x_dt) * D[j];
+    st_f32(out, row * HR + j, o_dt, v);
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < blockDim.x / 32) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+// One block per row.
+__global__ void __launch_bounds__(256)
+rmsnorm_gated_kernel(const void *__restrict__ x, int64_t x_srow, const void *__restrict__ gate,
+                     int64_t g_srow, int dt, const void *__restrict__ w, int w_dt, float eps,
+                     void *__restrict__ y, float *__restrict__ rstd, int64_t D) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int64_t j = threadIdx.x; j < D; j += blockDim.x) {
+    float v = ld_f32(x, row * x_srow + j, dt);
+    if (gate) { const float z = ld_f32(gate, row * g_srow + j, dt); v *= z * sigmoidf_(z); }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)D + eps);
+  if (rstd && threadIdx.x == 0) rstd[row] = rs;
+  for (int64_t j = threadIdx.x; j < D; j += blockDim.x) {
+    float v = ld_f32(x, row * x_srow + j, dt);
+    if (gate) { const float z = ld_f32(gate, row * g_srow + j, dt); v *= z * sigmoidf_(z); }
+    st_f32(y, row * D + j, dt, v * rs * ld_f32(w, j, w_dt));
+  }
+}
+
+// One block per (b, l) row of width H*R: un-flatten h, add the D skip, gate, normalise.
+__global__ void __launch_bounds__(256)
+scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t h_sl,
+                     const void *__restrict__ x, int64_t x_sb, int64_t x_sl,
+                     const void *__restrict__ gate, int64_t g_sb, int64_t g_sl, int dt,
+                     const float *__restrict__ Dp, const void *__restrict__ w, int w_dt,
+                     float gate_bias, float eps, void *__restrict__ y, int64_t L, int64_t H,
+                     int64_t R) {
+  __shared__ float red[32];
+  const int64_t HR = H * R;
+  const int64_t row = blockIdx.x, b = row / L, l = row % L;
+  float ss = 0.f;
+  for (int64_t j = threadIdx.x; j < HR; j += blockDim.x) {
+    const int64_t hh = j / R, r = j % R;
+    float v = ld_f32(h, (b * H + hh) * h_sb + l * h_sl + r, h_dt) +
+              ld_f32(x, b * x_sb + l * x_sl + j, dt) * Dp[j];
+    const float z = ld_f32(gate, b * g_sb + l * g_sl + j, dt) + gate_bias;
+    v *= z * sigmoidf_(z);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)HR + eps);
+  for (int64_t j = threadIdx.x; j < HR; j += blockDim.x) {
+    const int64_t hh = j / R, r = j % R;
+    float v = ld_f32(h, (b * H + hh) * h_sb + l * h_sl + r, h_dt) +
+              ld_f32(x, b * x_sb + l * x_sl + j, dt) * Dp[j];
+    const float z = ld_f32(gate, b * g_sb + l * g_sl + j, dt) + gate_bias;
+    v *= z * sigmoidf_(z);
+    st_f32(y, row * HR + j, dt, v * rs * ld_f32(w, j, w_dt));
+  }
+}
+
+}  // namespace fracssm
+
+extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64_t dyn_sl,
+                                      const void *rw, int rw_dtype, int64_t rw_sb, int64_t rw_sl,
+                                      const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl,
+                                      const float *mask, int64_t m_sb, int64_t m_sl,
+                                      const float *dt_bias, const float *base_log_tau,
+                                      float read_gate_logit, float write_gate_logit, float read_temp,
+                                      float dt_min, float dt_max, float alpha_min, float alpha_max,
+                                      float lambda_min, float lambda_max, void *u, float *c,
+                                      float *kappa, float *rho, int64_t Bt, int64_t L, int64_t H,
+                                      int64_t R, int64_t M, void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || L < 0 || H <= 0 || R <= 0 || M <= 0) return fail(FRACSSM_ERR_ARG, "compute_params: bad sizes");
+  if (!known_dtype(dyn_dtype) || !known_dtype(rw_dtype) || !known_dtype(x_dtype))
+    return fail(FRACSSM_ERR_ARG, "compute_params: unsupported dtype");
+  if (Bt == 0 || L == 0) return FRACSSM_OK;
+  if (!dyn || !rw || !x_conv || !dt_bias || !base_log_tau || !u || !c || !kappa || !rho)
+    return fail(FRACSSM_ERR_ARG, "compute_params: null pointer");
+  if (Bt * H > 65535) return fail(FRACSSM_ERR_UNSUPPORTED, "compute_params: batch*heads too large for one launch");
+  ParamArgs a{};
+  a.dyn = dyn; a.dyn_dt = dyn_dtype; a.dyn_sb = dyn_sb; a.dyn_sl = dyn_sl;
+  a.rw = rw; a.rw_dt = rw_dtype; a.rw_sb = rw_sb; a.rw_sl = rw_sl;
+  a.x = x_conv; a.x_dt = x_dtype; a.x_sb = x_sb; a.x_sl = x_sl;
+  a.mask = mask; a.m_sb = m_sb; a.m_sl = m_sl;
+  a.dt_bias = dt_bias; a.log_tau = base_log_tau;
+  a.read_gate = 1.f / (1.f + expf(-read_gate_logit));
+  a.write_gate = 1.f / (1.f + expf(-write_gate_logit));
+  a.inv_read_temp = 1.f / read_temp;
+  a.dt_min = dt_min; a.dt_max = dt_max; a.a_min = alpha_min; a.a_max = alpha_max;
+  a.l_min = lambda_min; a.l_max = lambda_max;
+  a.u = u; a.c = c; a.kappa = kappa; a.rho = rho;
+  a.L = L; a.H = H; a.R = R; a.M = M;
+  dim3 grid((unsigned)ceil_div(L, 4), (unsigned)(Bt * H));
+  compute_params_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+  return check_launch("compute_params");
+}
+
+extern "C" int fracssm_skip_mix(const void *mixed_flat, int mf_dtype, int64_t mf_sb, int64_t mf_sl,
+                                const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl,
+                                const float *D, void *out, int out_dtype, int64_t Bt, int64_t L,
+                                int64_t H, int64_t R, void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || L < 0 || H <= 0 || R <= 0) return fail(FRACSSM_ERR_ARG, "skip_mix: bad sizes");
+  if (!known_dtype(mf_dtype) || !known_dtype(x_dtype) || !known_dtype(out_dtype))
+    return fail(FRACSSM_ERR_ARG, "skip_mix: unsupported dtype");
+  if (Bt == 0 || L == 0) return FRACSSM_OK;
+  if (!mixed_flat || !x_conv || !D || !out) return fail(FRACSSM_ERR_ARG, "skip_mix: null pointer");
+  skip_mix_kernel<<<(unsigned)(Bt * L), 256, 0, (cudaStream_t)stream>>>(
+      mixed_flat, mf_dtype, mf_sb, mf_sl, x_conv, x_dtype, x_sb, x_sl, D, out, out_dtype, L, H, R);
+  return check_launch("skip_mix");
+}
+
+extern "C" int fracssm_rmsnorm_gated(const void *x, int64_t x_srow, const void *gate, int64_t g_srow,
+                                     int xg_dtype, const void *weight, int w_dtype, float eps,
+                                     void *y, float *rstd, int64_t rows, int64_t D, void *stream) {
+  using namespace fracssm;
+  if (rows < 0 || D <= 0) return fail(FRACSSM_ERR_ARG, "rmsnorm_gated: bad sizes");
+  if (!known_dtype(xg_dtype) || !known_dtype(w_dtype)) return fail(FRACSSM_ERR_ARG, "rmsnorm_gated: unsupported dtype");
+  if (rows == 0) return FRACSSM_OK;
+  if (!x || !weight || !y) return fail(FRACSSM_ERR_ARG, "rmsnorm_gated: null pointer");
+  rmsnorm_gated_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+      x, x_srow, gate, g_srow, xg_dtype, weight, w_dtype, eps, y, rstd, D);
+  return check_launch("rmsnorm_gated");
+}
+
+extern "C" int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                     const void *x_conv, int64_t x_sb, int64_t x_sl,
+                                     const void *gate, int64_t g_sb, int64_t g_sl, int xg_dtype,
+                                     const float *D, const void *weight, int w_dtype,
+                                     float gate_bias, float eps, void *y, int64_t Bt, int64_t L,
+                                     int64_t H, int64_t R, void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || L < 0 || H <= 0 || R <= 0) return fail(FRACSSM_ERR_ARG, "scan_epilogue: bad sizes");
+  if (!known_dtype(h_dtype) || !known_dtype(xg_dtype) || !known_dtype(w_dtype))
+    return fail(FRACSSM_ERR_ARG, "scan_epilogue: unsupported dtype");
+  if (Bt == 0 || L == 0) return FRACSSM_OK;
+  if (!h || !x_conv || !gate || !D || !weight || !y) return fail(FRACSSM_ERR_ARG, "scan_epilogue: null pointer");
+  scan_epilogue_kernel<<<(unsigned)(Bt * L), 256, 0, (cudaStream_t)stream>>>(
+      h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb, g_sl, xg_dtype, D, weight, w_dtype,
+      gate_bias, eps, y, L, H, R);
+  return check_launch("scan_epilogue");
+}

@@ -1,0 +1,5 @@
+from .compute_params import compute_params_from_projections, frac_compute_scan_params
+from .output_mix import frac_skip_mix, scan_epilogue, skip_mix
+
+__all__ = ["frac_compute_scan_params", "frac_skip_mix", "compute_params_from_projections",
+           "skip_mix", "scan_epilogue"]

@@ -1,0 +1,67 @@
+"""Scan-parameter prep on the B200 CUDA extension.
+
+Interface of `frac_ssm/layers/compute_params.py:583-596`: the two projections stay library
+GEMMs (`F.linear`), everything after them is one kernel.  Forward only.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _cabi as C
+
+
+def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, read_residual_logit,
+                                    write_residual_scale, base_log_tau, num_heads, head_dim,
+                                    num_modes, read_temp, dt_min, dt_max, alpha_min, alpha_max,
+                                    lambda_min, lambda_max):
+    """Elementwise part: dyn [B,L,3H], rw [B,L,2HM], x_conv [B,L,HR] ->
+    (u [BH,L,R] in x_conv.dtype, c, kappa, rho [BH,L,M] float32), head-major."""
+    assert dyn.dim() == 3 and rw.dim() == 3 and x_conv.dim() == 3, "dyn, rw and x_conv must be 3D"
+    assert dyn.is_cuda and rw.is_cuda and x_conv.is_cuda, "inputs must be on CUDA"
+    B, L, _ = x_conv.shape
+    H, R, M = num_heads, head_dim, num_modes
+    assert dyn.shape == (B, L, 3 * H), "dyn shape must be (B, L, 3*H)"
+    assert rw.shape == (B, L, 2 * H * M), "rw shape must be (B, L, 2*H*M)"
+    assert x_conv.shape == (B, L, H * R), "x_conv shape must be (B, L, H*R)"
+    dev = x_conv.device
+    dyn, rw, x_conv = C.rows(dyn), C.rows(rw), C.rows(x_conv)
+    mask = None
+    if attention_mask is not None:
+        assert attention_mask.shape == (B, L), "attention_mask shape must be (B, L)"
+        mask = attention_mask.to(device=dev, dtype=torch.float32)
+    u = torch.empty(B * H, L, R, device=dev, dtype=x_conv.dtype)
+    c = torch.empty(B * H, L, M, device=dev, dtype=torch.float32)
+    kappa = torch.empty_like(c)
+    rho = torch.empty_like(c)
+    if B == 0 or L == 0:
+        return u, c, kappa, rho
+    dtb = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
+    ltau = base_log_tau.detach().to(device=dev, dtype=torch.float32).contiguous()
+    with torch.cuda.device(dev):
+        C.check(C.lib().fracssm_compute_params(
+            C.ptr(dyn), C.dt(dyn), dyn.stride(0), dyn.stride(1), C.ptr(rw), C.dt(rw), rw.stride(0),
+            rw.stride(1), C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1),
+            C.ptr(mask), 0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1),
+            C.ptr(dtb), C.ptr(ltau), float(read_residual_logit), float(write_residual_scale),
+            float(read_temp), float(dt_min), float(dt_max), float(alpha_min), float(alpha_max),
+            float(lambda_min), float(lambda_max), C.ptr(u), C.ptr(c), C.ptr(kappa), C.ptr(rho),
+            B, L, H, R, M, C.stream_of(x_conv)), "compute_params")
+    return u, c, kappa, rho
+
+
+def frac_compute_scan_params(model, x_conv, x, attention_mask=None):
+    """Compute scan inputs (u, c, kappa, rho) from post-conv features.
+
+    `model` is a mixer holding dyn_proj, rw_proj, dt_bias, read_residual_logit,
+    write_residual_scale, base_log_tau, num_heads, head_dim, num_modes, read_temp and config.
+    """
+    dyn = F.linear(x, model.dyn_proj.weight, model.dyn_proj.bias)
+    rw = F.linear(x_conv, model.rw_proj.weight)
+    cfg = model.config
+    return compute_params_from_projections(
+        dyn, rw, x_conv, attention_mask, model.dt_bias, model.read_residual_logit.item(),
+        model.write_residual_scale.item(), model.base_log_tau, model.num_heads, model.head_dim,
+        model.num_modes, model.read_temp, cfg.frac_dt_min, cfg.frac_dt_max, cfg.frac_alpha_min,
+        cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max)

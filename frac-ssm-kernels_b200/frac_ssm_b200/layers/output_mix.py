@@ -1,0 +1,59 @@
+"""D skip connection + un-flatten on the B200 CUDA extension
+(interface of `frac_ssm/layers/output_mix.py:232-243`), and the fused epilogue that also
+applies the gated RMSNorm (`frac_ssm/models/modeling_frac.py:213-214`).  Forward only."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi as C
+
+
+def skip_mix(mixed_flat, x_conv, D, num_heads, head_dim, out_dtype=None):
+    """out[b, l, h*R + r] = mixed_flat[b*H + h, l, r] + x_conv[b, l, h*R + r] * D[h, r]."""
+    assert mixed_flat.dim() == 3 and x_conv.dim() == 3, "mixed_flat and x_conv must be 3D"
+    assert mixed_flat.is_cuda and x_conv.is_cuda, "inputs must be on CUDA"
+    H, R = num_heads, head_dim
+    B, L, HR = x_conv.shape
+    assert HR == H * R, "x_conv last dim must be num_heads * head_dim"
+    assert mixed_flat.shape == (B * H, L, R), "mixed_flat shape must be (B*H, L, R)"
+    out_dtype = x_conv.dtype if out_dtype is None else out_dtype
+    mixed_flat, x_conv = C.rows(mixed_flat), C.rows(x_conv)
+    Df = D.detach().to(device=x_conv.device, dtype=torch.float32).contiguous()
+    out = torch.empty(B, L, HR, device=x_conv.device, dtype=out_dtype)
+    if B == 0 or L == 0:
+        return out
+    with torch.cuda.device(x_conv.device):
+        C.check(C.lib().fracssm_skip_mix(
+            C.ptr(mixed_flat), C.dt(mixed_flat), mixed_flat.stride(0), mixed_flat.stride(1),
+            C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1), C.ptr(Df), C.ptr(out),
+            C.dt(out), B, L, H, R, C.stream_of(x_conv)), "skip_mix")
+    return out
+
+
+def frac_skip_mix(model, mixed_flat, x_conv, out_dtype=None):
+    """D skip connection, reshape."""
+    return skip_mix(mixed_flat, x_conv, model.D, model.num_heads, model.head_dim, out_dtype)
+
+
+def scan_epilogue(h, x_conv, gate, D, weight, num_heads, head_dim, eps=1e-6, gate_bias=0.0):
+    """y = weight * rmsnorm((h_unflat + x_conv * D) * silu(gate + gate_bias)) in one pass."""
+    assert h.dim() == 3 and x_conv.dim() == 3 and gate.dim() == 3, "h, x_conv and gate must be 3D"
+    assert h.is_cuda and x_conv.is_cuda and gate.is_cuda, "inputs must be on CUDA"
+    H, R = num_heads, head_dim
+    B, L, HR = x_conv.shape
+    assert HR == H * R and gate.shape == x_conv.shape and h.shape == (B * H, L, R)
+    assert gate.dtype == x_conv.dtype, "gate and x_conv must have the same dtype"
+    h, x_conv, gate = C.rows(h), C.rows(x_conv), C.rows(gate)
+    Df = D.detach().to(device=x_conv.device, dtype=torch.float32).contiguous()
+    w = weight.detach().contiguous()
+    y = torch.empty(B, L, HR, device=x_conv.device, dtype=x_conv.dtype)
+    if B == 0 or L == 0:
+        return y
+    with torch.cuda.device(x_conv.device):
+        C.check(C.lib().fracssm_scan_epilogue(
+            C.ptr(h), C.dt(h), h.stride(0), h.stride(1), C.ptr(x_conv), x_conv.stride(0),
+            x_conv.stride(1), C.ptr(gate), gate.stride(0), gate.stride(1), C.dt(x_conv), C.ptr(Df),
+            C.ptr(w), C.dt(w), float(gate_bias), float(eps), C.ptr(y), B, L, H, R,
+            C.stream_of(x_conv)), "scan_epilogue")
+    return y

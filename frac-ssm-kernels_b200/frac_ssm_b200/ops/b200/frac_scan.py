@@ -1,0 +1,80 @@
+"""The composed forward scan on the B200 CUDA extension.
+
+Backend-module interface of the reference (`frac_ssm/ops/triton/frac_scan.py:102-130`):
+`frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False)`.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ... import _cabi as C
+
+# "auto": the single-pass tcgen05 kernel when it covers the shape, else the staged kernels.
+_PATHS = {"auto": C.PATH_AUTO, "staged": C.PATH_STAGED, "fused": C.PATH_FUSED}
+
+
+def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False, *,
+              final_state_dtype=None, path="auto"):
+    """Fractional chunked scan, forward.
+
+    Args:
+        u: [B, L, R] input features (bfloat16, float16 or float32); dim 0 is batch*heads.
+        c, kappa: [B, L, M] read / write coefficients, same dtype as each other (u's or float32).
+        rho: [B, L, M] float32 decay.
+        chunk_size: tokens per chunk.
+        initial_state: [B, R, M] float32 or None.
+        return_final_state: also return the state after the last token.
+        final_state_dtype: dtype of the returned state; default follows the reference
+            (bfloat16 when u is bfloat16, else float32).  The state is always carried in float32.
+        path: "auto", "staged" or "fused".
+    Returns:
+        h [B, L, R] in u.dtype, and final_state [B, R, M] if requested.
+    """
+    assert rho.dtype == torch.float32, "rho must be float32 for numerical stability"
+    if initial_state is not None:
+        assert initial_state.dtype == torch.float32, "initial_state must be float32"
+    assert u.dim() == 3, f"u must be 3D (B, L, R), got {u.dim()}D"
+    assert c.dim() == 3, f"c must be 3D (B, L, M), got {c.dim()}D"
+    assert kappa.dim() == 3, f"kappa must be 3D (B, L, M), got {kappa.dim()}D"
+    assert rho.dim() == 3, f"rho must be 3D (B, L, M), got {rho.dim()}D"
+    assert all(x.is_cuda for x in (u, c, kappa, rho)), "inputs must be on CUDA"
+    assert c.dtype == kappa.dtype and c.dtype in (u.dtype, torch.float32), (
+        "c and kappa dtype must match u dtype or be float32"
+    )
+    assert isinstance(chunk_size, int) and chunk_size > 0, (
+        f"chunk_size must be a positive integer, got {chunk_size}"
+    )
+    B, L, R = u.shape
+    M = c.shape[-1]
+    assert c.shape == (B, L, M) and kappa.shape == (B, L, M) and rho.shape == (B, L, M), (
+        "c, kappa and rho shapes must match (B, L, M)"
+    )
+    if initial_state is not None:
+        assert initial_state.shape == (B, R, M), "initial_state shape must be (B, R, M)"
+        assert initial_state.is_cuda, "initial_state must be on CUDA"
+    if final_state_dtype is None:
+        final_state_dtype = torch.bfloat16 if u.dtype == torch.bfloat16 else torch.float32
+    assert final_state_dtype in (torch.float32, torch.bfloat16)
+
+    u, c, kappa, rho = C.rows(u), C.rows(c), C.rows(kappa), C.rows(rho)
+    init = None if initial_state is None else initial_state.contiguous()
+    h = torch.empty(B, L, R, device=u.device, dtype=u.dtype)
+    fin = torch.empty(B, R, M, device=u.device, dtype=final_state_dtype) if return_final_state else None
+    if B > 0:
+        lib = C.lib()
+        p = _PATHS[path]
+        with torch.cuda.device(u.device):
+            nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, p)
+            ws = torch.empty(max(nbytes, 256), device=u.device, dtype=torch.uint8)
+            C.check(lib.fracssm_frac_scan_fwd(
+                C.ptr(u), C.dt(u), u.stride(0), u.stride(1), C.ptr(c), C.ptr(kappa), C.dt(c),
+                c.stride(0), c.stride(1), kappa.stride(0), kappa.stride(1), C.ptr(rho), rho.stride(0),
+                rho.stride(1), C.ptr(init), C.ptr(h), C.ptr(fin), C.dt_of(final_state_dtype),
+                C.ptr(ws), ws.numel(), B, L, R, M, chunk_size, p, C.stream_of(u)), "frac_scan")
+    if return_final_state:
+        return h, fin
+    return h
+
+
+__all__ = ["frac_scan"]

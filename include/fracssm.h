@@ -1,0 +1,183 @@
+/*
+ * fracssm.h — C ABI of the B200 (sm_100a) implementation of the FRAC fractional-SSM
+ * chunked scan, forward pass.
+ *
+ * Every entry point takes raw DEVICE pointers (unless it says "host"), sizes, element
+ * strides and a CUDA stream (cudaStream_t passed as void*), owns nothing, allocates
+ * nothing unless stated, launches asynchronously on the given stream and returns an
+ * int status (0 = ok).  fracssm_last_error() returns the text of the last failure on
+ * the calling thread.  Tensors are row-major with a contiguous last dimension; "sb"
+ * and "sl" arguments are the strides (in elements) of dim 0 and dim 1.  Outputs are
+ * dense.  Dim 0 is the flattened (batch, head) index, bh = b * H + h.
+ *
+ * Each declaration names the interface of quorbix/frac-ssm-kernels it stands behind
+ * (path within that project : line).
+ */
+#ifndef FRACSSM_H
+#define FRACSSM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FRACSSM_ABI_VERSION 1
+
+/* element types */
+#define FRACSSM_F32 0
+#define FRACSSM_BF16 1
+#define FRACSSM_F16 2
+
+/* status codes */
+#define FRACSSM_OK 0
+#define FRACSSM_ERR_ARG 1         /* bad size, null pointer, unsupported dtype combination */
+#define FRACSSM_ERR_CUDA 2        /* a CUDA runtime call or launch failed */
+#define FRACSSM_ERR_UNSUPPORTED 3 /* shape outside what a specialised kernel covers */
+#define FRACSSM_ERR_WAIT 4        /* a bounded device-side wait ran out */
+
+int fracssm_abi_version(void);
+const char *fracssm_last_error(void);
+
+/* 1 if the shape is covered by the tcgen05 single-pass scan kernel, else 0. */
+int fracssm_scan_fused_supported(int64_t B, int64_t L, int64_t R, int64_t M, int64_t T,
+                                 int u_dtype, int ck_dtype);
+
+/*
+ * Within-chunk inclusive running sum of the log-decay, and per-chunk totals.
+ * src_is_rho = 0: src is log_rho;  1: src is rho and log(max(rho, 1e-6)) is fused in.
+ * lcr [B, L, M] f32, chunk_decay [B, ceil(L/T), M] f32.
+ * Replaces frac_ssm/ops/triton/chunk_cumsum.py:189 `chunk_cumsum(log_rho, chunk_size)`
+ * and, with src_is_rho, also frac_ssm/ops/triton/frac_scan.py:40.
+ */
+int fracssm_chunk_cumsum(const float *src, int64_t sb, int64_t sl, int src_is_rho, float *lcr,
+                         float *chunk_decay, int64_t B, int64_t L, int64_t M, int64_t T,
+                         void *stream);
+
+/*
+ * Per-chunk state contribution, states [B, N, R, M] (states_dtype f32 or bf16):
+ *   states[b,n,r,m] = sum_t u[t,r] * kappa[t,m] * exp(lcr[last,m] - lcr[t,m]).
+ * Replaces frac_ssm/ops/triton/chunk_state.py:305
+ * `chunk_state(u, kappa, log_cum_rho, chunk_size, state_fp32)`.
+ */
+int fracssm_chunk_state(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl, const void *kappa,
+                        int k_dtype, int64_t k_sb, int64_t k_sl, const float *lcr, int64_t g_sb,
+                        int64_t g_sl, void *states, int states_dtype, int64_t B, int64_t L,
+                        int64_t R, int64_t M, int64_t T, void *stream);
+
+/*
+ * Inter-chunk recurrence: states_acc[n] = run; run = exp(chunk_decay[n]) * run + states[n].
+ * initial_state may be NULL (zero).  The carry is kept in float32 whatever the I/O types.
+ * states, states_acc [B, N, R, M]; chunk_decay [B, N, M] f32; initial/final [B, R, M].
+ * Replaces frac_ssm/ops/triton/state_passing.py:322
+ * `state_passing(states, chunk_decay, initial_state)`.
+ */
+int fracssm_state_passing(const void *states, int states_dtype, const float *chunk_decay,
+                          const void *initial_state, int init_dtype, void *states_acc,
+                          int acc_dtype, void *final_state, int final_dtype, int64_t B, int64_t N,
+                          int64_t R, int64_t M, void *stream);
+
+/*
+ * Causal intra-chunk matrix W [B, N, T, T] f32 (zero above the diagonal):
+ *   W[t,k] = sum_m c[t,m] * exp(lcr[t,m] - lcr[k,m]) * kappa[k,m],  k <= t.
+ * Replaces frac_ssm/ops/triton/chunk_w.py:418 `chunk_w(c, kappa, log_cum_rho, chunk_size)`.
+ */
+int fracssm_chunk_w(const void *c, const void *kappa, int ck_dtype, int64_t c_sb, int64_t c_sl,
+                    int64_t k_sb, int64_t k_sl, const float *lcr, int64_t g_sb, int64_t g_sl,
+                    float *W, int64_t B, int64_t L, int64_t M, int64_t T, void *stream);
+
+/*
+ * h = (c * exp(lcr)) . states_acc^T + W . u per chunk; h [B, L, R] in u's dtype.
+ * Replaces frac_ssm/ops/triton/chunk_readout.py:657
+ * `chunk_readout(u, c, states_acc, W, log_cum_rho, chunk_size)`.
+ */
+int fracssm_chunk_readout(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl, const void *c,
+                          int c_dtype, int64_t c_sb, int64_t c_sl, const void *states_acc,
+                          int acc_dtype, const void *W, int w_dtype, const float *lcr, int64_t g_sb,
+                          int64_t g_sl, void *h, int64_t B, int64_t L, int64_t R, int64_t M,
+                          int64_t T, void *stream);
+
+/*
+ * chunk_w and chunk_readout in one kernel; W never reaches memory.
+ * Replaces frac_ssm/ops/cute/chunk_fused_readout.py:150
+ * `chunk_fused_readout(u, c, kappa, states_acc, log_cum_rho, chunk_size)`.
+ */
+int fracssm_chunk_fused_readout(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl,
+                                const void *c, const void *kappa, int ck_dtype, int64_t c_sb,
+                                int64_t c_sl, int64_t k_sb, int64_t k_sl, const void *states_acc,
+                                int acc_dtype, const float *lcr, int64_t g_sb, int64_t g_sl,
+                                void *h, int64_t B, int64_t L, int64_t R, int64_t M, int64_t T,
+                                void *stream);
+
+/*
+ * The composed forward scan.  u [B,L,R]; c, kappa [B,L,M] (same dtype: u's or f32);
+ * rho [B,L,M] f32; initial_state [B,R,M] f32 or NULL; h [B,L,R] in u's dtype;
+ * final_state [B,R,M] (final_dtype f32 or bf16) or NULL.  workspace: device scratch of at
+ * least fracssm_frac_scan_workspace_bytes(...) bytes, 256-byte aligned, caller-owned.
+ * path: 0 = pick (single-pass tcgen05 kernel when the shape is covered, else staged),
+ *       1 = staged kernels, 2 = single-pass kernel (error if the shape is not covered).
+ * Replaces frac_ssm/ops/frac_scan.py:53 `frac_scan(...)` /
+ * frac_ssm/ops/triton/frac_scan.py:102.
+ */
+size_t fracssm_frac_scan_workspace_bytes(int64_t B, int64_t L, int64_t R, int64_t M, int64_t T,
+                                         int path);
+int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl, const void *c,
+                          const void *kappa, int ck_dtype, int64_t c_sb, int64_t c_sl,
+                          int64_t k_sb, int64_t k_sl, const float *rho, int64_t r_sb, int64_t r_sl,
+                          const float *initial_state, void *h, void *final_state, int final_dtype,
+                          void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                          int64_t M, int64_t T, int path, void *stream);
+
+/*
+ * Elementwise scan-parameter prep after the two projections.
+ * dyn [Bt, L, 3H] (dt, alpha, lambda logits), rw [Bt, L, 2*H*M] (read then write residuals),
+ * x_conv [Bt, L, H*R]; mask [Bt, L] f32 or NULL; dt_bias [H], base_log_tau [M] f32;
+ * read_gate_logit, write_gate_logit: the two scalar parameters (sigmoid is applied here).
+ * Outputs head-major: u [Bt*H, L, R] (x dtype), c, kappa, rho [Bt*H, L, M] f32.
+ * Replaces the kernel behind frac_ssm/layers/compute_params.py:583
+ * `frac_compute_scan_params(model, x_conv, x, attention_mask)` (:165-213).
+ */
+int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64_t dyn_sl,
+                           const void *rw, int rw_dtype, int64_t rw_sb, int64_t rw_sl,
+                           const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl,
+                           const float *mask, int64_t m_sb, int64_t m_sl, const float *dt_bias,
+                           const float *base_log_tau, float read_gate_logit,
+                           float write_gate_logit, float read_temp, float dt_min, float dt_max,
+                           float alpha_min, float alpha_max, float lambda_min, float lambda_max,
+                           void *u, float *c, float *kappa, float *rho, int64_t Bt, int64_t L,
+                           int64_t H, int64_t R, int64_t M, void *stream);
+
+/*
+ * out[b, l, h*R + r] = mixed_flat[b*H + h, l, r] + x_conv[b, l, h*R + r] * D[h, r].
+ * Replaces frac_ssm/layers/output_mix.py:232 `frac_skip_mix(model, mixed_flat, x_conv, out_dtype)`.
+ */
+int fracssm_skip_mix(const void *mixed_flat, int mf_dtype, int64_t mf_sb, int64_t mf_sl,
+                     const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl, const float *D,
+                     void *out, int out_dtype, int64_t Bt, int64_t L, int64_t H, int64_t R,
+                     void *stream);
+
+/*
+ * y = w * rmsnorm(x * silu(gate)) over rows of width D; gate may be NULL; rstd [rows] f32 or NULL.
+ * Replaces frac_ssm/modules/rmsnorm_gated.py:65 `rmsnorm_gated_fwd` behind
+ * `MambaRMSNormGated.forward` (:292-299).
+ */
+int fracssm_rmsnorm_gated(const void *x, int64_t x_srow, const void *gate, int64_t g_srow,
+                          int xg_dtype, const void *weight, int w_dtype, float eps, void *y,
+                          float *rstd, int64_t rows, int64_t D, void *stream);
+
+/*
+ * Skip-mix and gated RMSNorm in one pass over the scan output:
+ *   y[b,l,:] = w * rmsnorm((h[bh,l,:] + x_conv[b,l,:] * D) * silu(gate[b,l,:])).
+ * Replaces the pair frac_ssm/models/modeling_frac.py:213-214.
+ */
+int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                          const void *x_conv, int64_t x_sb, int64_t x_sl, const void *gate,
+                          int64_t g_sb, int64_t g_sl, int xg_dtype, const float *D,
+                          const void *weight, int w_dtype, float gate_bias, float eps, void *y,
+                          int64_t Bt, int64_t L, int64_t H, int64_t R, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRACSSM_H */

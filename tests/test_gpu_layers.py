@@ -1,0 +1,128 @@
+"""Parity of the layer-level stages (parameter prep, skip-mix, gated RMSNorm, fused epilogue)."""
+
+import os
+import types
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import frac_oracle as O
+from tests.helpers import TOL_BF16, TOL_F32, assert_ref_error, close
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(dt_min=1e-4, dt_max=1.0, alpha_min=0.2, alpha_max=0.95, lambda_min=0.25, lambda_max=4.0)
+
+
+def _golden(golden_dir):
+    return torch.load(os.path.join(golden_dir, "layer_small.pt"), weights_only=False)
+
+
+def _mixer(g, device):
+    """A stand-in for the reference's FracMixer holding just what the layer ops read."""
+    m = g["meta"]
+    mod = types.SimpleNamespace(num_heads=m["H"], head_dim=m["R"], num_modes=m["M"], read_temp=1.0)
+    mod.dyn_proj = types.SimpleNamespace(weight=g["dyn_w"].to(device), bias=g["dyn_b"].to(device))
+    mod.rw_proj = types.SimpleNamespace(weight=g["rw_w"].to(device))
+    for k in ("dt_bias", "read_residual_logit", "write_residual_scale", "base_log_tau", "D"):
+        setattr(mod, k, g[k].to(device))
+    mod.config = types.SimpleNamespace(frac_dt_min=1e-4, frac_dt_max=1.0, frac_alpha_min=0.2,
+                                       frac_alpha_max=0.95, frac_lambda_min=0.25, frac_lambda_max=4.0)
+    return mod
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_compute_params_on_golden(golden_dir, masked):
+    from frac_ssm_b200.layers import frac_compute_scan_params
+    g = _golden(golden_dir)
+    mod = _mixer(g, "cuda")
+    mask = g["mask"].cuda() if masked else None
+    out = frac_compute_scan_params(mod, g["x_conv"].cuda(), g["x"].cuda(), mask)
+    tag = "mask" if masked else "nomask"
+    ref, pt = g[f"params_exact_{tag}"], g[f"params_work_{tag}"]
+    for name, t in zip(("u", "c", "kappa", "rho"), out):
+        close(t, ref[name], **TOL_F32)
+        assert_ref_error(t, pt[name], ref[name], 1e-4)
+    if masked:   # mask identity: kappa = 0 and rho = 1 where the mask is 0
+        H = g["meta"]["H"]
+        dead = (g["mask"] == 0)[:, None, :].expand(-1, H, -1).reshape(-1, g["mask"].shape[1])
+        assert (out[2].cpu()[dead] == 0).all() and (out[3].cpu()[dead] == 1).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_compute_params_larger(dtype):
+    from frac_ssm_b200.layers import compute_params_from_projections
+    B, L, H, R, M = 2, 130, 6, 64, 128
+    g = torch.Generator().manual_seed(2)
+    dyn = torch.randn(B, L, 3 * H, generator=g).to(dtype)
+    rw = torch.randn(B, L, 2 * H * M, generator=g).to(dtype)
+    x = torch.randn(B, L, H * R, generator=g).to(dtype)
+    dt_bias = torch.randn(H, generator=g)
+    log_tau = torch.linspace(0.0, 11.09, M)
+    args = (dt_bias, torch.tensor([-2.0]), torch.tensor([-1.1]), log_tau, H, R, M, 1.0,
+            *CFG.values())
+    out = compute_params_from_projections(dyn.cuda(), rw.cuda(), x.cuda(), None, dt_bias.cuda(), -2.0,
+                                          -1.1, log_tau.cuda(), H, R, M, 1.0, *CFG.values())
+    ref = O.compute_params(dyn.double(), rw.double(), x, None, *args, exact=True)
+    pt = O.compute_params(dyn, rw, x, None, *args, exact=False)
+    assert torch.equal(out[0].cpu(), pt[0].contiguous())
+    for a, b, c_ in zip(out[1:], pt[1:], ref[1:]):
+        close(a, c_, **TOL_F32)
+        assert_ref_error(a, b, c_, 1e-4)
+
+
+def test_skip_mix_on_golden(golden_dir):
+    from frac_ssm_b200.layers import frac_skip_mix
+    g = _golden(golden_dir)
+    mod = _mixer(g, "cuda")
+    out = frac_skip_mix(mod, g["mixed_flat"].cuda(), g["x_conv"].cuda())
+    close(out, g["mix_exact"], **TOL_F32)
+    assert_ref_error(out, g["mix_work"], g["mix_exact"], 1e-4)
+    out16 = frac_skip_mix(mod, g["mixed_flat"].cuda().bfloat16(), g["x_conv"].cuda().bfloat16())
+    assert out16.dtype == torch.bfloat16
+    close(out16, g["mix_exact"], rtol=3e-2, atol=3e-2)
+
+
+def test_rmsnorm_gated_on_golden(golden_dir):
+    from frac_ssm_b200.modules import MambaRMSNormGated, rmsnorm_gated_fwd
+    g = _golden(golden_dir)
+    x, gate, w = g["norm_x"].cuda(), g["norm_gate"].cuda(), g["norm_w"].cuda()
+    y, rstd = rmsnorm_gated_fwd(x, w, gate, 1e-6)
+    assert y.shape == x.shape and rstd.shape == x.shape[:-1] and y.dtype == x.dtype
+    close(y, g["norm_exact"], **TOL_BF16)
+    assert_ref_error(y, g["norm_work"], g["norm_exact"], 1e-3)
+    y2, _ = rmsnorm_gated_fwd(x, w, None, 1e-6)
+    close(y2, g["norm_work_nogate"], **TOL_BF16)
+    mod = MambaRMSNormGated(48).cuda()
+    close(mod(x.float(), gate.float()), O.rmsnorm_gated(x.float().cpu(), torch.ones(48), gate.float().cpu(),
+                                                        exact=True), **TOL_F32)
+
+
+@pytest.mark.parametrize("rows,D", [(1, 1536), (33, 1536), (7, 4096), (5, 100)])
+def test_rmsnorm_gated_shapes(rows, D):
+    from frac_ssm_b200.modules import rmsnorm_gated_fwd
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, D, generator=g).bfloat16()
+    z = torch.randn(rows, D, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16()
+    y, rstd = rmsnorm_gated_fwd(x.cuda(), w.cuda(), z.cuda(), 1e-5)
+    ref = O.rmsnorm_gated(x, w, z, 1e-5, exact=True)
+    close(y, ref, **TOL_BF16)
+    v = (x.double() * F.silu(z.double()))
+    close(rstd, torch.rsqrt(v.pow(2).mean(-1) + 1e-5), **TOL_F32)
+
+
+def test_scan_epilogue_matches_unfused_pair():
+    from frac_ssm_b200.layers import scan_epilogue
+    B, L, H, R = 2, 50, 24, 64
+    g = torch.Generator().manual_seed(3)
+    h = torch.randn(B * H, L, R, generator=g).bfloat16()
+    x = torch.randn(B, L, H * R, generator=g).bfloat16()
+    z = torch.randn(B, L, H * R, generator=g).bfloat16()
+    D = torch.randn(H, R, generator=g)
+    w = (1 + 0.1 * torch.randn(H * R, generator=g)).bfloat16()
+    y = scan_epilogue(h.cuda(), x.cuda(), z.cuda(), D.cuda(), w.cuda(), H, R, 1e-6, gate_bias=0.5)
+    mixed = O.skip_mix(h, x, D, H, R, exact=True)
+    ref = O.rmsnorm_gated(mixed, w, z.double() + 0.5, 1e-6, exact=True)
+    close(y, ref, **TOL_BF16)

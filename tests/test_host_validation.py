@@ -1,0 +1,48 @@
+"""Host-side argument checks mirror the reference's messages (runs on CPU tensors)."""
+
+import pytest
+import torch
+
+from frac_ssm_b200 import ops
+from frac_ssm_b200.ops.b200 import frac_scan as backend_scan
+
+
+def test_cu_seqlens_rejected():
+    x = torch.zeros(1, 4, 2)
+    with pytest.raises(NotImplementedError, match="cu_seqlens is not supported yet"):
+        ops.frac_scan(x, x, x, x, 4, cu_seqlens=torch.tensor([0, 4]))
+
+
+def test_unknown_backend():
+    x = torch.zeros(1, 4, 2)
+    with pytest.raises(ValueError, match="Unknown backend"):
+        ops.frac_scan(x, x, x, x, 4, impl="nope")
+
+
+def test_rho_and_initial_state_dtype():
+    u = torch.zeros(1, 4, 2, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="rho must be float32"):
+        backend_scan(u, u, u, u, 4)
+    rho = torch.ones(1, 4, 2)
+    with pytest.raises(AssertionError, match="initial_state must be float32"):
+        backend_scan(u, u, u, rho, 4, torch.zeros(1, 2, 2, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("fn,args,pattern", [
+    (ops.chunk_cumsum, (torch.zeros(4, 2), 4), "3D"),
+    (ops.chunk_cumsum, (torch.zeros(1, 4, 2), 4), "CUDA"),
+    (ops.chunk_w, (torch.zeros(4, 2), torch.zeros(1, 4, 2), torch.zeros(1, 4, 2), 32), "3D"),
+    (ops.chunk_w, (torch.zeros(1, 4, 2),) * 3 + (32,), "CUDA"),
+    (ops.state_passing, (torch.zeros(1, 1, 2), torch.zeros(1, 1, 2)), "4D"),
+    (ops.chunk_readout, (torch.zeros(4, 2),) * 5 + (4,), "3D"),
+    (ops.chunk_fused_readout, (torch.zeros(4, 2),) * 5 + (4,), "3D"),
+    (ops.chunk_state, (torch.zeros(1, 4, 2),) * 3 + (4,), "CUDA"),
+])
+def test_stage_messages(fn, args, pattern):
+    with pytest.raises(AssertionError, match=pattern):
+        fn(*args)
+
+
+def test_cute_backend_is_reported_absent():
+    ok, why = ops.cute_supported()
+    assert not ok and "b200" in why
