@@ -187,8 +187,12 @@ def test_full_size_split_and_slab_properties(scan):
 
 def test_full_size_linearity(scan):
     u, c, kappa, rho = _full_inputs(B=48, seed=1)
+    # quantise u to multiples of 1/32 below 2 so that u + u2 is exact in bfloat16: what is left
+    # is the rounding of the three outputs (about 1.5 bfloat16 ulps, 2^-8 relative each)
+    u = (u.float().clamp(-1.9, 1.9) * 32).round().div(32).bfloat16()
     u2 = torch.roll(u, 1, dims=0)
     ha = scan(u, c, kappa, rho, 256).float()
     hb = scan(u2, c, kappa, rho, 256).float()
     hs = scan((u.float() + u2.float()).bfloat16(), c, kappa, rho, 256).float()
-    torch.testing.assert_close(hs, ha + hb, rtol=3e-2, atol=3e-2)
+    scale = max(1.0, ha.abs().max().item(), hb.abs().max().item())
+    torch.testing.assert_close(hs, ha + hb, rtol=2e-2, atol=2e-2 * scale)
