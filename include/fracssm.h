@@ -177,6 +177,17 @@ int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl
                           const void *weight, int w_dtype, float gate_bias, float eps, void *y,
                           int64_t Bt, int64_t L, int64_t H, int64_t R, void *stream);
 
+/*
+ * Diagnostic: one 128-row tcgen05 MMA tile, D[128,N] = A[128,128] * B[N,128]^T, with the
+ * shared-memory operand layouts the scan kernel uses (K-major / MN-major, strided row groups,
+ * TMA-loaded B).  A and B are float32 [128][128] tiles rounded to bf16 on staging; B_bf16
+ * (bf16 [128][64], dense) is only read when b_via_tma != 0.  status: device int, 0 = ok.
+ * No counterpart in the reference; used by the GPU tests.
+ */
+int fracssm_selftest_umma(const float *A, const float *B, const void *B_bf16, float *D, int *status,
+                          int a_mn_major, int b_mn_major, int N, int b_row_group0, int b_sbo_bytes,
+                          int b_via_tma, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
