@@ -1,18 +1,564 @@
-// Single-pass tcgen05 scan kernel: entry points used by frac_scan.cu.
+// Single-pass FRAC scan on sm_100a: every input is read once, the state stays on chip or
+// in L2, all contractions run on tcgen05 with accumulators in tensor memory.
+//
+// Shapes covered: R = 64, M = 128, bf16 u / c / kappa, fp32 rho, dense tensors, any L.
+//
+// Work item = (bh, tile of 128 tokens), handed out by an atomic ticket in tile-major order
+// (all bh of tile 0, then tile 1, ...).  The item (bh, j) needs the state left by (bh, j-1);
+// it waits on a per-bh counter in global memory with a time limit.  A ticket is only taken
+// by a running CTA and dependencies point to lower tickets, so the lowest unfinished item can
+// always proceed.
+//
+// Math per tile (tokens t, k in 0..127; modes m; rho floored at 1e-6, 1 beyond L):
+//   h[t]   = sum_m Chat[t,m] S[m,:]  +  sum_{k<=t} W[t,k] u[k,:]
+//   S_next = Gt (.) S + sum_k Khat[k,:]^T u[k,:]
+//   W[t,k] = sum_m c[t,m] kappa[k,m] prod_{k<j<=t} rho[j,m]
+// The decay product inside W is never formed as a ratio of two long products (which would
+// overflow).  W is assembled from pieces whose two factors are each <= 1:
+//   * sibling levels s = 64, 32, 16, 8: for t in the second half and k in the first half of a
+//     block of 2s tokens, the reference point is the boundary between the halves:
+//       A_s[t] = c[t] prod_{bnd<=j<=t} rho[j],  B_s[k] = kappa[k] prod_{k<j<bnd} rho[j]
+//     A-role and B-role rows share one operand tile X_s (every token has exactly one role);
+//   * base: the 8x8 diagonal blocks use the middle of the block as reference, which keeps
+//     the reciprocal products below 1e24.
+// Every piece is a bf16 tcgen05 GEMM over the modes; an epilogue picks, for each (t, k), the
+// accumulator of the one level that holds it.  Chat / Khat are the same factors taken to the
+// tile's start / end; Khat is split into bf16 high and low parts so that the state keeps
+// float32-level accuracy.
+#include <mutex>
+
 #include "common.cuh"
+#include "tmap.cuh"
+#include "umma.cuh"
 
 namespace fracssm {
+namespace {
 
-size_t scan_fused_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t) { return 0; }
+constexpr int kTile = 128, kR = 64, kM = 128, kThreads = 512;
+constexpr uint32_t kTileBytes = 32768;  // [128 x 128] bf16 operand tile
+constexpr uint32_t kAtom = 16384;       // one 64-column block of such a tile
+// shared memory map (bytes from the 1024-aligned base)
+constexpr uint32_t kOffArea0 = 0, kOffArea1 = 65536, kOffS = 131072, kOffU = 147456;
+constexpr uint32_t kOffSeg = 163840;    // float [16][128]: decay product of each 8-token segment
+constexpr uint32_t kOffGt = 172032;     // float [128]: decay product of the whole tile
+constexpr uint32_t kOffMisc = 172544;   // mbarriers, TMEM base, ticket
+constexpr uint32_t kSmemBytes = kOffMisc + 128 + 1024;
+// tensor-memory columns (fp32, 128 lanes each)
+constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
+                   kColL64 = 448;
+constexpr uint64_t kWaitNs = 2000000000ull;  // limit of every device-side wait
 
-int scan_fused_launch(const void *, const void *, const void *, int, const float *, const float *,
-                      void *, void *, int, void *, size_t, int64_t, int64_t, int64_t, int64_t,
-                      int64_t, void *) {
-  return fail(FRACSSM_ERR_UNSUPPORTED, "single-pass scan kernel not built");
+struct FusedArgs {
+  const __nv_bfloat16 *c, *kappa;
+  const float *rho, *init;
+  __nv_bfloat16 *h;
+  void *fin;
+  int fin_dt;
+  int *ctrl;     // [0] ticket counter, [1] error word
+  int *flags;    // [BH] tiles finished per bh
+  float *state;  // [BH][128 m][64 r] running state
+  int BH, L, ntiles, total;
+};
+
+__device__ __forceinline__ void emit4(uint8_t *tile, int row, int lane, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 pk;
+  pk.x = *reinterpret_cast<const uint32_t *>(&a);
+  pk.y = *reinterpret_cast<const uint32_t *>(&b);
+  const uint32_t off = (lane >> 4) * kAtom + row * 128 +
+                       (((((lane & 15) >> 1) ^ (row & 7)) << 4) | ((lane & 1) << 3));
+  *reinterpret_cast<uint2 *>(tile + off) = pk;
+}
+
+// Product of the segment decays seg[lo..hi) for this lane's four modes.
+__device__ __forceinline__ void seg_prod(const float *seg, int lo, int hi, int lane, float (&out)[4]) {
+  out[0] = out[1] = out[2] = out[3] = 1.f;
+  for (int s = lo; s < hi; ++s) {
+    const float4 g = *reinterpret_cast<const float4 *>(seg + s * kM + 4 * lane);
+    out[0] *= g.x; out[1] *= g.y; out[2] *= g.z; out[3] *= g.w;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&t);
+}
+
+__device__ __forceinline__ int ld_acquire(const int *p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int *p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *area0 = smem + kOffArea0, *area1 = smem + kOffArea1;
+  uint8_t *s_tile = smem + kOffS, *u_tile = smem + kOffU;
+  float *seg = reinterpret_cast<float *>(smem + kOffSeg);
+  float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
+  uint64_t *bar0 = reinterpret_cast<uint64_t *>(smem + kOffMisc);
+  uint64_t *bar1 = bar0 + 1, *barH = bar0 + 2, *barU = bar0 + 3;
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bar0 + 4);
+  int *item_s = reinterpret_cast<int *>(tmem_s + 1);
+
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
+
+  if (tid == 0) {
+    umma::mbar_init(bar0, 1);
+    umma::mbar_init(bar1, 1);
+    umma::mbar_init(barH, 1);
+    umma::mbar_init(barU, 1);
+    umma::fence_mbar_init();
+    umma::prefetch_tmap(&u_map);
+  }
+  if (w == 0) umma::tmem_alloc(tmem_s, 512);
+  umma::tc_fence_before();
+  __syncthreads();
+  umma::tc_fence_after();
+  const uint32_t tmem = *tmem_s;
+  const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
+
+  const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
+  const uint32_t sS = umma::smem_u32(s_tile), sU = umma::smem_u32(u_tile);
+  constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
+  constexpr uint32_t kIdKK64 = umma::make_idesc(128, 64, false, false);
+  constexpr uint32_t kIdKK32 = umma::make_idesc(128, 32, false, false);
+  constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
+  constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
+  // start offset of contraction step ks inside a K-major 128-column tile
+  auto koff = [](int ks) -> uint32_t { return (ks >> 2) * kAtom + (ks & 3) * 32; };
+
+  uint32_t ph0 = 0, ph1 = 0, phH = 0, phU = 0;  // completed phases of each mbarrier
+  bool ok = true;
+
+  while (true) {
+    if (tid == 0) *item_s = atomicAdd(&a.ctrl[0], 1);
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const int item = *item_s;
+    if (item >= a.total) break;
+    const int j = item / a.BH, bh = item - j * a.BH;
+    const int t0 = j * kTile;
+
+    if (tid == 0) {
+      umma::mbar_expect_tx(barU, kTile * kR * 2);
+      umma::tma_load_3d(u_tile, &u_map, barU, 0, t0, bh);
+    }
+    if (tid == 32) {  // pull the likely next tile of this CTA into L2
+      const int nxt = item + gridDim.x;
+      if (nxt < a.total) {
+        const int nj = nxt / a.BH, nb = nxt - nj * a.BH;
+        const int ntok = min(kTile, a.L - nj * kTile);
+        const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
+        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
+        umma::prefetch_l2(a.c + tok * kM, ntok * kM * 2);
+        umma::prefetch_l2(a.kappa + tok * kM, ntok * kM * 2);
+      }
+    }
+
+    // ---- P1: load this warp's 8 tokens x this lane's 4 modes; segment products; base tiles
+    float cp[8][4], ks[8][4], g8[4];
+    {
+      float rr[8][4];
+      uint2 cc[8], kk[8];
+      const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0 + 8 * w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool live = t0 + 8 * w + i < a.L;
+        float4 r4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        cc[i] = make_uint2(0u, 0u);
+        kk[i] = make_uint2(0u, 0u);
+        if (live) {
+          r4 = __ldcs(reinterpret_cast<const float4 *>(a.rho + (tok0 + i) * kM) + lane);
+          cc[i] = __ldcs(reinterpret_cast<const uint2 *>(a.c + (tok0 + i) * kM) + lane);
+          kk[i] = __ldcs(reinterpret_cast<const uint2 *>(a.kappa + (tok0 + i) * kM) + lane);
+        }
+        rr[i][0] = fmaxf(r4.x, kRhoFloor); rr[i][1] = fmaxf(r4.y, kRhoFloor);
+        rr[i][2] = fmaxf(r4.z, kRhoFloor); rr[i][3] = fmaxf(r4.w, kRhoFloor);
+      }
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        float a0[8][2], b0[8][2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int q = 2 * pair + e;
+          // p4: running product from the start of each group of 4 tokens (inclusive)
+          // s4: product of the tokens after t up to the end of its group of 4 (exclusive)
+          float p4[8], s4[8];
+          p4[0] = rr[0][q]; p4[1] = p4[0] * rr[1][q]; p4[2] = p4[1] * rr[2][q]; p4[3] = p4[2] * rr[3][q];
+          p4[4] = rr[4][q]; p4[5] = p4[4] * rr[5][q]; p4[6] = p4[5] * rr[6][q]; p4[7] = p4[6] * rr[7][q];
+          s4[3] = 1.f; s4[2] = rr[3][q]; s4[1] = s4[2] * rr[2][q]; s4[0] = s4[1] * rr[1][q];
+          s4[7] = 1.f; s4[6] = rr[7][q]; s4[5] = s4[6] * rr[6][q]; s4[4] = s4[5] * rr[5][q];
+          const float ga = p4[3], gb = p4[7];
+          g8[q] = ga * gb;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t cw = pair ? cc[i].y : cc[i].x, kw = pair ? kk[i].y : kk[i].x;
+            const float cf = __uint_as_float(e ? (cw & 0xFFFF0000u) : (cw << 16));
+            const float kf = __uint_as_float(e ? (kw & 0xFFFF0000u) : (kw << 16));
+            if (i < 4) {  // base reference point: between token 3 and token 4 of the segment
+              a0[i][e] = __fdividef(cf, s4[i]);
+              b0[i][e] = kf * s4[i];
+              cp[i][q] = cf * p4[i];
+              ks[i][q] = kf * s4[i] * gb;
+            } else {
+              a0[i][e] = cf * p4[i];
+              b0[i][e] = __fdividef(kf, p4[i]);
+              cp[i][q] = cf * ga * p4[i];
+              ks[i][q] = kf * s4[i];
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = 8 * w + i;
+          const uint32_t off = (lane >> 4) * kAtom + row * 128 +
+                               (((((lane & 15) >> 1) ^ (row & 7)) << 4) | ((lane & 1) << 3) | (pair << 2));
+          *reinterpret_cast<uint32_t *>(area0 + off) = pack2(a0[i][0], a0[i][1]);
+          *reinterpret_cast<uint32_t *>(area0 + kTileBytes + off) = pack2(b0[i][0], b0[i][1]);
+        }
+      }
+      *reinterpret_cast<float4 *>(seg + w * kM + 4 * lane) = make_float4(g8[0], g8[1], g8[2], g8[3]);
+    }
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {  // base: D[t,k] = A0[t,:] . B0[k,:]
+      umma::tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        umma::mma_ss(tmem + kColBase, umma::make_sdesc(sA0 + koff(s), 16, 1024),
+                     umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024), kIdKK128, s > 0);
+      umma::mma_commit(bar0);
+    }
+
+    // One sibling level: every token row holds its A-role or B-role value.
+    auto produce_level = [&](uint8_t *tile, int hseg) {
+      float sig[4];
+      const bool role_a = (w & hseg) != 0;
+      const int first = w - (w & (hseg - 1));
+      if (role_a) seg_prod(seg, first, w, lane, sig);
+      else seg_prod(seg, w + 1, first + hseg, lane, sig);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = (role_a ? cp[i][q] : ks[i][q]) * sig[q];
+        emit4(tile, 8 * w + i, lane, v);
+      }
+    };
+
+    // ---- levels 8 and 16 -> area1
+    produce_level(area1, 1);
+    produce_level(area1 + kTileBytes, 2);
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      umma::tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // level 8: first halves are every other 8-row group
+        umma::mma_ss(tmem + kColL8, umma::make_sdesc(sA1 + koff(s), 16, 1024),
+                     umma::make_sdesc(sA1 + koff(s), 16, 2048), kIdKK64, s > 0);
+#pragma unroll
+      for (int half = 0; half < 2; ++half)  // level 16: groups {0,4,8,12} then {1,5,9,13}
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma::mma_ss(tmem + kColL16 + 32 * half, umma::make_sdesc(sA1 + kTileBytes + koff(s), 16, 1024),
+                       umma::make_sdesc(sA1 + kTileBytes + half * 1024 + koff(s), 16, 4096), kIdKK32, s > 0);
+      umma::mma_commit(bar1);
+    }
+
+    // ---- levels 32 and 64 -> area0 (after the base MMAs have read it)
+    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
+    produce_level(area0, 4);
+    produce_level(area0 + kTileBytes, 8);
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      umma::tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half)  // level 32: rows 0..31 then rows 64..95
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma::mma_ss(tmem + kColL32 + 32 * half, umma::make_sdesc(sA0 + koff(s), 16, 1024),
+                       umma::make_sdesc(sA0 + half * 8192 + koff(s), 16, 1024), kIdKK32, s > 0);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // level 64: rows 0..63
+        umma::mma_ss(tmem + kColL64, umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024),
+                     umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024), kIdKK64, s > 0);
+      umma::mma_commit(bar0);
+    }
+
+    // ---- Chat and Khat(high) -> area1 (after levels 8/16 have read it)
+    ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;
+    {
+      float e[4], f[4];
+      seg_prod(seg, 0, w, lane, e);
+      seg_prod(seg, w + 1, 16, lane, f);
+      if (w == 0)
+        *reinterpret_cast<float4 *>(gt_s + 4 * lane) =
+            make_float4(g8[0] * f[0], g8[1] * f[1], g8[2] * f[2], g8[3] * f[3]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v[4], kh[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          v[q] = cp[i][q] * e[q];
+          const float full = ks[i][q] * f[q];
+          kh[q] = __bfloat162float(__float2bfloat16_rn(full));
+          ks[i][q] = full - kh[q];  // low part, emitted with the next batch
+        }
+        emit4(area1, 8 * w + i, lane, v);
+        emit4(area1 + kTileBytes, 8 * w + i, lane, kh);
+      }
+    }
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      ok = umma::mbar_wait(barU, phU & 1, kWaitNs) && ok;
+      umma::tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // Sacc[m,r] = sum_k Khi[k,m] u[k,r]
+        umma::mma_ss(tmem + kColS, umma::make_sdesc(sA1 + kTileBytes + s * 2048, kAtom, 1024),
+                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdMnMn64, s > 0);
+      umma::mma_commit(bar1);
+    }
+    ++phU;
+
+    // ---- Khat(low) and W -> area0 (after every level MMA has completed)
+    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
+    umma::tc_fence_after();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) emit4(area0, 8 * w + i, lane, ks[i]);
+    {
+      uint8_t *wt = area0 + kTileBytes;
+      const int t = 32 * Q + lane;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float v[8];
+        if (P > Q) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) v[x] = 0.f;
+        } else if (P < Q) {
+          const uint32_t col = ((Q >> 1) != (P >> 1)) ? (kColL64 + 32 * P + 8 * g)
+                                                      : (kColL32 + (P >> 1) * 32 + 8 * g);
+          umma::tmem_ld8(lane_addr + col, v);
+          umma::tmem_ld_wait();
+        } else {
+          float b[8], l8[8], l16[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) l8[x] = l16[x] = 0.f;
+          umma::tmem_ld8(lane_addr + kColBase + 32 * Q + 8 * g, b);
+          if ((g & 1) == 0) umma::tmem_ld8(lane_addr + kColL8 + (2 * Q + (g >> 1)) * 8, l8);
+          if (g < 2) umma::tmem_ld8(lane_addr + kColL16 + (g & 1) * 32 + Q * 8, l16);
+          umma::tmem_ld_wait();
+          const int tb = lane >> 3;  // 8-token block of this row inside its 32-token block
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            float r = 0.f;
+            if (g == tb) r = (x <= (lane & 7)) ? b[x] : 0.f;
+            else if (g < tb) r = ((tb ^ g) >= 2) ? l16[x] : l8[x];
+            v[x] = r;
+          }
+        }
+        uint4 pk;
+        pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
+        const uint32_t chunk = (4 * P + g) & 7;
+        *reinterpret_cast<uint4 *>(wt + (P >> 1) * kAtom + t * 128 + ((chunk ^ (t & 7)) << 4)) = pk;
+      }
+    }
+    umma::fence_async_smem();
+    umma::tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      umma::tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // Sacc += Klo^T u
+        umma::mma_ss(tmem + kColS, umma::make_sdesc(sA0 + s * 2048, kAtom, 1024),
+                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdMnMn64, 1u);
+      umma::mma_commit(bar0);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // H = W u
+        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024),
+                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdKMn64, s > 0);
+      // wait for the state left by the previous tile of this (batch, head) row
+      if (j > 0) {
+        const uint64_t t_start = umma::global_ns();
+        while (ld_acquire(a.flags + bh) < j) {
+          __nanosleep(100);
+          if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- incoming state: float32 copy in registers, bf16 copy as the MMA operand
+    const int m_row = 32 * Q + lane;
+    float sj[16];
+    {
+      float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+      if (j > 0) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float4 v = __ldcg(reinterpret_cast<const float4 *>(sp) + x);
+          sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
+        }
+      } else if (a.init) {
+#pragma unroll
+        for (int x = 0; x < 16; ++x)
+          sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
+      } else {
+#pragma unroll
+        for (int x = 0; x < 16; ++x) sj[x] = 0.f;
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint4 pk;
+        pk.x = pack2(sj[8 * half], sj[8 * half + 1]); pk.y = pack2(sj[8 * half + 2], sj[8 * half + 3]);
+        pk.z = pack2(sj[8 * half + 4], sj[8 * half + 5]); pk.w = pack2(sj[8 * half + 6], sj[8 * half + 7]);
+        const uint32_t chunk = 2 * P + half;
+        *reinterpret_cast<uint4 *>(s_tile + m_row * 128 + ((chunk ^ (m_row & 7)) << 4)) = pk;
+      }
+    }
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // H += Chat S
+        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA1 + koff(s), 16, 1024),
+                     umma::make_sdesc(sS + s * 2048, kAtom, 1024), kIdKMn64, 1u);
+      umma::mma_commit(barH);
+    }
+
+    // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
+    ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;   // Khat(high) MMAs
+    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;   // Khat(low) MMAs
+    umma::tc_fence_after();
+    {
+      float acc[16];
+      umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
+      umma::tmem_ld_wait();
+      const float gt = gt_s[m_row];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) sj[x] = fmaf(gt, sj[x], acc[x]);
+      float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+      if (j + 1 < a.ntiles) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+          __stcg(reinterpret_cast<float4 *>(sp) + x,
+                 make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
+      } else if (a.fin) {
+#pragma unroll
+        for (int x = 0; x < 16; ++x)
+          st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, sj[x]);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
+
+    // ---- output rows
+    ok = umma::mbar_wait(barH, phH & 1, kWaitNs) && ok; ++phH;
+    umma::tc_fence_after();
+    {
+      float acc[16];
+      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
+      umma::tmem_ld_wait();
+      const int t = t0 + 32 * Q + lane;
+      if (t < a.L) {
+        uint4 lo, hi;
+        lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
+        hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
+        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(bh) * a.L + t) * kR + 16 * P);
+        __stcs(dst, lo);
+        __stcs(dst + 1, hi);
+      }
+    }
+  }
+
+  if (!ok) atomicExch(&a.ctrl[1], 1);
+  umma::tc_fence_before();
+  __syncthreads();
+  if (w == 0) umma::tmem_dealloc(tmem, 512);
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+
+size_t scan_fused_workspace_bytes(int64_t B, int64_t, int64_t R, int64_t M, int64_t) {
+  return 256 + align256((size_t)B * 4) + (size_t)B * R * M * 4;
+}
+
+int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
+                      const float *initial_state, void *h, void *final_state, int final_dtype,
+                      void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                      int64_t M, int64_t T, void *stream) {
+  (void)T; (void)ck_dtype;
+  if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
+    return fail(FRACSSM_ERR_ARG, "frac_scan: workspace too small");
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(scan_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(attr_err));
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot query the SM count");
+
+  char *ws = reinterpret_cast<char *>(workspace);
+  FusedArgs a{};
+  a.c = reinterpret_cast<const __nv_bfloat16 *>(c);
+  a.kappa = reinterpret_cast<const __nv_bfloat16 *>(kappa);
+  a.rho = rho;
+  a.init = initial_state;
+  a.h = reinterpret_cast<__nv_bfloat16 *>(h);
+  a.fin = final_state;
+  a.fin_dt = final_dtype;
+  a.ctrl = reinterpret_cast<int *>(ws);
+  a.flags = reinterpret_cast<int *>(ws + 256);
+  a.state = reinterpret_cast<float *>(ws + 256 + align256((size_t)B * 4));
+  a.BH = (int)B;
+  a.L = (int)L;
+  a.ntiles = (int)ceil_div(L, kTile);
+  a.total = a.ntiles * a.BH;
+  CUtensorMap map;
+  int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
+  if (rc) return rc;
+  cudaError_t e = cudaMemsetAsync(ws, 0, 256 + align256((size_t)B * 4), (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
+  const int grid = a.total < sms ? a.total : sms;
+  scan_fused_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
+  return check_launch("frac_scan (single-pass kernel)");
 }
 
 }  // namespace fracssm
 
-extern "C" int fracssm_scan_fused_supported(int64_t, int64_t, int64_t, int64_t, int64_t, int, int) {
-  return 0;
+extern "C" int fracssm_scan_fused_supported(int64_t B, int64_t L, int64_t R, int64_t M, int64_t T,
+                                            int u_dtype, int ck_dtype) {
+  (void)T;
+  using namespace fracssm;
+  return B >= 1 && L >= 1 && R == kR && M == kM && u_dtype == FRACSSM_BF16 && ck_dtype == FRACSSM_BF16 &&
+         B * ceil_div(L, kTile) < (int64_t(1) << 30) && L < (int64_t(1) << 30);
+}
+
+// Reads back the error word of the last single-pass launch that used `workspace`
+// (synchronises the stream).  0 = ok, FRACSSM_ERR_WAIT if a device-side wait ran out.
+extern "C" int fracssm_scan_fused_status(const void *workspace, void *stream) {
+  using namespace fracssm;
+  if (!workspace) return fail(FRACSSM_ERR_ARG, "scan_fused_status: null workspace");
+  int ctrl[2] = {0, 0};
+  cudaError_t e = cudaMemcpyAsync(ctrl, workspace, sizeof(ctrl), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "scan_fused_status: %s", cudaGetErrorString(e));
+  if (ctrl[1] != 0) return fail(FRACSSM_ERR_WAIT, "single-pass scan: a device-side wait ran out");
+  return FRACSSM_OK;
 }

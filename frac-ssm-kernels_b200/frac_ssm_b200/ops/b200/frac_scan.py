@@ -15,7 +15,7 @@ _PATHS = {"auto": C.PATH_AUTO, "staged": C.PATH_STAGED, "fused": C.PATH_FUSED}
 
 
 def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False, *,
-              final_state_dtype=None, path="auto"):
+              final_state_dtype=None, path="auto", check=False):
     """Fractional chunked scan, forward.
 
     Args:
@@ -28,6 +28,8 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
         final_state_dtype: dtype of the returned state; default follows the reference
             (bfloat16 when u is bfloat16, else float32).  The state is always carried in float32.
         path: "auto", "staged" or "fused".
+        check: after the launch, synchronise and raise if a bounded device-side wait of the
+            single-pass kernel ran out (debugging aid; the default stays asynchronous).
     Returns:
         h [B, L, R] in u.dtype, and final_state [B, R, M] if requested.
     """
@@ -72,6 +74,9 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
                 c.stride(0), c.stride(1), kappa.stride(0), kappa.stride(1), C.ptr(rho), rho.stride(0),
                 rho.stride(1), C.ptr(init), C.ptr(h), C.ptr(fin), C.dt_of(final_state_dtype),
                 C.ptr(ws), ws.numel(), B, L, R, M, chunk_size, p, C.stream_of(u)), "frac_scan")
+            if check and L > 0 and p != C.PATH_STAGED and u.is_contiguous() and lib.fracssm_scan_fused_supported(
+                    B, L, R, M, chunk_size, C.dt(u), C.dt(c)):
+                C.check(lib.fracssm_scan_fused_status(C.ptr(ws), C.stream_of(u)), "frac_scan")
     if return_final_state:
         return h, fin
     return h

@@ -130,6 +130,14 @@ int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl
                           int64_t M, int64_t T, int path, void *stream);
 
 /*
+ * Reads back the error word of the last single-pass launch that used `workspace` (this call
+ * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
+ * (for a predecessor tile's state, a TMA load or an MMA) ran out and the results are invalid.
+ * No counterpart in the reference (its kernels have no cross-CTA waits).
+ */
+int fracssm_scan_fused_status(const void *workspace, void *stream);
+
+/*
  * Elementwise scan-parameter prep after the two projections.
  * dyn [Bt, L, 3H] (dt, alpha, lambda logits), rw [Bt, L, 2*H*M] (read then write residuals),
  * x_conv [Bt, L, H*R]; mask [Bt, L] f32 or NULL; dt_bias [H], base_log_tau [M] f32;

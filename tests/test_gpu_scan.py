@@ -43,7 +43,7 @@ def _oracle(key, u, c, kappa, rho, T, init):
 def _check(scan, u, c, kappa, rho, T, init, path="auto", key=None):
     ug, cg, kg, rg = cuda(u, c, kappa, rho)
     ig = None if init is None else init.cuda()
-    h, fin = scan(ug, cg, kg, rg, T, ig, True, final_state_dtype=torch.float32, path=path)
+    h, fin = scan(ug, cg, kg, rg, T, ig, True, final_state_dtype=torch.float32, path=path, check=True)
     key = key or (tuple(u.shape), c.shape[-1], T, u.dtype, c.dtype, init is None,
                   float(rho.double().sum()), float(u.double().sum()))
     (h_ref, fin_ref), (h_pt, fin_pt) = _oracle(key, u, c, kappa, rho, T, init)
@@ -61,6 +61,7 @@ def _check(scan, u, c, kappa, rho, T, init, path="auto", key=None):
 @pytest.mark.parametrize("B,L,R,M,T", [
     (1, 1, 64, 16, 64), (17, 32, 64, 16, 64), (2, 4001, 64, 16, 128), (1, 4096, 128, 16, 64),
     (3, 1000, 64, 128, 256), (2, 2048, 64, 128, 256), (2, 700, 192, 16, 128), (2, 515, 64, 64, 64),
+    (5, 129, 64, 128, 64), (1, 128, 64, 128, 128), (300, 257, 64, 128, 256), (2, 4096, 64, 128, 256),
 ])
 def test_scan_bf16(scan, path, gen, with_init, B, L, R, M, T):
     u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, dtype=torch.bfloat16, gen=gen, seed=0)
@@ -167,7 +168,7 @@ def test_full_size_split_and_slab_properties(scan):
     (3) the final state equals the token recurrence's on one row."""
     u, c, kappa, rho = _full_inputs()
     T = 256
-    h, fin = scan(u, c, kappa, rho, T, None, True, final_state_dtype=torch.float32)
+    h, fin = scan(u, c, kappa, rho, T, None, True, final_state_dtype=torch.float32, check=True)
     half = u.shape[1] // 2
     h1, f1 = scan(u[:, :half], c[:, :half], kappa[:, :half], rho[:, :half], T, None, True,
                   final_state_dtype=torch.float32)
@@ -196,3 +197,26 @@ def test_full_size_linearity(scan):
     hs = scan((u.float() + u2.float()).bfloat16(), c, kappa, rho, 256).float()
     scale = max(1.0, ha.abs().max().item(), hb.abs().max().item())
     torch.testing.assert_close(hs, ha + hb, rtol=2e-2, atol=2e-2 * scale)
+
+
+def test_fused_path_is_taken_and_matches_staged(scan):
+    """The single-pass tcgen05 kernel against the staged kernels on the same inputs."""
+    from frac_ssm_b200 import _cabi as C
+    assert C.lib().fracssm_scan_fused_supported(6, 1000, 64, 128, 256, C.BF16, C.BF16) == 1
+    u, c, kappa, rho, init = cuda(*O.scan_inputs(6, 1000, 64, 128, gen="model_like", seed=21))
+    hf, ff = scan(u, c, kappa, rho, 256, init, True, final_state_dtype=torch.float32, path="fused", check=True)
+    hs, fs = scan(u, c, kappa, rho, 256, init, True, final_state_dtype=torch.float32, path="staged")
+    torch.testing.assert_close(hf.float(), hs.float(), **TOL_BF16)
+    torch.testing.assert_close(ff, fs, **TOL_F32)
+    with pytest.raises(Exception, match="not covered"):
+        scan(u[:, :, :32].contiguous(), c, kappa, rho, 256, path="fused")
+
+
+def test_fused_adversarial_decay(scan):
+    """Modes pinned at the 1e-6 floor next to modes that never decay: the factorisation must stay
+    finite and exact."""
+    u, c, kappa, rho, _ = O.scan_inputs(2, 512, 64, 128, dtype=torch.bfloat16, gen="random", seed=5)
+    rho[:, :, :64] = 1e-7
+    rho[:, 40:400, 64:96] = 1.0
+    rho[:, ::3, 96:] = 1e-6
+    _check(scan, u, c, kappa, rho, 256, None, "fused")
