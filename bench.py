@@ -196,6 +196,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "staged", "fused"])
     ap.add_argument("--seq-len", type=int, default=None,
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
+    ap.add_argument("--phases", action="store_true",
+                    help="also print the single-pass kernel's per-phase cycle shares (diagnostic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -303,6 +305,13 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": ems, "steps": k2}
         del host, y_host
 
+    if rank == 0 and args.phases and use_fused:
+        from frac_ssm_b200.ops.b200.frac_scan import last_phase_cycles
+        frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path, keep_workspace=True)
+        cyc = last_phase_cycles()
+        tot = max(1, sum(cyc))
+        print("phase shares:", " ".join(f"{i}:{100.0 * v / tot:.1f}%" for i, v in enumerate(cyc)),
+              f"| cycles per tile {tot / (BH * ((L + 127) // 128)):.0f}", file=sys.stderr, flush=True)
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         alg = algorithmic_bytes(BH, L, R, M)

@@ -38,15 +38,20 @@ constexpr int kTile = 128, kR = 64, kM = 128, kThreads = 512;
 constexpr uint32_t kTileBytes = 32768;  // [128 x 128] bf16 operand tile
 constexpr uint32_t kAtom = 16384;       // one 64-column block of such a tile
 // shared memory map (bytes from the 1024-aligned base)
-constexpr uint32_t kOffArea0 = 0, kOffArea1 = 65536, kOffS = 131072, kOffU = 147456;
-constexpr uint32_t kOffSeg = 163840;    // float [16][128]: decay product of each 8-token segment
-constexpr uint32_t kOffGt = 172032;     // float [128]: decay product of the whole tile
-constexpr uint32_t kOffMisc = 172544;   // mbarriers, TMEM base, ticket
-constexpr uint32_t kSmemBytes = kOffMisc + 128 + 1024;
+constexpr uint32_t kOffArea0 = 0, kOffArea1 = 65536;
+constexpr uint32_t kOffChatLo = 131072;                  // low part of Chat, one operand tile
+constexpr uint32_t kOffS = 163840, kOffSlo = 180224;     // incoming state, bf16 high and low parts
+constexpr uint32_t kOffU = 196608;
+constexpr uint32_t kOffSeg = 212992;    // float [16][128]: decay product of each 8-token segment
+constexpr uint32_t kOffGt = 221184;     // float [128]: decay product of the whole tile
+constexpr uint32_t kOffMisc = 221696;   // mbarriers, TMEM base, ticket
+constexpr uint32_t kSmemBytes = kOffMisc + 128 + 128 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
 constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
                    kColL64 = 448;
 constexpr uint64_t kWaitNs = 2000000000ull;  // limit of every device-side wait
+constexpr int kProfCtas = 256, kProfPhases = 16;
+constexpr size_t kCtrlBytes = 256, kProfBytes = kProfCtas * kProfPhases * sizeof(long long);
 
 struct FusedArgs {
   const __nv_bfloat16 *c, *kappa;
@@ -55,6 +60,7 @@ struct FusedArgs {
   void *fin;
   int fin_dt;
   int *ctrl;     // [0] ticket counter, [1] error word
+  long long *prof;  // [kProfCtas][16] cycles spent per phase by thread 0 of each CTA
   int *flags;    // [BH] tiles finished per bh
   float *state;  // [BH][128 m][64 r] running state
   int BH, L, ntiles, total;
@@ -98,7 +104,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *area0 = smem + kOffArea0, *area1 = smem + kOffArea1;
-  uint8_t *s_tile = smem + kOffS, *u_tile = smem + kOffU;
+  uint8_t *s_tile = smem + kOffS, *slo_tile = smem + kOffSlo, *u_tile = smem + kOffU;
+  uint8_t *chat_lo = smem + kOffChatLo;
   float *seg = reinterpret_cast<float *>(smem + kOffSeg);
   float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
   uint64_t *bar0 = reinterpret_cast<uint64_t *>(smem + kOffMisc);
@@ -125,7 +132,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
 
   const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
-  const uint32_t sS = umma::smem_u32(s_tile), sU = umma::smem_u32(u_tile);
+  const uint32_t sS = umma::smem_u32(s_tile), sSlo = umma::smem_u32(slo_tile), sU = umma::smem_u32(u_tile);
+  const uint32_t sClo = umma::smem_u32(chat_lo);
   constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
   constexpr uint32_t kIdKK64 = umma::make_idesc(128, 64, false, false);
   constexpr uint32_t kIdKK32 = umma::make_idesc(128, 32, false, false);
@@ -136,6 +144,17 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
   uint32_t ph0 = 0, ph1 = 0, phH = 0, phU = 0;  // completed phases of each mbarrier
   bool ok = true;
+  // thread 0 charges the cycles since the last mark to a phase (diagnostic, a few clock reads per tile)
+  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 128);  // thread 0 only
+  if (tid == 0)
+    for (int i = 0; i < kProfPhases; ++i) prof[i] = 0;
+  long long t_mark = clock64();
+#define FRACSSM_MARK(phase)                         \
+  if (tid == 0) {                                   \
+    const long long now_ = clock64();               \
+    prof[phase] += now_ - t_mark;                   \
+    t_mark = now_;                                  \
+  }
 
   while (true) {
     if (tid == 0) *item_s = atomicAdd(&a.ctrl[0], 1);
@@ -144,6 +163,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     umma::tc_fence_after();
     const int item = *item_s;
     if (item >= a.total) break;
+    FRACSSM_MARK(0)
     const int j = item / a.BH, bh = item - j * a.BH;
     const int t0 = j * kTile;
 
@@ -229,6 +249,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     }
     umma::fence_async_smem();
     __syncthreads();
+    FRACSSM_MARK(1)
     if (tid == 0) {  // base: D[t,k] = A0[t,:] . B0[k,:]
       umma::tc_fence_after();
 #pragma unroll
@@ -259,6 +280,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     produce_level(area1 + kTileBytes, 2);
     umma::fence_async_smem();
     __syncthreads();
+    FRACSSM_MARK(2)
     if (tid == 0) {
       umma::tc_fence_after();
 #pragma unroll
@@ -275,7 +297,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     }
 
     // ---- levels 32 and 64 -> area0 (after the base MMAs have read it)
+    FRACSSM_MARK(3)
     ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
+    FRACSSM_MARK(4)
     produce_level(area0, 4);
     produce_level(area0 + kTileBytes, 8);
     umma::fence_async_smem();
@@ -296,7 +320,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     }
 
     // ---- Chat and Khat(high) -> area1 (after levels 8/16 have read it)
+    FRACSSM_MARK(5)
     ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;
+    FRACSSM_MARK(6)
     {
       float e[4], f[4];
       seg_prod(seg, 0, w, lane, e);
@@ -306,20 +332,24 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             make_float4(g8[0] * f[0], g8[1] * f[1], g8[2] * f[2], g8[3] * f[3]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float v[4], kh[4];
+        float v[4], vl[4], kh[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          v[q] = cp[i][q] * e[q];
+          const float chat = cp[i][q] * e[q];
+          v[q] = __bfloat162float(__float2bfloat16_rn(chat));
+          vl[q] = chat - v[q];
           const float full = ks[i][q] * f[q];
           kh[q] = __bfloat162float(__float2bfloat16_rn(full));
           ks[i][q] = full - kh[q];  // low part, emitted with the next batch
         }
         emit4(area1, 8 * w + i, lane, v);
+        emit4(chat_lo, 8 * w + i, lane, vl);
         emit4(area1 + kTileBytes, 8 * w + i, lane, kh);
       }
     }
     umma::fence_async_smem();
     __syncthreads();
+    FRACSSM_MARK(7)
     if (tid == 0) {
       ok = umma::mbar_wait(barU, phU & 1, kWaitNs) && ok;
       umma::tc_fence_after();
@@ -332,7 +362,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     ++phU;
 
     // ---- Khat(low) and W -> area0 (after every level MMA has completed)
+    FRACSSM_MARK(8)
     ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
+    FRACSSM_MARK(9)
     umma::tc_fence_after();
 #pragma unroll
     for (int i = 0; i < 8; ++i) emit4(area0, 8 * w + i, lane, ks[i]);
@@ -376,6 +408,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     umma::fence_async_smem();
     umma::tc_fence_before();
     __syncthreads();
+    FRACSSM_MARK(10)
     if (tid == 0) {
       umma::tc_fence_after();
 #pragma unroll
@@ -397,6 +430,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
     }
     __syncthreads();
+    FRACSSM_MARK(11)
 
     // ---- incoming state: float32 copy in registers, bf16 copy as the MMA operand
     const int m_row = 32 * Q + lane;
@@ -419,26 +453,44 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint4 pk;
-        pk.x = pack2(sj[8 * half], sj[8 * half + 1]); pk.y = pack2(sj[8 * half + 2], sj[8 * half + 3]);
-        pk.z = pack2(sj[8 * half + 4], sj[8 * half + 5]); pk.w = pack2(sj[8 * half + 6], sj[8 * half + 7]);
-        const uint32_t chunk = 2 * P + half;
-        *reinterpret_cast<uint4 *>(s_tile + m_row * 128 + ((chunk ^ (m_row & 7)) << 4)) = pk;
+        float hi[8], lo[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
+          lo[x] = sj[8 * half + x] - hi[x];
+        }
+        uint4 pk, pl;
+        pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
+        pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
+        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+        *reinterpret_cast<uint4 *>(s_tile + off) = pk;
+        *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
       }
     }
     umma::fence_async_smem();
     __syncthreads();
     if (tid == 0) {
+      // H += Chat S with both factors split into bf16 high and low parts (low x low dropped)
 #pragma unroll
-      for (int s = 0; s < 8; ++s)  // H += Chat S
+      for (int s = 0; s < 8; ++s)
         umma::mma_ss(tmem + kColH, umma::make_sdesc(sA1 + koff(s), 16, 1024),
                      umma::make_sdesc(sS + s * 2048, kAtom, 1024), kIdKMn64, 1u);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        umma::mma_ss(tmem + kColH, umma::make_sdesc(sClo + koff(s), 16, 1024),
+                     umma::make_sdesc(sS + s * 2048, kAtom, 1024), kIdKMn64, 1u);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA1 + koff(s), 16, 1024),
+                     umma::make_sdesc(sSlo + s * 2048, kAtom, 1024), kIdKMn64, 1u);
       umma::mma_commit(barH);
     }
 
     // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
+    FRACSSM_MARK(12)
     ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;   // Khat(high) MMAs
     ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;   // Khat(low) MMAs
+    FRACSSM_MARK(13)
     umma::tc_fence_after();
     {
       float acc[16];
@@ -462,9 +514,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     __threadfence();
     __syncthreads();
     if (tid == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
+    FRACSSM_MARK(14)
 
     // ---- output rows
     ok = umma::mbar_wait(barH, phH & 1, kWaitNs) && ok; ++phH;
+    FRACSSM_MARK(15)
     umma::tc_fence_after();
     {
       float acc[16];
@@ -482,6 +536,10 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     }
   }
 
+  if (tid == 0 && a.prof && blockIdx.x < kProfCtas) {
+#pragma unroll
+    for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
+  }
   if (!ok) atomicExch(&a.ctrl[1], 1);
   umma::tc_fence_before();
   __syncthreads();
@@ -493,7 +551,7 @@ size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 }  // namespace
 
 size_t scan_fused_workspace_bytes(int64_t B, int64_t, int64_t R, int64_t M, int64_t) {
-  return 256 + align256((size_t)B * 4) + (size_t)B * R * M * 4;
+  return kCtrlBytes + kProfBytes + align256((size_t)B * 4) + (size_t)B * R * M * 4;
 }
 
 int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
@@ -524,8 +582,9 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   a.fin = final_state;
   a.fin_dt = final_dtype;
   a.ctrl = reinterpret_cast<int *>(ws);
-  a.flags = reinterpret_cast<int *>(ws + 256);
-  a.state = reinterpret_cast<float *>(ws + 256 + align256((size_t)B * 4));
+  a.prof = reinterpret_cast<long long *>(ws + kCtrlBytes);
+  a.flags = reinterpret_cast<int *>(ws + kCtrlBytes + kProfBytes);
+  a.state = reinterpret_cast<float *>(ws + kCtrlBytes + kProfBytes + align256((size_t)B * 4));
   a.BH = (int)B;
   a.L = (int)L;
   a.ntiles = (int)ceil_div(L, kTile);
@@ -533,7 +592,7 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
   if (rc) return rc;
-  cudaError_t e = cudaMemsetAsync(ws, 0, 256 + align256((size_t)B * 4), (cudaStream_t)stream);
+  cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + kProfBytes + align256((size_t)B * 4), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
   scan_fused_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
@@ -560,5 +619,22 @@ extern "C" int fracssm_scan_fused_status(const void *workspace, void *stream) {
   if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "scan_fused_status: %s", cudaGetErrorString(e));
   if (ctrl[1] != 0) return fail(FRACSSM_ERR_WAIT, "single-pass scan: a device-side wait ran out");
+  return FRACSSM_OK;
+}
+
+// Diagnostic: cycles thread 0 of each CTA spent in each of the 16 phases of the tile loop during
+// the last single-pass launch that used `workspace`, summed over CTAs (synchronises the stream).
+extern "C" int fracssm_scan_fused_phase_cycles(const void *workspace, long long *out16, void *stream) {
+  using namespace fracssm;
+  if (!workspace || !out16) return fail(FRACSSM_ERR_ARG, "scan_fused_phase_cycles: null pointer");
+  static long long host[kProfCtas * kProfPhases];
+  cudaError_t e = cudaMemcpyAsync(host, reinterpret_cast<const char *>(workspace) + kCtrlBytes, kProfBytes,
+                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "scan_fused_phase_cycles: %s", cudaGetErrorString(e));
+  for (int p = 0; p < kProfPhases; ++p) {
+    out16[p] = 0;
+    for (int cta = 0; cta < kProfCtas; ++cta) out16[p] += host[cta * kProfPhases + p];
+  }
   return FRACSSM_OK;
 }

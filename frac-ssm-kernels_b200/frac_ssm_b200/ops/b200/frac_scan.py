@@ -13,9 +13,24 @@ from ... import _cabi as C
 # "auto": the single-pass tcgen05 kernel when it covers the shape, else the staged kernels.
 _PATHS = {"auto": C.PATH_AUTO, "staged": C.PATH_STAGED, "fused": C.PATH_FUSED}
 
+_last_ws = None     # scratch of the last call made with keep_workspace=True (diagnostics)
+
+
+def last_phase_cycles():
+    """Cycles per phase of the single-pass kernel's tile loop in the last call made with
+    keep_workspace=True (16 numbers summed over CTAs; synchronises).  Diagnostic."""
+    import ctypes
+    if _last_ws is None:
+        raise RuntimeError("no call with keep_workspace=True yet")
+    out = (ctypes.c_longlong * 16)()
+    with torch.cuda.device(_last_ws.device):
+        C.check(C.lib().fracssm_scan_fused_phase_cycles(C.ptr(_last_ws), out, C.stream_of(_last_ws)),
+                "scan_fused_phase_cycles")
+    return list(out)
+
 
 def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False, *,
-              final_state_dtype=None, path="auto", check=False):
+              final_state_dtype=None, path="auto", check=False, keep_workspace=False):
     """Fractional chunked scan, forward.
 
     Args:
@@ -69,6 +84,9 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
         with torch.cuda.device(u.device):
             nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, p)
             ws = torch.empty(max(nbytes, 256), device=u.device, dtype=torch.uint8)
+            if keep_workspace:
+                global _last_ws
+                _last_ws = ws
             C.check(lib.fracssm_frac_scan_fwd(
                 C.ptr(u), C.dt(u), u.stride(0), u.stride(1), C.ptr(c), C.ptr(kappa), C.dt(c),
                 c.stride(0), c.stride(1), kappa.stride(0), kappa.stride(1), C.ptr(rho), rho.stride(0),

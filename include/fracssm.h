@@ -138,6 +138,13 @@ int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl
 int fracssm_scan_fused_status(const void *workspace, void *stream);
 
 /*
+ * Diagnostic: cycles spent per phase of the single-pass kernel's tile loop (16 phases, summed
+ * over CTAs, as seen by thread 0 of each CTA) during the last launch that used `workspace`.
+ * Synchronises the stream.  No counterpart in the reference.
+ */
+int fracssm_scan_fused_phase_cycles(const void *workspace, long long *out16, void *stream);
+
+/*
  * Elementwise scan-parameter prep after the two projections.
  * dyn [Bt, L, 3H] (dt, alpha, lambda logits), rw [Bt, L, 2*H*M] (read then write residuals),
  * x_conv [Bt, L, H*R]; mask [Bt, L] f32 or NULL; dt_bias [H], base_log_tau [M] f32;
