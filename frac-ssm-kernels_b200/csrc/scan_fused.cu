@@ -638,3 +638,72 @@ extern "C" int fracssm_scan_fused_phase_cycles(const void *workspace, long long 
   }
   return FRACSSM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Single-pass scan without any allocation by caller or library.
+//
+// Some callers cannot provide scratch memory: code that runs where the CUDA allocator must not
+// be touched (inside another framework's memory-pool callback, in a latency-critical serving
+// loop that forbids cudaMalloc after start-up, or in a host language binding that has no
+// device allocator of its own).  For them the scratch of the single-pass kernel (ticket, error
+// word, per-row progress counters and the running state) lives in a fixed array in the
+// library's device image.  The array exists once per GPU that loads the library and stays until
+// the process exits; it bounds the batch*heads count to kNoAllocMaxRows.
+namespace fracssm {
+namespace {
+constexpr int64_t kNoAllocMaxRows = 64;
+constexpr size_t kNoAllocBytes =
+    kCtrlBytes + kProfBytes + ((kNoAllocMaxRows * 4 + 255) / 256) * 256 + kNoAllocMaxRows * kR * kM * 4;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void *g_noalloc_ptr[kMaxDevices] = {};  // device address of g_noalloc_scratch on each device
+
+// Device address of the scratch array on the current device.  The array's name is only a
+// host-side handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+int noalloc_scratch(void **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan (no-alloc): %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan (no-alloc): device index too large");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(FRACSSM_ERR_CUDA, "frac_scan (no-alloc): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return FRACSSM_OK;
+}
+}  // namespace
+}  // namespace fracssm
+
+extern "C" int fracssm_frac_scan_fwd_noalloc(const void *u, const void *c, const void *kappa,
+                                             const float *rho, const float *initial_state, void *h,
+                                             void *final_state, int final_dtype, int64_t B, int64_t L,
+                                             int64_t R, int64_t M, void *stream) {
+  using namespace fracssm;
+  if (B < 0 || L < 0) return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): bad sizes");
+  if (B == 0 || L == 0) return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan (no-alloc): empty input");
+  if (B > kNoAllocMaxRows)
+    return fail(FRACSSM_ERR_UNSUPPORTED,
+                "frac_scan (no-alloc): batch*heads = %lld exceeds the built-in scratch (max %lld rows); "
+                "use fracssm_frac_scan_fwd with a caller-provided workspace",
+                (long long)B, (long long)kNoAllocMaxRows);
+  if (!fracssm_scan_fused_supported(B, L, R, M, 128, FRACSSM_BF16, FRACSSM_BF16))
+    return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan (no-alloc): needs R = 64, M = 128 and bfloat16 u, c, kappa");
+  if (!u || !c || !kappa || !rho || !h) return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): null pointer");
+  if (final_state && final_dtype != FRACSSM_F32 && final_dtype != FRACSSM_BF16)
+    return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): final_state dtype must be float32 or bfloat16");
+  void *scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  // scan_fused_launch clears the ticket, error word and progress counters on the stream before
+  // the kernel; the state rows are written before they are read.
+  return scan_fused_launch(u, c, kappa, FRACSSM_BF16, rho, initial_state, h, final_state, final_dtype,
+                           scratch, kNoAllocBytes, B, L, R, M, 128, stream);
+}

@@ -130,6 +130,25 @@ int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl
                           int64_t M, int64_t T, int path, void *stream);
 
 /*
+ * The composed forward scan for callers that can neither allocate device memory nor let the
+ * library do so (allocator callbacks of another framework, serving loops that forbid
+ * cudaMalloc after start-up, bindings without a device allocator).  Same math and kernel as
+ * fracssm_frac_scan_fwd with path = 2, but the kernel's scratch is a fixed array inside the
+ * library's device image (about 2.1 MB per GPU that loads the library, held until exit), so
+ * there is no workspace argument.  Limits: dense tensors, R = 64, M = 128, bf16 u/c/kappa,
+ * fp32 rho, and batch*heads B <= 64; larger B is rejected with FRACSSM_ERR_UNSUPPORTED.
+ * Calls no cudaMalloc / cudaFree.  The first call on a device looks up the array's device
+ * address (once, with that device current): make that first call outside any stream capture.
+ * All calls on a device share the array: the ticket and progress counters are cleared on the
+ * stream before each launch, and two calls whose kernels overlap on the GPU (different
+ * streams) race on it: serialise them.  No counterpart in the reference.
+ */
+int fracssm_frac_scan_fwd_noalloc(const void *u, const void *c, const void *kappa, const float *rho,
+                                  const float *initial_state, void *h, void *final_state,
+                                  int final_dtype, int64_t B, int64_t L, int64_t R, int64_t M,
+                                  void *stream);
+
+/*
  * Reads back the error word of the last single-pass launch that used `workspace` (this call
  * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
  * (for a predecessor tile's state, a TMA load or an MMA) ran out and the results are invalid.
