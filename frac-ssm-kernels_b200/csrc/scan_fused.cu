@@ -561,16 +561,24 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   (void)T; (void)ck_dtype;
   if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
     return fail(FRACSSM_ERR_ARG, "frac_scan: workspace too small");
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(scan_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  });
-  if (attr_err != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(attr_err));
+  // per device, once: opt in to the large dynamic shared memory and remember the SM count
+  static std::mutex mu;
+  static int sm_count[64] = {};
   int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (sms <= 0) return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot query the SM count");
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot identify the current device");
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (sm_count[dev] == 0) {
+      cudaError_t ae = cudaFuncSetAttribute(scan_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
+      int n = 0;
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+      if (n <= 0) return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot query the SM count");
+      sm_count[dev] = n;
+    }
+    sms = sm_count[dev];
+  }
 
   char *ws = reinterpret_cast<char *>(workspace);
   FusedArgs a{};
