@@ -77,7 +77,7 @@ __device__ __forceinline__ void tc_fence_after() {
 
 // ---- TMA -----------------------------------------------------------------------------------
 // 3D tile load global -> shared, completion counted in bytes on `bar`.  x is the innermost
-// coordinate and must be a multiple of 8 for bf16 (16-byte rule).  No cluster multicast.
+// coordinate and must be a multiple of 8 for bf16 (16-byte rule).  The copy targets this CTA only.
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int x,
                                             int y, int z) {
   asm volatile(

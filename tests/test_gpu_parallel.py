@@ -1,0 +1,69 @@
+"""Sequence sharding on real devices: emulated on one GPU, and over NCCL when two are present."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+from oracle import frac_oracle as O
+from tests.helpers import TOL_BF16, TOL_F32, close
+
+pytestmark = pytest.mark.gpu
+
+
+def test_segment_summaries_compose_on_one_gpu():
+    """The CUDA stage functions of the sequence-parallel path, run segment after segment on one
+    device: summaries -> incoming states -> per-segment scans must equal one scan of the whole."""
+    from frac_ssm_b200 import parallel
+    B, L, R, M, T, G = 3, 2048, 64, 128, 256, 4
+    u, c, kappa, rho, init = (t.cuda() for t in O.scan_inputs(B, L, R, M, gen="model_like", seed=41))
+    ops = parallel.CudaStageOps
+    toks = [parallel.shard_tokens(L, T, g, G) for g in range(G)]
+    summ = [ops.segment_summary(u[:, t], kappa[:, t], rho[:, t], T) for t in toks]
+    D = torch.stack([s[0] for s in summ])
+    F = torch.stack([s[1] for s in summ])
+    hs = []
+    for g, t in enumerate(toks):
+        s_in = parallel.incoming_state(D, F, g, init)
+        h, fin = ops.scan(u[:, t].contiguous(), c[:, t].contiguous(), kappa[:, t].contiguous(),
+                          rho[:, t].contiguous(), T, s_in)
+        hs.append(h)
+    h_ref, f_ref = O.frac_scan_slabs(u.cpu().float(), c.cpu().float(), kappa.cpu().float(), rho.cpu(), T,
+                                     init.cpu(), True, exact=True, slab=1)
+    close(torch.cat(hs, 1), h_ref, **TOL_BF16)
+    close(fin, f_ref, **TOL_F32)
+
+
+def _nccl_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from frac_ssm_b200 import parallel
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        B, L, R, M, T = 2, 2048, 64, 128, 256
+        u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, gen="model_like", seed=43)
+        tok = parallel.shard_tokens(L, T, rank, world)
+        dev = lambda x: x[:, tok].contiguous().cuda()
+        h, fin = parallel.seq_parallel_scan(dev(u), dev(c), dev(kappa), dev(rho), T, init.cuda(), True)
+        h_ref, f_ref = O.frac_scan_slabs(u.float(), c.float(), kappa.float(), rho, T, init, True,
+                                         exact=True, slab=1)
+        ok = torch.allclose(h.float().cpu(), h_ref[:, tok], rtol=2e-2, atol=2e-2) and \
+            torch.allclose(fin.cpu(), f_ref, rtol=1e-3, atol=1e-3)
+        out[rank] = int(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_sharding_over_nccl():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_nccl_worker, args=(world, port, out), nprocs=world, join=True)
+        assert dict(out) == {0: 1, 1: 1}

@@ -1,0 +1,107 @@
+"""Host logic of the multi-GPU paths on CPU ranks (gloo, world size 2 and 3).
+
+The stage functions are the CPU oracle here: what is under test is the partitioning, the
+exchange and the composition of segment summaries, not the kernels.
+"""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from frac_ssm_b200 import parallel
+from oracle import frac_oracle as O
+
+
+class OracleStageOps:
+    @staticmethod
+    def segment_summary(u, kappa, rho, T):
+        lcr, cd = O.chunk_cumsum(O.log_decay(rho, True), T, True)
+        st = O.chunk_state(u.float(), kappa.float(), lcr, T, exact=True)
+        _, fin = O.state_passing(st, cd, None, exact=True)
+        return cd.sum(1), fin.float()
+
+    @staticmethod
+    def scan(u, c, kappa, rho, T, init):
+        return O.frac_scan(u.float(), c.float(), kappa.float(), rho, T, init, True, exact=True)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, mode, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, L, R, M, T = 3, 200, 8, 16, 16
+        u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, dtype=torch.float32, gen="model_like", seed=7)
+        h_ref, f_ref = O.frac_scan(u, c, kappa, rho, T, init, True, exact=True)
+        if mode == "seq":
+            tok = parallel.shard_tokens(L, T, rank, world)
+            h, fin = parallel.seq_parallel_scan(u[:, tok], c[:, tok], kappa[:, tok], rho[:, tok], T, init,
+                                                True, ops=OracleStageOps)
+            ok = torch.allclose(h, h_ref[:, tok], rtol=1e-4, atol=1e-4) and \
+                torch.allclose(fin, f_ref, rtol=1e-4, atol=1e-4)
+        elif mode == "rows":
+            rows = parallel.shard_rows(B, rank, world)
+            h, fin = OracleStageOps.scan(u[rows], c[rows], kappa[rows], rho[rows], T, init[rows])
+            ok = torch.allclose(h, h_ref[rows], rtol=1e-5, atol=1e-5) and \
+                torch.allclose(fin, f_ref[rows], rtol=1e-5, atol=1e-5)
+        else:  # a segment that is not chunk-aligned must be refused on the offending rank
+            try:
+                parallel.seq_parallel_scan(u[:, :17], c[:, :17], kappa[:, :17], rho[:, :17], T, None,
+                                           False, ops=OracleStageOps)
+                ok = rank == world - 1
+            except ValueError:
+                ok = rank < world - 1
+        flag = torch.tensor([1 if ok else 0])
+        if mode != "misaligned":
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        out[rank] = int(flag.item())
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, mode):
+    port = _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, port, mode, out), nprocs=world, join=True)
+        assert dict(out) == {r: 1 for r in range(world)}
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_sharding_matches_single_scan(world):
+    _run(world, "seq")
+
+
+def test_row_sharding_matches_single_scan():
+    _run(2, "rows")
+
+
+def test_shard_helpers():
+    assert [parallel.shard_rows(10, r, 3) for r in range(3)] == [slice(0, 4), slice(4, 7), slice(7, 10)]
+    assert parallel.shard_rows(2, 3, 4) == slice(2, 2)
+    toks = [parallel.shard_tokens(1000, 256, r, 2) for r in range(2)]
+    assert toks == [slice(0, 512), slice(512, 1000)]
+    with pytest.raises(ValueError):
+        parallel.shard_rows(4, 4, 4)
+
+
+def test_incoming_state_composition():
+    g = torch.Generator().manual_seed(0)
+    D = -torch.rand(3, 2, 4, generator=g)
+    F = torch.randn(3, 2, 5, 4, generator=g)
+    s0 = torch.randn(2, 5, 4, generator=g)
+    s = s0.clone()
+    for r in range(3):
+        torch.testing.assert_close(parallel.incoming_state(D, F, r, s0), s)
+        s = torch.exp(D[r])[:, None, :] * s + F[r]
+    with pytest.raises(ValueError):
+        parallel.incoming_state(D[:2], F, 1)
