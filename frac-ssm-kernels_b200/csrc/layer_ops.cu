@@ -168,6 +168,60 @@ scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t
   }
 }
 
+// bf16 fast path of the epilogue: one block per (b, l) row, 8 elements (16 bytes) per thread held
+// in registers, so every tensor is read once and written once.
+__device__ __forceinline__ void unpack8(const uint4 &p, float (&f)[8]) {
+  const uint32_t wds[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(wds[i] << 16);
+    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int64_t h_sl,
+                          const __nv_bfloat16 *__restrict__ x, int64_t x_sb, int64_t x_sl,
+                          const __nv_bfloat16 *__restrict__ gate, int64_t g_sb, int64_t g_sl,
+                          const float *__restrict__ Dp, const void *__restrict__ w, int w_dt,
+                          float gate_bias, float eps, __nv_bfloat16 *__restrict__ y, int64_t L, int64_t H,
+                          int64_t R) {
+  __shared__ float red[32];
+  const int64_t HR = H * R;
+  const int64_t row = blockIdx.x, b = row / L, l = row % L;
+  const int64_t j = (int64_t)threadIdx.x * 8;
+  float v[8];
+  float ss = 0.f;
+  const bool live = j < HR;
+  if (live) {
+    const int64_t hh = j / R, r = j % R;
+    float hv[8], xv[8], zv[8];
+    unpack8(__ldcs(reinterpret_cast<const uint4 *>(h + (b * H + hh) * h_sb + l * h_sl + r)), hv);
+    unpack8(__ldcs(reinterpret_cast<const uint4 *>(x + b * x_sb + l * x_sl + j)), xv);
+    unpack8(__ldcs(reinterpret_cast<const uint4 *>(gate + b * g_sb + l * g_sl + j)), zv);
+    const float4 d0 = *reinterpret_cast<const float4 *>(Dp + j), d1 = *reinterpret_cast<const float4 *>(Dp + j + 4);
+    const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float z = zv[i] + gate_bias;
+      v[i] = (hv[i] + xv[i] * dv[i]) * (z * sigmoidf_(z));
+      ss = fmaf(v[i], v[i], ss);
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)HR + eps);
+  if (live) {
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i] * rs * ld_f32(w, j + 2 * i, w_dt),
+                                                     v[2 * i + 1] * rs * ld_f32(w, j + 2 * i + 1, w_dt));
+      o[i] = *reinterpret_cast<const uint32_t *>(&t);
+    }
+    __stcs(reinterpret_cast<uint4 *>(y + row * HR + j), make_uint4(o[0], o[1], o[2], o[3]));
+  }
+}
+
 }  // namespace fracssm
 
 extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64_t dyn_sl,
@@ -246,6 +300,18 @@ extern "C" int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, i
     return fail(FRACSSM_ERR_ARG, "scan_epilogue: unsupported dtype");
   if (Bt == 0 || L == 0) return FRACSSM_OK;
   if (!h || !x_conv || !gate || !D || !weight || !y) return fail(FRACSSM_ERR_ARG, "scan_epilogue: null pointer");
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int64_t HR = H * R;
+  if (h_dtype == FRACSSM_BF16 && xg_dtype == FRACSSM_BF16 && R % 8 == 0 && HR <= 8192 && al16(h) && al16(x_conv) &&
+      al16(gate) && al16(y) && al16(D) && h_sb % 8 == 0 && h_sl % 8 == 0 && x_sb % 8 == 0 && x_sl % 8 == 0 &&
+      g_sb % 8 == 0 && g_sl % 8 == 0) {
+    const unsigned threads = (unsigned)(((HR / 8) + 31) / 32 * 32);
+    scan_epilogue_bf16_kernel<<<(unsigned)(Bt * L), threads, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16 *>(h), h_sb, h_sl, reinterpret_cast<const __nv_bfloat16 *>(x_conv),
+        x_sb, x_sl, reinterpret_cast<const __nv_bfloat16 *>(gate), g_sb, g_sl, D, weight, w_dtype, gate_bias,
+        eps, reinterpret_cast<__nv_bfloat16 *>(y), L, H, R);
+    return check_launch("scan_epilogue");
+  }
   scan_epilogue_kernel<<<(unsigned)(Bt * L), 256, 0, (cudaStream_t)stream>>>(
       h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb, g_sl, xg_dtype, D, weight, w_dtype,
       gate_bias, eps, y, L, H, R);

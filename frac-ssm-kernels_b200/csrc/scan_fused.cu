@@ -6,8 +6,15 @@
 // Work item = (bh, tile of 128 tokens), handed out by an atomic ticket in tile-major order
 // (all bh of tile 0, then tile 1, ...).  The item (bh, j) needs the state left by (bh, j-1);
 // it waits on a per-bh counter in global memory with a time limit.  A ticket is only taken
-// by a running CTA and dependencies point to lower tickets, so the lowest unfinished item can
-// always proceed.
+// by a running CTA (one item ahead of the one it is working on) and dependencies point to
+// lower tickets, so the lowest unfinished item is always being worked on and never waits.
+//
+// One CTA per SM, 20 warps (three of them only pad the control warp's register group).  Warps 0-15 ("workers") turn the raw inputs into bf16 operand tiles
+// in shared memory and run the epilogues; warp 16 ("control") takes tickets, issues the TMA
+// load of u and every tcgen05.mma, and polls the state counter.  Workers hand a batch of tiles
+// over by arriving on a "full" mbarrier (one arrival per warp, after a proxy fence); the
+// control warp hands buffers and accumulators back through tcgen05.commit mbarriers.  The next
+// ticket is taken a whole tile ahead, so its inputs can be pulled into L2 exactly.
 //
 // Math per tile (tokens t, k in 0..127; modes m; rho floored at 1e-6, 1 beyond L):
 //   h[t]   = sum_m Chat[t,m] S[m,:]  +  sum_{k<=t} W[t,k] u[k,:]
@@ -34,7 +41,12 @@
 namespace fracssm {
 namespace {
 
-constexpr int kTile = 128, kR = 64, kM = 128, kThreads = 512;
+constexpr int kTile = 128, kR = 64, kM = 128, kWorkers = 512, kThreads = 640;
+// Registers are re-divided after launch (setmaxnreg): the 16 worker warps grow to kWorkerRegs,
+// the control warp's group of four shrinks to kControlRegs.  The launch allocation per thread
+// (checked on the host) must cover both, or the growing warps would wait forever.
+constexpr int kWorkerRegs = 112, kControlRegs = 32;
+constexpr int kLaunchRegsNeeded = (kWorkers * kWorkerRegs + (kThreads - kWorkers) * kControlRegs + kThreads - 1) / kThreads;
 constexpr uint32_t kTileBytes = 32768;  // [128 x 128] bf16 operand tile
 constexpr uint32_t kAtom = 16384;       // one 64-column block of such a tile
 // shared memory map (bytes from the 1024-aligned base)
@@ -44,7 +56,7 @@ constexpr uint32_t kOffS = 163840, kOffSlo = 180224;     // incoming state, bf16
 constexpr uint32_t kOffU = 196608;
 constexpr uint32_t kOffSeg = 212992;    // float [16][128]: decay product of each 8-token segment
 constexpr uint32_t kOffGt = 221184;     // float [128]: decay product of the whole tile
-constexpr uint32_t kOffMisc = 221696;   // mbarriers, TMEM base, ticket
+constexpr uint32_t kOffMisc = 221696;   // mbarriers, TMEM base, tickets
 constexpr uint32_t kSmemBytes = kOffMisc + 128 + 128 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
 constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
@@ -60,7 +72,7 @@ struct FusedArgs {
   void *fin;
   int fin_dt;
   int *ctrl;     // [0] ticket counter, [1] error word
-  long long *prof;  // [kProfCtas][16] cycles spent per phase by thread 0 of each CTA
+  long long *prof;  // [kProfCtas][16] cycles spent per phase by worker thread 0 of each CTA
   int *flags;    // [BH] tiles finished per bh
   float *state;  // [BH][128 m][64 r] running state
   int BH, L, ntiles, total;
@@ -99,6 +111,39 @@ __device__ __forceinline__ void st_release(int *p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+
+// Raw inputs of one item for one worker thread: 8 tokens x 4 modes.
+struct RawRegs {
+  float4 r[8];
+  uint2 c[8], k[8];
+};
+
+__device__ __forceinline__ void load_raw(RawRegs &raw, const FusedArgs &a, int item, int w, int lane) {
+  const int j = item / a.BH, bh = item - j * a.BH;
+  const int t0 = j * kTile + 8 * w;
+  const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    raw.r[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+    raw.c[i] = make_uint2(0u, 0u);
+    raw.k[i] = make_uint2(0u, 0u);
+    if (t0 + i < a.L) {
+      raw.r[i] = __ldcs(reinterpret_cast<const float4 *>(a.rho + (tok0 + i) * kM) + lane);
+      raw.c[i] = __ldcs(reinterpret_cast<const uint2 *>(a.c + (tok0 + i) * kM) + lane);
+      raw.k[i] = __ldcs(reinterpret_cast<const uint2 *>(a.kappa + (tok0 + i) * kM) + lane);
+    }
+  }
+}
+
+// One arrival per warp on a "full" barrier: every lane's shared-memory writes are fenced for
+// the async proxy and its TMEM reads are ordered before the control warp's next MMAs.
+__device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
+  umma::fence_async_smem();
+  umma::tc_fence_before();
+  __syncwarp();
+  if (lane == 0) umma::mbar_arrive(bar);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -108,47 +153,173 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   uint8_t *chat_lo = smem + kOffChatLo;
   float *seg = reinterpret_cast<float *>(smem + kOffSeg);
   float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
+  // mbarriers: bar0 / bar1 / barH are completed by tcgen05.commit, barU by the TMA load,
+  // full[0..5] by the 16 worker warps, item_bar and state_bar by the control warp.
   uint64_t *bar0 = reinterpret_cast<uint64_t *>(smem + kOffMisc);
-  uint64_t *bar1 = bar0 + 1, *barH = bar0 + 2, *barU = bar0 + 3;
-  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bar0 + 4);
-  int *item_s = reinterpret_cast<int *>(tmem_s + 1);
+  uint64_t *bar1 = bar0 + 1, *barH = bar0 + 2, *barU = bar0 + 3, *full = bar0 + 4;
+  uint64_t *item_bar = bar0 + 10, *state_bar = bar0 + 11, *out_bar = bar0 + 12;
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bar0 + 13);
+  volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
+  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 128);  // worker thread 0 only
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
 
   if (tid == 0) {
     umma::mbar_init(bar0, 1);
     umma::mbar_init(bar1, 1);
     umma::mbar_init(barH, 1);
     umma::mbar_init(barU, 1);
+    for (int i = 0; i < 6; ++i) umma::mbar_init(full + i, 16);
+    umma::mbar_init(item_bar, 1);
+    umma::mbar_init(state_bar, 1);
+    umma::mbar_init(out_bar, 16);
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
+    for (int i = 0; i < kProfPhases; ++i) prof[i] = 0;
   }
   if (w == 0) umma::tmem_alloc(tmem_s, 512);
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
   const uint32_t tmem = *tmem_s;
-  const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
+  bool ok = true;  // cleared when a bounded wait runs out; later waits are then skipped
+#define FRACSSM_WAIT(bar, parity) \
+  if (ok) ok = umma::mbar_wait_parked(bar, (parity) & 1u, kWaitNs)
 
-  const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
-  const uint32_t sS = umma::smem_u32(s_tile), sSlo = umma::smem_u32(slo_tile), sU = umma::smem_u32(u_tile);
-  const uint32_t sClo = umma::smem_u32(chat_lo);
-  constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
-  constexpr uint32_t kIdKK64 = umma::make_idesc(128, 64, false, false);
-  constexpr uint32_t kIdKK32 = umma::make_idesc(128, 32, false, false);
-  constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
-  constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
-  // start offset of contraction step ks inside a K-major 128-column tile
-  auto koff = [](int ks) -> uint32_t { return (ks >> 2) * kAtom + (ks & 3) * 32; };
+  // (each setmaxnreg sits inside its role's branch: the register limit must not merge across roles)
+  if (w > 16) {
+    // spare warps of the control warp's register group: give the registers back, nothing else
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+  } else if (w == 16) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+    // =========================== control warp ===========================
+    const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
+    const uint32_t sS = umma::smem_u32(s_tile), sSlo = umma::smem_u32(slo_tile), sU = umma::smem_u32(u_tile);
+    const uint32_t sClo = umma::smem_u32(chat_lo);
+    constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
+    constexpr uint32_t kIdKK64 = umma::make_idesc(128, 64, false, false);
+    constexpr uint32_t kIdKK32 = umma::make_idesc(128, 32, false, false);
+    constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
+    constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
+    // One GEMM piece = 8 contraction steps of 16.  A K-major 128-column tile advances by 32 bytes
+    // inside a 64-column atom and by one atom after 4 steps; an MN-major tile by 16 rows (2048 B).
+    // The loop is kept rolled so the control warp needs few registers.
+    auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t b_sbo,
+                     uint32_t idesc, uint32_t acc_first) {
+      const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
+      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, b_sbo);
+#pragma unroll 1
+      for (uint32_t s = 0; s < 8; ++s) {
+        const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
+        umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
+                     s > 0 ? 1u : acc_first);
+      }
+    };
 
-  uint32_t ph0 = 0, ph1 = 0, phH = 0, phU = 0;  // completed phases of each mbarrier
-  bool ok = true;
-  // thread 0 charges the cycles since the last mark to a phase (diagnostic, a few clock reads per tile)
-  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 128);  // thread 0 only
-  if (tid == 0)
-    for (int i = 0; i < kProfPhases; ++i) prof[i] = 0;
-  long long t_mark = clock64();
+    int item = 0;
+    if (lane == 0) {
+      item = atomicAdd(&a.ctrl[0], 1);
+      items[0] = item;
+      umma::mbar_arrive(item_bar);
+    }
+    item = __shfl_sync(0xffffffffu, item, 0);
+#pragma unroll 1
+    for (uint32_t n = 0; item < a.total; ++n) {
+      const int j = item / a.BH, bh = item - j * a.BH;
+      int next = 0;
+      if (lane == 0) {  // take the next ticket now: the workers prefetch it during this tile
+        next = atomicAdd(&a.ctrl[0], 1);
+        items[(n + 1) & 1] = next;
+        umma::mbar_arrive(item_bar);
+      }
+      next = __shfl_sync(0xffffffffu, next, 0);
+      if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
+        const int nj = next / a.BH, nb = next - nj * a.BH;
+        const int ntok = min(kTile, a.L - nj * kTile);
+        const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
+        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
+        umma::prefetch_l2(a.c + tok * kM, ntok * kM * 2);
+        umma::prefetch_l2(a.kappa + tok * kM, ntok * kM * 2);
+      }
+      if (n > 0) { FRACSSM_WAIT(barH, n - 1); }  // every MMA of the previous tile has finished
+      if (lane == 0) {
+        umma::mbar_expect_tx(barU, kTile * kR * 2);
+        umma::tma_load_3d(u_tile, &u_map, barU, 0, j * kTile, bh);
+      }
+      // base: D[t,k] = A0[t,:] . B0[k,:]
+      FRACSSM_WAIT(full + 0, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColBase, sA0, false, sA0 + kTileBytes, false, 1024, kIdKK128, 0u);
+        umma::mma_commit(bar0);
+      }
+      // levels 8 and 16 (area1): first halves are picked by the B descriptor's row-group stride
+      FRACSSM_WAIT(full + 1, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColL8, sA1, false, sA1, false, 2048, kIdKK64, 0u);                      // every other 8-row group
+        piece(kColL16, sA1 + kTileBytes, false, sA1 + kTileBytes, false, 4096, kIdKK32, 0u);   // groups 0,4,8,12
+        piece(kColL16 + 32, sA1 + kTileBytes, false, sA1 + kTileBytes + 1024, false, 4096, kIdKK32, 0u);  // 1,5,9,13
+        umma::mma_commit(bar1);
+      }
+      // levels 32 and 64 (area0)
+      FRACSSM_WAIT(full + 2, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColL32, sA0, false, sA0, false, 1024, kIdKK32, 0u);                     // rows 0..31
+        piece(kColL32 + 32, sA0, false, sA0 + 8192, false, 1024, kIdKK32, 0u);         // rows 64..95
+        piece(kColL64, sA0 + kTileBytes, false, sA0 + kTileBytes, false, 1024, kIdKK64, 0u);  // rows 0..63
+        umma::mma_commit(bar0);
+      }
+      // Sacc[m,r] = sum_k Khi[k,m] u[k,r]
+      FRACSSM_WAIT(full + 3, n);
+      FRACSSM_WAIT(barU, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
+        umma::mma_commit(bar1);
+      }
+      // Sacc += Klo^T u;  H = W u
+      FRACSSM_WAIT(full + 4, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColS, sA0, true, sU, true, 1024, kIdMnMn64, 1u);
+        umma::mma_commit(bar0);
+        piece(kColH, sA0 + kTileBytes, false, sU, true, 1024, kIdKMn64, 0u);
+        // the state left by the previous tile of this (batch, head) row
+        if (j > 0 && ok) {
+          const uint64_t t_start = umma::global_ns();
+          while (ld_acquire(a.flags + bh) < j) {
+            __nanosleep(100);
+            if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+          }
+        }
+        umma::mbar_arrive(state_bar);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      // H += Chat S, both factors split into bf16 high and low parts (low x low dropped)
+      FRACSSM_WAIT(full + 5, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColH, sA1, false, sS, true, 1024, kIdKMn64, 1u);
+        piece(kColH, sClo, false, sS, true, 1024, kIdKMn64, 1u);
+        piece(kColH, sA1, false, sSlo, true, 1024, kIdKMn64, 1u);
+        umma::mma_commit(barH);
+      }
+      // publish the outgoing state: the workers' stores are ordered before their arrivals on
+      // out_bar, this release makes them visible to the CTA that takes the next tile of the row
+      FRACSSM_WAIT(out_bar, n);
+      if (lane == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
+      __syncwarp();
+      item = next;
+    }
+  } else {
+    // =========================== worker warps ===========================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
+    const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
+    // worker thread 0 charges the cycles since the last mark to a phase (diagnostic)
+    long long t_mark = clock64();
 #define FRACSSM_MARK(phase)                         \
   if (tid == 0) {                                   \
     const long long now_ = clock64();               \
@@ -156,390 +327,283 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     t_mark = now_;                                  \
   }
 
-  while (true) {
-    if (tid == 0) *item_s = atomicAdd(&a.ctrl[0], 1);
-    umma::tc_fence_before();
-    __syncthreads();
-    umma::tc_fence_after();
-    const int item = *item_s;
-    if (item >= a.total) break;
-    FRACSSM_MARK(0)
-    const int j = item / a.BH, bh = item - j * a.BH;
-    const int t0 = j * kTile;
+    FRACSSM_WAIT(item_bar, 0);
+    int item = items[0];
 
-    if (tid == 0) {
-      umma::mbar_expect_tx(barU, kTile * kR * 2);
-      umma::tma_load_3d(u_tile, &u_map, barU, 0, t0, bh);
-    }
-    if (tid == 32) {  // pull the likely next tile of this CTA into L2
-      const int nxt = item + gridDim.x;
-      if (nxt < a.total) {
-        const int nj = nxt / a.BH, nb = nxt - nj * a.BH;
-        const int ntok = min(kTile, a.L - nj * kTile);
-        const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
-        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
-        umma::prefetch_l2(a.c + tok * kM, ntok * kM * 2);
-        umma::prefetch_l2(a.kappa + tok * kM, ntok * kM * 2);
-      }
-    }
+    for (uint32_t n = 0; item < a.total; ++n) {
+      const int j = item / a.BH, bh = item - j * a.BH;
+      const int t0 = j * kTile;
+      RawRegs raw;
+      load_raw(raw, a, item, w, lane);
 
-    // ---- P1: load this warp's 8 tokens x this lane's 4 modes; segment products; base tiles
-    float cp[8][4], ks[8][4], g8[4];
-    {
-      float rr[8][4];
-      uint2 cc[8], kk[8];
-      const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0 + 8 * w;
+      // ---- segment products and the base tiles, from the raw registers; one group of 4 tokens
+      // at a time to keep few values live
+      float cp[8][4], ks[8][4], g8[4];
+      {
+        float ga[4], gb[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool live = t0 + 8 * w + i < a.L;
-        float4 r4 = make_float4(1.f, 1.f, 1.f, 1.f);
-        cc[i] = make_uint2(0u, 0u);
-        kk[i] = make_uint2(0u, 0u);
-        if (live) {
-          r4 = __ldcs(reinterpret_cast<const float4 *>(a.rho + (tok0 + i) * kM) + lane);
-          cc[i] = __ldcs(reinterpret_cast<const uint2 *>(a.c + (tok0 + i) * kM) + lane);
-          kk[i] = __ldcs(reinterpret_cast<const uint2 *>(a.kappa + (tok0 + i) * kM) + lane);
-        }
-        rr[i][0] = fmaxf(r4.x, kRhoFloor); rr[i][1] = fmaxf(r4.y, kRhoFloor);
-        rr[i][2] = fmaxf(r4.z, kRhoFloor); rr[i][3] = fmaxf(r4.w, kRhoFloor);
-      }
+        for (int grp = 0; grp < 2; ++grp) {
+          float a0[4][4], b0[4][4];
 #pragma unroll
-      for (int pair = 0; pair < 2; ++pair) {
-        float a0[8][2], b0[8][2];
+          for (int q = 0; q < 4; ++q) {
+            float rr[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int q = 2 * pair + e;
-          // p4: running product from the start of each group of 4 tokens (inclusive)
-          // s4: product of the tokens after t up to the end of its group of 4 (exclusive)
-          float p4[8], s4[8];
-          p4[0] = rr[0][q]; p4[1] = p4[0] * rr[1][q]; p4[2] = p4[1] * rr[2][q]; p4[3] = p4[2] * rr[3][q];
-          p4[4] = rr[4][q]; p4[5] = p4[4] * rr[5][q]; p4[6] = p4[5] * rr[6][q]; p4[7] = p4[6] * rr[7][q];
-          s4[3] = 1.f; s4[2] = rr[3][q]; s4[1] = s4[2] * rr[2][q]; s4[0] = s4[1] * rr[1][q];
-          s4[7] = 1.f; s4[6] = rr[7][q]; s4[5] = s4[6] * rr[6][q]; s4[4] = s4[5] * rr[5][q];
-          const float ga = p4[3], gb = p4[7];
-          g8[q] = ga * gb;
+            for (int i = 0; i < 4; ++i) {
+              const float4 v = raw.r[4 * grp + i];
+              rr[i] = fmaxf(q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w, kRhoFloor);
+            }
+            // p4: running product from the start of the group (inclusive)
+            // s4: product of the tokens after t up to the end of the group (exclusive)
+            float p4[4], s4[4];
+            p4[0] = rr[0]; p4[1] = p4[0] * rr[1]; p4[2] = p4[1] * rr[2]; p4[3] = p4[2] * rr[3];
+            s4[3] = 1.f; s4[2] = rr[3]; s4[1] = s4[2] * rr[2]; s4[0] = s4[1] * rr[1];
+            if (grp == 0) ga[q] = p4[3]; else gb[q] = p4[3];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t cw = pair ? cc[i].y : cc[i].x, kw = pair ? kk[i].y : kk[i].x;
-            const float cf = __uint_as_float(e ? (cw & 0xFFFF0000u) : (cw << 16));
-            const float kf = __uint_as_float(e ? (kw & 0xFFFF0000u) : (kw << 16));
-            if (i < 4) {  // base reference point: between token 3 and token 4 of the segment
-              a0[i][e] = __fdividef(cf, s4[i]);
-              b0[i][e] = kf * s4[i];
-              cp[i][q] = cf * p4[i];
-              ks[i][q] = kf * s4[i] * gb;
-            } else {
-              a0[i][e] = cf * p4[i];
-              b0[i][e] = __fdividef(kf, p4[i]);
-              cp[i][q] = cf * ga * p4[i];
-              ks[i][q] = kf * s4[i];
+            for (int i = 0; i < 4; ++i) {
+              const uint2 cu = raw.c[4 * grp + i], ku = raw.k[4 * grp + i];
+              const uint32_t cw = (q < 2) ? cu.x : cu.y, kw = (q < 2) ? ku.x : ku.y;
+              const float cf = __uint_as_float((q & 1) ? (cw & 0xFFFF0000u) : (cw << 16));
+              const float kf = __uint_as_float((q & 1) ? (kw & 0xFFFF0000u) : (kw << 16));
+              if (grp == 0) {  // base reference point: between token 3 and token 4 of the segment
+                a0[i][q] = __fdividef(cf, s4[i]);
+                b0[i][q] = kf * s4[i];
+                cp[i][q] = cf * p4[i];
+                ks[i][q] = kf * s4[i];          // times gb, below
+              } else {
+                a0[i][q] = cf * p4[i];
+                b0[i][q] = __fdividef(kf, p4[i]);
+                cp[4 + i][q] = cf * ga[q] * p4[i];
+                ks[4 + i][q] = kf * s4[i];
+              }
             }
           }
-        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int row = 8 * w + i;
-          const uint32_t off = (lane >> 4) * kAtom + row * 128 +
-                               (((((lane & 15) >> 1) ^ (row & 7)) << 4) | ((lane & 1) << 3) | (pair << 2));
-          *reinterpret_cast<uint32_t *>(area0 + off) = pack2(a0[i][0], a0[i][1]);
-          *reinterpret_cast<uint32_t *>(area0 + kTileBytes + off) = pack2(b0[i][0], b0[i][1]);
-        }
-      }
-      *reinterpret_cast<float4 *>(seg + w * kM + 4 * lane) = make_float4(g8[0], g8[1], g8[2], g8[3]);
-    }
-    umma::fence_async_smem();
-    __syncthreads();
-    FRACSSM_MARK(1)
-    if (tid == 0) {  // base: D[t,k] = A0[t,:] . B0[k,:]
-      umma::tc_fence_after();
-#pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma::mma_ss(tmem + kColBase, umma::make_sdesc(sA0 + koff(s), 16, 1024),
-                     umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024), kIdKK128, s > 0);
-      umma::mma_commit(bar0);
-    }
-
-    // One sibling level: every token row holds its A-role or B-role value.
-    auto produce_level = [&](uint8_t *tile, int hseg) {
-      float sig[4];
-      const bool role_a = (w & hseg) != 0;
-      const int first = w - (w & (hseg - 1));
-      if (role_a) seg_prod(seg, first, w, lane, sig);
-      else seg_prod(seg, w + 1, first + hseg, lane, sig);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float v[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = (role_a ? cp[i][q] : ks[i][q]) * sig[q];
-        emit4(tile, 8 * w + i, lane, v);
-      }
-    };
-
-    // ---- levels 8 and 16 -> area1
-    produce_level(area1, 1);
-    produce_level(area1 + kTileBytes, 2);
-    umma::fence_async_smem();
-    __syncthreads();
-    FRACSSM_MARK(2)
-    if (tid == 0) {
-      umma::tc_fence_after();
-#pragma unroll
-      for (int s = 0; s < 8; ++s)  // level 8: first halves are every other 8-row group
-        umma::mma_ss(tmem + kColL8, umma::make_sdesc(sA1 + koff(s), 16, 1024),
-                     umma::make_sdesc(sA1 + koff(s), 16, 2048), kIdKK64, s > 0);
-#pragma unroll
-      for (int half = 0; half < 2; ++half)  // level 16: groups {0,4,8,12} then {1,5,9,13}
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma::mma_ss(tmem + kColL16 + 32 * half, umma::make_sdesc(sA1 + kTileBytes + koff(s), 16, 1024),
-                       umma::make_sdesc(sA1 + kTileBytes + half * 1024 + koff(s), 16, 4096), kIdKK32, s > 0);
-      umma::mma_commit(bar1);
-    }
-
-    // ---- levels 32 and 64 -> area0 (after the base MMAs have read it)
-    FRACSSM_MARK(3)
-    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
-    FRACSSM_MARK(4)
-    produce_level(area0, 4);
-    produce_level(area0 + kTileBytes, 8);
-    umma::fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      umma::tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half)  // level 32: rows 0..31 then rows 64..95
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma::mma_ss(tmem + kColL32 + 32 * half, umma::make_sdesc(sA0 + koff(s), 16, 1024),
-                       umma::make_sdesc(sA0 + half * 8192 + koff(s), 16, 1024), kIdKK32, s > 0);
-#pragma unroll
-      for (int s = 0; s < 8; ++s)  // level 64: rows 0..63
-        umma::mma_ss(tmem + kColL64, umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024),
-                     umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024), kIdKK64, s > 0);
-      umma::mma_commit(bar0);
-    }
-
-    // ---- Chat and Khat(high) -> area1 (after levels 8/16 have read it)
-    FRACSSM_MARK(5)
-    ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;
-    FRACSSM_MARK(6)
-    {
-      float e[4], f[4];
-      seg_prod(seg, 0, w, lane, e);
-      seg_prod(seg, w + 1, 16, lane, f);
-      if (w == 0)
-        *reinterpret_cast<float4 *>(gt_s + 4 * lane) =
-            make_float4(g8[0] * f[0], g8[1] * f[1], g8[2] * f[2], g8[3] * f[3]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float v[4], vl[4], kh[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float chat = cp[i][q] * e[q];
-          v[q] = __bfloat162float(__float2bfloat16_rn(chat));
-          vl[q] = chat - v[q];
-          const float full = ks[i][q] * f[q];
-          kh[q] = __bfloat162float(__float2bfloat16_rn(full));
-          ks[i][q] = full - kh[q];  // low part, emitted with the next batch
-        }
-        emit4(area1, 8 * w + i, lane, v);
-        emit4(chat_lo, 8 * w + i, lane, vl);
-        emit4(area1 + kTileBytes, 8 * w + i, lane, kh);
-      }
-    }
-    umma::fence_async_smem();
-    __syncthreads();
-    FRACSSM_MARK(7)
-    if (tid == 0) {
-      ok = umma::mbar_wait(barU, phU & 1, kWaitNs) && ok;
-      umma::tc_fence_after();
-#pragma unroll
-      for (int s = 0; s < 8; ++s)  // Sacc[m,r] = sum_k Khi[k,m] u[k,r]
-        umma::mma_ss(tmem + kColS, umma::make_sdesc(sA1 + kTileBytes + s * 2048, kAtom, 1024),
-                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdMnMn64, s > 0);
-      umma::mma_commit(bar1);
-    }
-    ++phU;
-
-    // ---- Khat(low) and W -> area0 (after every level MMA has completed)
-    FRACSSM_MARK(8)
-    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;
-    FRACSSM_MARK(9)
-    umma::tc_fence_after();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) emit4(area0, 8 * w + i, lane, ks[i]);
-    {
-      uint8_t *wt = area0 + kTileBytes;
-      const int t = 32 * Q + lane;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float v[8];
-        if (P > Q) {
-#pragma unroll
-          for (int x = 0; x < 8; ++x) v[x] = 0.f;
-        } else if (P < Q) {
-          const uint32_t col = ((Q >> 1) != (P >> 1)) ? (kColL64 + 32 * P + 8 * g)
-                                                      : (kColL32 + (P >> 1) * 32 + 8 * g);
-          umma::tmem_ld8(lane_addr + col, v);
-          umma::tmem_ld_wait();
-        } else {
-          float b[8], l8[8], l16[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) l8[x] = l16[x] = 0.f;
-          umma::tmem_ld8(lane_addr + kColBase + 32 * Q + 8 * g, b);
-          if ((g & 1) == 0) umma::tmem_ld8(lane_addr + kColL8 + (2 * Q + (g >> 1)) * 8, l8);
-          if (g < 2) umma::tmem_ld8(lane_addr + kColL16 + (g & 1) * 32 + Q * 8, l16);
-          umma::tmem_ld_wait();
-          const int tb = lane >> 3;  // 8-token block of this row inside its 32-token block
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            float r = 0.f;
-            if (g == tb) r = (x <= (lane & 7)) ? b[x] : 0.f;
-            else if (g < tb) r = ((tb ^ g) >= 2) ? l16[x] : l8[x];
-            v[x] = r;
+          for (int i = 0; i < 4; ++i) {
+            emit4(area0, 8 * w + 4 * grp + i, lane, a0[i]);
+            emit4(area0 + kTileBytes, 8 * w + 4 * grp + i, lane, b0[i]);
           }
         }
-        uint4 pk;
-        pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
-        const uint32_t chunk = (4 * P + g) & 7;
-        *reinterpret_cast<uint4 *>(wt + (P >> 1) * kAtom + t * 128 + ((chunk ^ (t & 7)) << 4)) = pk;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          g8[q] = ga[q] * gb[q];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ks[i][q] *= gb[q];
+        }
+        *reinterpret_cast<float4 *>(seg + w * kM + 4 * lane) = make_float4(g8[0], g8[1], g8[2], g8[3]);
       }
-    }
-    umma::fence_async_smem();
-    umma::tc_fence_before();
-    __syncthreads();
-    FRACSSM_MARK(10)
-    if (tid == 0) {
+      warp_arrive(full + 0, lane);
+      umma::named_barrier(1, kWorkers);  // segment products visible to every worker
+      FRACSSM_MARK(0)
+
+      // One sibling level: every token row holds its A-role or B-role value.
+      auto produce_level = [&](uint8_t *tile, int hseg) {
+        float sig[4];
+        const bool role_a = (w & hseg) != 0;
+        const int first = w - (w & (hseg - 1));
+        if (role_a) seg_prod(seg, first, w, lane, sig);
+        else seg_prod(seg, w + 1, first + hseg, lane, sig);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) v[q] = (role_a ? cp[i][q] : ks[i][q]) * sig[q];
+          emit4(tile, 8 * w + i, lane, v);
+        }
+      };
+
+      // ---- levels 8 and 16 -> area1
+      produce_level(area1, 1);
+      produce_level(area1 + kTileBytes, 2);
+      warp_arrive(full + 1, lane);
+      FRACSSM_MARK(1)
+
+      // ---- levels 32 and 64 -> area0 (after the base MMAs have read it)
+      FRACSSM_WAIT(bar0, 3 * n);
+      FRACSSM_MARK(2)
+      produce_level(area0, 4);
+      produce_level(area0 + kTileBytes, 8);
+      warp_arrive(full + 2, lane);
+      FRACSSM_MARK(3)
+
+      // ---- Chat (high, low) and Khat (high) -> area1 / chat_lo (after levels 8/16 have read area1)
+      FRACSSM_WAIT(bar1, 2 * n);
+      FRACSSM_MARK(4)
+      {
+        float e[4], f[4];
+        seg_prod(seg, 0, w, lane, e);
+        seg_prod(seg, w + 1, 16, lane, f);
+        if (w == 0)
+          *reinterpret_cast<float4 *>(gt_s + 4 * lane) =
+              make_float4(g8[0] * f[0], g8[1] * f[1], g8[2] * f[2], g8[3] * f[3]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v[4], vl[4], kh[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float chat = cp[i][q] * e[q];
+            v[q] = __bfloat162float(__float2bfloat16_rn(chat));
+            vl[q] = chat - v[q];
+            const float full_k = ks[i][q] * f[q];
+            kh[q] = __bfloat162float(__float2bfloat16_rn(full_k));
+            ks[i][q] = full_k - kh[q];  // low part, emitted with the next batch
+          }
+          emit4(area1, 8 * w + i, lane, v);
+          emit4(chat_lo, 8 * w + i, lane, vl);
+          emit4(area1 + kTileBytes, 8 * w + i, lane, kh);
+        }
+      }
+      warp_arrive(full + 3, lane);
+      FRACSSM_MARK(5)
+
+      // ---- Khat (low) and W -> area0 (after every level MMA has completed)
+      FRACSSM_WAIT(bar0, 3 * n + 1);
       umma::tc_fence_after();
+      FRACSSM_MARK(6)
 #pragma unroll
-      for (int s = 0; s < 8; ++s)  // Sacc += Klo^T u
-        umma::mma_ss(tmem + kColS, umma::make_sdesc(sA0 + s * 2048, kAtom, 1024),
-                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdMnMn64, 1u);
-      umma::mma_commit(bar0);
+      for (int i = 0; i < 8; ++i) emit4(area0, 8 * w + i, lane, ks[i]);
+
+      // the next item (published by the control warp at the start of this tile); it must be read
+      // here, before this warp's arrival lets the control warp move on and publish again
+      FRACSSM_WAIT(item_bar, n + 1);
+      const int next = items[(n + 1) & 1];
+      FRACSSM_MARK(7)
+
+      {
+        uint8_t *wt = area0 + kTileBytes;
+        const int t = 32 * Q + lane;
 #pragma unroll
-      for (int s = 0; s < 8; ++s)  // H = W u
-        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA0 + kTileBytes + koff(s), 16, 1024),
-                     umma::make_sdesc(sU + s * 2048, kAtom, 1024), kIdKMn64, s > 0);
-      // wait for the state left by the previous tile of this (batch, head) row
-      if (j > 0) {
-        const uint64_t t_start = umma::global_ns();
-        while (ld_acquire(a.flags + bh) < j) {
-          __nanosleep(100);
-          if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+        for (int g = 0; g < 4; ++g) {
+          float v[8];
+          if (P > Q) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) v[x] = 0.f;
+          } else if (P < Q) {
+            const uint32_t col = ((Q >> 1) != (P >> 1)) ? (kColL64 + 32 * P + 8 * g)
+                                                        : (kColL32 + (P >> 1) * 32 + 8 * g);
+            umma::tmem_ld8(lane_addr + col, v);
+            umma::tmem_ld_wait();
+          } else {
+            float b[8], l8[8], l16[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) l8[x] = l16[x] = 0.f;
+            umma::tmem_ld8(lane_addr + kColBase + 32 * Q + 8 * g, b);
+            if ((g & 1) == 0) umma::tmem_ld8(lane_addr + kColL8 + (2 * Q + (g >> 1)) * 8, l8);
+            if (g < 2) umma::tmem_ld8(lane_addr + kColL16 + (g & 1) * 32 + Q * 8, l16);
+            umma::tmem_ld_wait();
+            const int tb = lane >> 3;  // 8-token block of this row inside its 32-token block
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              float r = 0.f;
+              if (g == tb) r = (x <= (lane & 7)) ? b[x] : 0.f;
+              else if (g < tb) r = ((tb ^ g) >= 2) ? l16[x] : l8[x];
+              v[x] = r;
+            }
+          }
+          uint4 pk;
+          pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
+          const uint32_t chunk = (4 * P + g) & 7;
+          *reinterpret_cast<uint4 *>(wt + (P >> 1) * kAtom + t * 128 + ((chunk ^ (t & 7)) << 4)) = pk;
         }
       }
-    }
-    __syncthreads();
-    FRACSSM_MARK(11)
+      warp_arrive(full + 4, lane);
+      FRACSSM_MARK(8)
 
-    // ---- incoming state: float32 copy in registers, bf16 copy as the MMA operand
-    const int m_row = 32 * Q + lane;
-    float sj[16];
-    {
-      float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
-      if (j > 0) {
+      // ---- incoming state: float32 copy in registers, bf16 high / low copies as MMA operands
+      FRACSSM_WAIT(state_bar, n);
+      umma::named_barrier(2, kWorkers);  // also orders warp 0's write of gt_s before its readers
+      FRACSSM_MARK(9)
+      const int m_row = 32 * Q + lane;
+      float sj[16];
+      {
+        const float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+        if (j > 0) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const float4 v = __ldcg(reinterpret_cast<const float4 *>(sp) + x);
-          sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
+          for (int x = 0; x < 4; ++x) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(sp) + x);
+            sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
+          }
+        } else if (a.init) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
         }
-      } else if (a.init) {
 #pragma unroll
-        for (int x = 0; x < 16; ++x)
-          sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
-      } else {
+        for (int half = 0; half < 2; ++half) {
+          float hi[8], lo[8];
 #pragma unroll
-        for (int x = 0; x < 16; ++x) sj[x] = 0.f;
-      }
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float hi[8], lo[8];
-#pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
-          lo[x] = sj[8 * half + x] - hi[x];
+          for (int x = 0; x < 8; ++x) {
+            hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
+            lo[x] = sj[8 * half + x] - hi[x];
+          }
+          uint4 pk, pl;
+          pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
+          pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
+          const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+          *reinterpret_cast<uint4 *>(s_tile + off) = pk;
+          *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
         }
-        uint4 pk, pl;
-        pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
-        pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
-        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-        *reinterpret_cast<uint4 *>(s_tile + off) = pk;
-        *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
       }
-    }
-    umma::fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      // H += Chat S with both factors split into bf16 high and low parts (low x low dropped)
-#pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA1 + koff(s), 16, 1024),
-                     umma::make_sdesc(sS + s * 2048, kAtom, 1024), kIdKMn64, 1u);
-#pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma::mma_ss(tmem + kColH, umma::make_sdesc(sClo + koff(s), 16, 1024),
-                     umma::make_sdesc(sS + s * 2048, kAtom, 1024), kIdKMn64, 1u);
-#pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma::mma_ss(tmem + kColH, umma::make_sdesc(sA1 + koff(s), 16, 1024),
-                     umma::make_sdesc(sSlo + s * 2048, kAtom, 1024), kIdKMn64, 1u);
-      umma::mma_commit(barH);
-    }
+      warp_arrive(full + 5, lane);
+      FRACSSM_MARK(10)
 
-    // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
-    FRACSSM_MARK(12)
-    ok = umma::mbar_wait(bar1, ph1 & 1, kWaitNs) && ok; ++ph1;   // Khat(high) MMAs
-    ok = umma::mbar_wait(bar0, ph0 & 1, kWaitNs) && ok; ++ph0;   // Khat(low) MMAs
-    FRACSSM_MARK(13)
-    umma::tc_fence_after();
-    {
-      float acc[16];
-      umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
-      umma::tmem_ld_wait();
-      const float gt = gt_s[m_row];
+      // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
+      FRACSSM_WAIT(bar1, 2 * n + 1);  // Khat(high) MMAs
+      FRACSSM_WAIT(bar0, 3 * n + 2);  // Khat(low) MMAs
+      umma::tc_fence_after();
+      FRACSSM_MARK(11)
+      {
+        float acc[16];
+        umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
+        umma::tmem_ld_wait();
+        const float gt = gt_s[m_row];
 #pragma unroll
-      for (int x = 0; x < 16; ++x) sj[x] = fmaf(gt, sj[x], acc[x]);
-      float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
-      if (j + 1 < a.ntiles) {
+        for (int x = 0; x < 16; ++x) sj[x] = fmaf(gt, sj[x], acc[x]);
+        float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+        if (j + 1 < a.ntiles) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-          __stcg(reinterpret_cast<float4 *>(sp) + x,
-                 make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
-      } else if (a.fin) {
+          for (int x = 0; x < 4; ++x)
+            __stcg(reinterpret_cast<float4 *>(sp) + x,
+                   make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
+        } else if (a.fin) {
 #pragma unroll
-        for (int x = 0; x < 16; ++x)
-          st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, sj[x]);
+          for (int x = 0; x < 16; ++x)
+            st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, sj[x]);
+        }
       }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
-    FRACSSM_MARK(14)
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
+      FRACSSM_MARK(12)
 
-    // ---- output rows
-    ok = umma::mbar_wait(barH, phH & 1, kWaitNs) && ok; ++phH;
-    FRACSSM_MARK(15)
-    umma::tc_fence_after();
-    {
-      float acc[16];
-      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
-      umma::tmem_ld_wait();
-      const int t = t0 + 32 * Q + lane;
-      if (t < a.L) {
-        uint4 lo, hi;
-        lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
-        hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
-        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(bh) * a.L + t) * kR + 16 * P);
-        __stcs(dst, lo);
-        __stcs(dst + 1, hi);
+      // ---- output rows
+      FRACSSM_WAIT(barH, n);
+      umma::tc_fence_after();
+      FRACSSM_MARK(13)
+      {
+        float acc[16];
+        umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
+        umma::tmem_ld_wait();
+        const int t = t0 + 32 * Q + lane;
+        if (t < a.L) {
+          uint4 lo, hi;
+          lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
+          hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
+          uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(bh) * a.L + t) * kR + 16 * P);
+          __stcs(dst, lo);
+          __stcs(dst + 1, hi);
+        }
       }
+      umma::tc_fence_before();
+      FRACSSM_MARK(14)
+      item = next;
+    }
+    if (tid == 0 && a.prof && blockIdx.x < kProfCtas) {
+      for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
     }
   }
 
-  if (tid == 0 && a.prof && blockIdx.x < kProfCtas) {
-#pragma unroll
-    for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
-  }
   if (!ok) atomicExch(&a.ctrl[1], 1);
   umma::tc_fence_before();
   __syncthreads();
@@ -572,6 +636,13 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
     if (sm_count[dev] == 0) {
       cudaError_t ae = cudaFuncSetAttribute(scan_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
       if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
+      cudaFuncAttributes fa{};
+      ae = cudaFuncGetAttributes(&fa, scan_fused_kernel);
+      if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
+      if (fa.numRegs < kLaunchRegsNeeded)
+        return fail(FRACSSM_ERR_UNSUPPORTED,
+                    "frac_scan: the single-pass kernel was built with %d registers per thread, needs %d",
+                    fa.numRegs, kLaunchRegsNeeded);
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
       if (n <= 0) return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot query the SM count");

@@ -63,6 +63,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64
   return true;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Same contract as mbar_wait, built on try_wait (the hardware parks the warp for a while on
+// each attempt, so a waiting warp issues very few instructions).
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t *bar, uint32_t parity, uint64_t limit_ns) {
+  uint32_t ok = 0;
+  uint64_t t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (spins == 64) t0 = global_ns();
+    if (spins > 64 && global_ns() - t0 > limit_ns) return false;
+  }
+}
+// Barrier among the first `nthreads` threads of the CTA (a multiple of 32), id 1..15.
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // ---- proxy / tcgen05 fences ----------------------------------------------------------------
 // Make shared-memory writes by ordinary stores visible to the async proxy (MMA / TMA reads).
 __device__ __forceinline__ void fence_async_smem() {
