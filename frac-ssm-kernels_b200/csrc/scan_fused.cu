@@ -57,7 +57,7 @@ constexpr uint32_t kOffU = 196608;
 constexpr uint32_t kOffSeg = 212992;    // float [16][128]: decay product of each 8-token segment
 constexpr uint32_t kOffGt = 221184;     // float [128]: decay product of the whole tile
 constexpr uint32_t kOffMisc = 221696;   // mbarriers, TMEM base, tickets
-constexpr uint32_t kSmemBytes = kOffMisc + 128 + 128 + 1024;
+constexpr uint32_t kSmemBytes = kOffMisc + 192 + 128 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
 constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
                    kColL64 = 448;
@@ -74,7 +74,7 @@ struct FusedArgs {
   int *ctrl;     // [0] ticket counter, [1] error word
   long long *prof;  // [kProfCtas][16] cycles spent per phase by worker thread 0 of each CTA
   int *flags;    // [BH] tiles finished per bh
-  float *state;  // [BH][128 m][64 r] running state
+  float *state;  // running state per row, 128 m x 64 r floats in the order the workers access it
   int BH, L, ntiles, total;
 };
 
@@ -112,18 +112,18 @@ __device__ __forceinline__ void st_release(int *p, int v) {
 }
 
 
-// Raw inputs of one item for one worker thread: 8 tokens x 4 modes.
+// Raw inputs of one item for one worker thread, one group of 4 tokens x 4 modes.
 struct RawRegs {
-  float4 r[8];
-  uint2 c[8], k[8];
+  float4 r[4];
+  uint2 c[4], k[4];
 };
 
-__device__ __forceinline__ void load_raw(RawRegs &raw, const FusedArgs &a, int item, int w, int lane) {
+__device__ __forceinline__ void load_raw(RawRegs &raw, const FusedArgs &a, int item, int w, int lane, int grp) {
   const int j = item / a.BH, bh = item - j * a.BH;
-  const int t0 = j * kTile + 8 * w;
+  const int t0 = j * kTile + 8 * w + 4 * grp;
   const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4; ++i) {
     raw.r[i] = make_float4(1.f, 1.f, 1.f, 1.f);
     raw.c[i] = make_uint2(0u, 0u);
     raw.k[i] = make_uint2(0u, 0u);
@@ -153,20 +153,19 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   uint8_t *chat_lo = smem + kOffChatLo;
   float *seg = reinterpret_cast<float *>(smem + kOffSeg);
   float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
-  // mbarriers: bar0 / bar1 / barH are completed by tcgen05.commit, barU by the TMA load,
+  // mbarriers: cb[0..4] / barH are completed by tcgen05.commit (each once per tile), barU by the TMA load,
   // full[0..5] by the 16 worker warps, item_bar and state_bar by the control warp.
-  uint64_t *bar0 = reinterpret_cast<uint64_t *>(smem + kOffMisc);
-  uint64_t *bar1 = bar0 + 1, *barH = bar0 + 2, *barU = bar0 + 3, *full = bar0 + 4;
-  uint64_t *item_bar = bar0 + 10, *state_bar = bar0 + 11, *out_bar = bar0 + 12;
-  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bar0 + 13);
+  uint64_t *cb = reinterpret_cast<uint64_t *>(smem + kOffMisc);  // cb[0..4]: one per MMA batch
+  uint64_t *barH = cb + 5, *barU = cb + 6, *full = cb + 7;
+  uint64_t *item_bar = cb + 13, *state_bar = cb + 14, *out_bar = cb + 15;
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(cb + 16);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
-  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 128);  // worker thread 0 only
+  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 192);  // worker thread 0 only
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
-    umma::mbar_init(bar0, 1);
-    umma::mbar_init(bar1, 1);
+    for (int i = 0; i < 5; ++i) umma::mbar_init(cb + i, 1);
     umma::mbar_init(barH, 1);
     umma::mbar_init(barU, 1);
     for (int i = 0; i < 6; ++i) umma::mbar_init(full + i, 16);
@@ -251,7 +250,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       umma::tc_fence_after();
       if (lane == 0) {
         piece(kColBase, sA0, false, sA0 + kTileBytes, false, 1024, kIdKK128, 0u);
-        umma::mma_commit(bar0);
+        umma::mma_commit(cb + 0);
       }
       // levels 8 and 16 (area1): first halves are picked by the B descriptor's row-group stride
       FRACSSM_WAIT(full + 1, n);
@@ -260,32 +259,32 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         piece(kColL8, sA1, false, sA1, false, 2048, kIdKK64, 0u);                      // every other 8-row group
         piece(kColL16, sA1 + kTileBytes, false, sA1 + kTileBytes, false, 4096, kIdKK32, 0u);   // groups 0,4,8,12
         piece(kColL16 + 32, sA1 + kTileBytes, false, sA1 + kTileBytes + 1024, false, 4096, kIdKK32, 0u);  // 1,5,9,13
-        umma::mma_commit(bar1);
+        umma::mma_commit(cb + 1);
       }
-      // levels 32 and 64 (area0)
+      // levels 32 and 64 (the Chat-low and state slots, idle until late in the tile)
       FRACSSM_WAIT(full + 2, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColL32, sA0, false, sA0, false, 1024, kIdKK32, 0u);                     // rows 0..31
-        piece(kColL32 + 32, sA0, false, sA0 + 8192, false, 1024, kIdKK32, 0u);         // rows 64..95
-        piece(kColL64, sA0 + kTileBytes, false, sA0 + kTileBytes, false, 1024, kIdKK64, 0u);  // rows 0..63
-        umma::mma_commit(bar0);
+        piece(kColL32, sClo, false, sClo, false, 1024, kIdKK32, 0u);                   // rows 0..31
+        piece(kColL32 + 32, sClo, false, sClo + 8192, false, 1024, kIdKK32, 0u);       // rows 64..95
+        piece(kColL64, sS, false, sS, false, 1024, kIdKK64, 0u);                       // rows 0..63
+        umma::mma_commit(cb + 2);
       }
       // Sacc[m,r] = sum_k Khi[k,m] u[k,r]
       FRACSSM_WAIT(full + 3, n);
       FRACSSM_WAIT(barU, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
-        umma::mma_commit(bar1);
+        piece(kColS, sA0 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
+        umma::mma_commit(cb + 3);
       }
       // Sacc += Klo^T u;  H = W u
       FRACSSM_WAIT(full + 4, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColS, sA0, true, sU, true, 1024, kIdMnMn64, 1u);
-        umma::mma_commit(bar0);
-        piece(kColH, sA0 + kTileBytes, false, sU, true, 1024, kIdKMn64, 0u);
+        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
+        umma::mma_commit(cb + 4);
+        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 0u);
         // the state left by the previous tile of this (batch, head) row
         if (j > 0 && ok) {
           const uint64_t t_start = umma::global_ns();
@@ -301,9 +300,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_WAIT(full + 5, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColH, sA1, false, sS, true, 1024, kIdKMn64, 1u);
-        piece(kColH, sClo, false, sS, true, 1024, kIdKMn64, 1u);
-        piece(kColH, sA1, false, sSlo, true, 1024, kIdKMn64, 1u);
+        piece(kColH, sA0, false, sS, true, 1024, kIdKMn64, 1u);    // Chat(high) S(high)
+        piece(kColH, sA1, false, sS, true, 1024, kIdKMn64, 1u);    // Chat(low)  S(high)
+        piece(kColH, sA0, false, sSlo, true, 1024, kIdKMn64, 1u);  // Chat(high) S(low)
         umma::mma_commit(barH);
       }
       // publish the outgoing state: the workers' stores are ordered before their arrivals on
@@ -329,27 +328,30 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
+    RawRegs raw0;  // tokens 0..3 of this thread's segment, loaded one tile ahead
+    if (item < a.total) load_raw(raw0, a, item, w, lane, 0);
 
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
       const int t0 = j * kTile;
-      RawRegs raw;
-      load_raw(raw, a, item, w, lane);
 
       // ---- segment products and the base tiles, from the raw registers; one group of 4 tokens
       // at a time to keep few values live
       float cp[8][4], ks[8][4], g8[4];
       {
+        RawRegs raw1;  // tokens 4..7: in flight while the first group is worked on
+        load_raw(raw1, a, item, w, lane, 1);
         float ga[4], gb[4];
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
+          const RawRegs &raw = grp ? raw1 : raw0;
           float a0[4][4], b0[4][4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             float rr[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float4 v = raw.r[4 * grp + i];
+              const float4 v = raw.r[i];
               rr[i] = fmaxf(q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w, kRhoFloor);
             }
             // p4: running product from the start of the group (inclusive)
@@ -360,7 +362,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             if (grp == 0) ga[q] = p4[3]; else gb[q] = p4[3];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint2 cu = raw.c[4 * grp + i], ku = raw.k[4 * grp + i];
+              const uint2 cu = raw.c[i], ku = raw.k[i];
               const uint32_t cw = (q < 2) ? cu.x : cu.y, kw = (q < 2) ? ku.x : ku.y;
               const float cf = __uint_as_float((q & 1) ? (cw & 0xFFFF0000u) : (cw << 16));
               const float kf = __uint_as_float((q & 1) ? (kw & 0xFFFF0000u) : (kw << 16));
@@ -417,16 +419,18 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       warp_arrive(full + 1, lane);
       FRACSSM_MARK(1)
 
-      // ---- levels 32 and 64 -> area0 (after the base MMAs have read it)
-      FRACSSM_WAIT(bar0, 3 * n);
-      FRACSSM_MARK(2)
-      produce_level(area0, 4);
-      produce_level(area0 + kTileBytes, 8);
+      // ---- levels 32 and 64 -> the Chat-low and state slots (their readers finished with the
+      // previous tile), so nothing has to be waited for here
+      produce_level(chat_lo, 4);
+      produce_level(s_tile, 8);
       warp_arrive(full + 2, lane);
       FRACSSM_MARK(3)
 
-      // ---- Chat (high, low) and Khat (high) -> area1 / chat_lo (after levels 8/16 have read area1)
-      FRACSSM_WAIT(bar1, 2 * n);
+      // ---- Chat (high) and Khat (high) -> area0 (after the base MMAs), Chat (low) -> area1 tile 0
+      // (after the level-8/16 MMAs)
+      FRACSSM_WAIT(cb + 0, n);
+      FRACSSM_MARK(2)
+      FRACSSM_WAIT(cb + 1, n);
       FRACSSM_MARK(4)
       {
         float e[4], f[4];
@@ -447,20 +451,20 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             kh[q] = __bfloat162float(__float2bfloat16_rn(full_k));
             ks[i][q] = full_k - kh[q];  // low part, emitted with the next batch
           }
-          emit4(area1, 8 * w + i, lane, v);
-          emit4(chat_lo, 8 * w + i, lane, vl);
-          emit4(area1 + kTileBytes, 8 * w + i, lane, kh);
+          emit4(area0, 8 * w + i, lane, v);
+          emit4(area1, 8 * w + i, lane, vl);
+          emit4(area0 + kTileBytes, 8 * w + i, lane, kh);
         }
       }
       warp_arrive(full + 3, lane);
       FRACSSM_MARK(5)
 
-      // ---- Khat (low) and W -> area0 (after every level MMA has completed)
-      FRACSSM_WAIT(bar0, 3 * n + 1);
+      // ---- Khat (low) -> area1 tile 1, W -> the Chat-low slot (after every level MMA has completed)
+      FRACSSM_WAIT(cb + 2, n);
       umma::tc_fence_after();
       FRACSSM_MARK(6)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) emit4(area0, 8 * w + i, lane, ks[i]);
+      for (int i = 0; i < 8; ++i) emit4(area1 + kTileBytes, 8 * w + i, lane, ks[i]);
 
       // the next item (published by the control warp at the start of this tile); it must be read
       // here, before this warp's arrival lets the control warp move on and publish again
@@ -469,7 +473,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_MARK(7)
 
       {
-        uint8_t *wt = area0 + kTileBytes;
+        uint8_t *wt = chat_lo;
         const int t = 32 * Q + lane;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -515,11 +519,13 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       const int m_row = 32 * Q + lane;
       float sj[16];
       {
-        const float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
+        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
+                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
         if (j > 0) {
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(sp) + x);
+            const float4 v = __ldcg(sp + x * kM);
             sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
           }
         } else if (a.init) {
@@ -550,8 +556,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_MARK(10)
 
       // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
-      FRACSSM_WAIT(bar1, 2 * n + 1);  // Khat(high) MMAs
-      FRACSSM_WAIT(bar0, 3 * n + 2);  // Khat(low) MMAs
+      FRACSSM_WAIT(cb + 3, n);  // Khat(high) MMAs
+      FRACSSM_WAIT(cb + 4, n);  // Khat(low) MMAs
       umma::tc_fence_after();
       FRACSSM_MARK(11)
       {
@@ -561,12 +567,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         const float gt = gt_s[m_row];
 #pragma unroll
         for (int x = 0; x < 16; ++x) sj[x] = fmaf(gt, sj[x], acc[x]);
-        float *sp = a.state + (static_cast<int64_t>(bh) * kM + m_row) * kR + 16 * P;
+        float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
         if (j + 1 < a.ntiles) {
 #pragma unroll
           for (int x = 0; x < 4; ++x)
-            __stcg(reinterpret_cast<float4 *>(sp) + x,
-                   make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
+            __stcg(sp + x * kM, make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
         } else if (a.fin) {
 #pragma unroll
           for (int x = 0; x < 16; ++x)
@@ -575,6 +580,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
       __syncwarp();
       if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
+      // start the loads of the next item; they land while the output rows are written
+      if (next < a.total) load_raw(raw0, a, next, w, lane, 0);
       FRACSSM_MARK(12)
 
       // ---- output rows
