@@ -316,8 +316,12 @@ def main():
         peak, peak_kind = measured_peak_gbs()
         alg = algorithmic_bytes(BH, L, R, M)
         achieved = alg / (scan_ms * 1e-3) / 1e9
+        # DRAM bytes per launch from one ncu capture of the single-pass kernel on a 192 x 1024 case
+        # (dram read 228.0 MB + the 25.2 MB of h it writes), scaled by head-tokens; traffic grows in
+        # proportion to the tiles processed.  Staged path: not captured.
+        traffic = int(253.2e6 / (192 * 1024) * BH * L) if use_fused else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                    "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                     "kernel": "scan_fused_kernel" if use_fused else
                               "staged scan (chunk_cumsum + chunk_state + state_passing + chunk_readout<fused>)",
                     "kernel_ms": scan_ms, "algorithmic_bytes": alg}
