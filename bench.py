@@ -244,6 +244,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # preheat: a fresh GPU needs a few hundred ms of work before its clocks settle (the reference's
+    # timer does the same with a 200 ms GEMM, frac_ssm/benchmark.py:274-293); untimed, like the warm-up
+    t_pre = time.perf_counter()
+    while time.perf_counter() - t_pre < 0.5:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
     for _ in range(args.warmup):
         step()
     barrier()

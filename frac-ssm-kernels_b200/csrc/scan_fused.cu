@@ -88,13 +88,30 @@ __device__ __forceinline__ void emit4(uint8_t *tile, int row, int lane, const fl
   *reinterpret_cast<uint2 *>(tile + off) = pk;
 }
 
-// Product of the segment decays seg[lo..hi) for this lane's four modes.
-__device__ __forceinline__ void seg_prod(const float *seg, int lo, int hi, int lane, float (&out)[4]) {
-  out[0] = out[1] = out[2] = out[3] = 1.f;
+// Product of the segment decays seg[lo..hi) for this lane's four modes (as two packed pairs).
+__device__ __forceinline__ void seg_prod(const float *seg, int lo, int hi, int lane, float2 (&out)[2]) {
+  out[0] = out[1] = make_float2(1.f, 1.f);
   for (int s = lo; s < hi; ++s) {
     const float4 g = *reinterpret_cast<const float4 *>(seg + s * kM + 4 * lane);
-    out[0] *= g.x; out[1] *= g.y; out[2] *= g.z; out[3] *= g.w;
+    out[0] = __fmul2_rn(out[0], make_float2(g.x, g.y));
+    out[1] = __fmul2_rn(out[1], make_float2(g.z, g.w));
   }
+}
+
+// Store four consecutive modes of token row 8*w + i of an operand tile (32-bit shared address).
+// th_off = this thread's fixed part of the swizzled offset, c16 = its 16-byte chunk index << 4.
+__device__ __forceinline__ void emit_row(uint32_t tile_s, uint32_t th_off, uint32_t c16, int i, float2 v0,
+                                         float2 v1) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v0.x, v0.y), b = __floats2bfloat162_rn(v1.x, v1.y);
+  const uint32_t addr = tile_s + th_off + i * 128 + (c16 ^ (static_cast<uint32_t>(i) << 4));
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(*reinterpret_cast<const uint32_t *>(&a)),
+               "r"(*reinterpret_cast<const uint32_t *>(&b))
+               : "memory");
+}
+__device__ __forceinline__ float2 bf16_round2(float2 v) {  // each component rounded to bf16, as floats
+  const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
+  const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
 }
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -316,6 +333,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     // =========================== worker warps ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
     const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
+    // operand-tile addressing of this thread: rows 8w..8w+7, modes 4*lane..4*lane+3
+    const uint32_t th_off = (lane >> 4) * kAtom + ((lane & 1) << 3) + w * 1024;
+    const uint32_t c16 = ((lane & 15) >> 1) << 4;
+    const uint32_t sArea0 = umma::smem_u32(area0), sArea1 = umma::smem_u32(area1);
+    const uint32_t sChatLo = umma::smem_u32(chat_lo), sSt = umma::smem_u32(s_tile);
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
     // worker thread 0 charges the cycles since the last mark to a phase (diagnostic)
     long long t_mark = clock64();
@@ -337,7 +359,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
       // ---- segment products and the base tiles, from the raw registers; one group of 4 tokens
       // at a time to keep few values live
-      float cp[8][4], ks[8][4], g8[4];
+      float2 cp[8][2], ks[8][2];
+      float g8[4];
       {
         RawRegs raw1;  // tokens 4..7: in flight while the first group is worked on
         load_raw(raw1, a, item, w, lane, 1);
@@ -366,30 +389,34 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
               const uint32_t cw = (q < 2) ? cu.x : cu.y, kw = (q < 2) ? ku.x : ku.y;
               const float cf = __uint_as_float((q & 1) ? (cw & 0xFFFF0000u) : (cw << 16));
               const float kf = __uint_as_float((q & 1) ? (kw & 0xFFFF0000u) : (kw << 16));
+              float &cpv = (q & 1) ? cp[4 * grp + i][q >> 1].y : cp[4 * grp + i][q >> 1].x;
+              float &ksv = (q & 1) ? ks[4 * grp + i][q >> 1].y : ks[4 * grp + i][q >> 1].x;
               if (grp == 0) {  // base reference point: between token 3 and token 4 of the segment
                 a0[i][q] = __fdividef(cf, s4[i]);
                 b0[i][q] = kf * s4[i];
-                cp[i][q] = cf * p4[i];
-                ks[i][q] = kf * s4[i];          // times gb, below
+                cpv = cf * p4[i];
+                ksv = kf * s4[i];          // times gb, below
               } else {
                 a0[i][q] = cf * p4[i];
                 b0[i][q] = __fdividef(kf, p4[i]);
-                cp[4 + i][q] = cf * ga[q] * p4[i];
-                ks[4 + i][q] = kf * s4[i];
+                cpv = cf * ga[q] * p4[i];
+                ksv = kf * s4[i];
               }
             }
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            emit4(area0, 8 * w + 4 * grp + i, lane, a0[i]);
-            emit4(area0 + kTileBytes, 8 * w + 4 * grp + i, lane, b0[i]);
+            emit_row(sArea0, th_off, c16, 4 * grp + i, make_float2(a0[i][0], a0[i][1]), make_float2(a0[i][2], a0[i][3]));
+            emit_row(sArea0 + kTileBytes, th_off, c16, 4 * grp + i, make_float2(b0[i][0], b0[i][1]),
+                     make_float2(b0[i][2], b0[i][3]));
           }
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          g8[q] = ga[q] * gb[q];
+        for (int q = 0; q < 4; ++q) g8[q] = ga[q] * gb[q];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) ks[i][q] *= gb[q];
+        for (int i = 0; i < 4; ++i) {
+          ks[i][0] = __fmul2_rn(ks[i][0], make_float2(gb[0], gb[1]));
+          ks[i][1] = __fmul2_rn(ks[i][1], make_float2(gb[2], gb[3]));
         }
         *reinterpret_cast<float4 *>(seg + w * kM + 4 * lane) = make_float4(g8[0], g8[1], g8[2], g8[3]);
       }
@@ -398,31 +425,28 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_MARK(0)
 
       // One sibling level: every token row holds its A-role or B-role value.
-      auto produce_level = [&](uint8_t *tile, int hseg) {
-        float sig[4];
+      auto produce_level = [&](uint32_t tile_s, int hseg) {
+        float2 sig[2];
         const bool role_a = (w & hseg) != 0;
         const int first = w - (w & (hseg - 1));
         if (role_a) seg_prod(seg, first, w, lane, sig);
         else seg_prod(seg, w + 1, first + hseg, lane, sig);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float v[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) v[q] = (role_a ? cp[i][q] : ks[i][q]) * sig[q];
-          emit4(tile, 8 * w + i, lane, v);
-        }
+        for (int i = 0; i < 8; ++i)
+          emit_row(tile_s, th_off, c16, i, __fmul2_rn(role_a ? cp[i][0] : ks[i][0], sig[0]),
+                   __fmul2_rn(role_a ? cp[i][1] : ks[i][1], sig[1]));
       };
 
       // ---- levels 8 and 16 -> area1
-      produce_level(area1, 1);
-      produce_level(area1 + kTileBytes, 2);
+      produce_level(sArea1, 1);
+      produce_level(sArea1 + kTileBytes, 2);
       warp_arrive(full + 1, lane);
       FRACSSM_MARK(1)
 
       // ---- levels 32 and 64 -> the Chat-low and state slots (their readers finished with the
       // previous tile), so nothing has to be waited for here
-      produce_level(chat_lo, 4);
-      produce_level(s_tile, 8);
+      produce_level(sChatLo, 4);
+      produce_level(sSt, 8);
       warp_arrive(full + 2, lane);
       FRACSSM_MARK(3)
 
@@ -433,27 +457,27 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_WAIT(cb + 1, n);
       FRACSSM_MARK(4)
       {
-        float e[4], f[4];
+        float2 e[2], f[2];
         seg_prod(seg, 0, w, lane, e);
         seg_prod(seg, w + 1, 16, lane, f);
         if (w == 0)
           *reinterpret_cast<float4 *>(gt_s + 4 * lane) =
-              make_float4(g8[0] * f[0], g8[1] * f[1], g8[2] * f[2], g8[3] * f[3]);
+              make_float4(g8[0] * f[0].x, g8[1] * f[0].y, g8[2] * f[1].x, g8[3] * f[1].y);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float v[4], vl[4], kh[4];
+          float2 ch[2], cl[2], kh[2];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float chat = cp[i][q] * e[q];
-            v[q] = __bfloat162float(__float2bfloat16_rn(chat));
-            vl[q] = chat - v[q];
-            const float full_k = ks[i][q] * f[q];
-            kh[q] = __bfloat162float(__float2bfloat16_rn(full_k));
-            ks[i][q] = full_k - kh[q];  // low part, emitted with the next batch
+          for (int hf = 0; hf < 2; ++hf) {
+            const float2 chat = __fmul2_rn(cp[i][hf], e[hf]);
+            ch[hf] = bf16_round2(chat);
+            cl[hf] = __fadd2_rn(chat, make_float2(-ch[hf].x, -ch[hf].y));
+            const float2 full_k = __fmul2_rn(ks[i][hf], f[hf]);
+            kh[hf] = bf16_round2(full_k);
+            ks[i][hf] = __fadd2_rn(full_k, make_float2(-kh[hf].x, -kh[hf].y));  // low part, next batch
           }
-          emit4(area0, 8 * w + i, lane, v);
-          emit4(area1, 8 * w + i, lane, vl);
-          emit4(area0 + kTileBytes, 8 * w + i, lane, kh);
+          emit_row(sArea0, th_off, c16, i, ch[0], ch[1]);
+          emit_row(sArea1, th_off, c16, i, cl[0], cl[1]);
+          emit_row(sArea0 + kTileBytes, th_off, c16, i, kh[0], kh[1]);
         }
       }
       warp_arrive(full + 3, lane);
@@ -464,7 +488,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       umma::tc_fence_after();
       FRACSSM_MARK(6)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) emit4(area1 + kTileBytes, 8 * w + i, lane, ks[i]);
+      for (int i = 0; i < 8; ++i) emit_row(sArea1 + kTileBytes, th_off, c16, i, ks[i][0], ks[i][1]);
 
       // the next item (published by the control warp at the start of this tile); it must be read
       // here, before this warp's arrival lets the control warp move on and publish again
