@@ -294,15 +294,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       if (lane == 0) {
         piece(kColS, sA0 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
         umma::mma_commit(cb + 3);
-      }
-      // Sacc += Klo^T u;  H = W u
-      FRACSSM_WAIT(full + 4, n);
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
-        umma::mma_commit(cb + 4);
-        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 0u);
-        // the state left by the previous tile of this (batch, head) row
+        // the state left by the previous tile of this (batch, head) row: usually there already,
+        // so tell the workers before they ask
         if (j > 0 && ok) {
           const uint64_t t_start = umma::global_ns();
           while (ld_acquire(a.flags + bh) < j) {
@@ -313,6 +306,14 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         umma::mbar_arrive(state_bar);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      // Sacc += Klo^T u;  H = W u
+      FRACSSM_WAIT(full + 4, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
+        umma::mma_commit(cb + 4);
+        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 0u);
+      }
       // H += Chat S, both factors split into bf16 high and low parts (low x low dropped)
       FRACSSM_WAIT(full + 5, n);
       umma::tc_fence_after();
@@ -350,8 +351,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
-    RawRegs raw0;  // tokens 0..3 of this thread's segment, loaded one tile ahead
-    if (item < a.total) load_raw(raw0, a, item, w, lane, 0);
 
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
@@ -362,7 +361,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       float2 cp[8][2], ks[8][2];
       float g8[4];
       {
-        RawRegs raw1;  // tokens 4..7: in flight while the first group is worked on
+        // the inputs were pulled into L2 a tile ahead; both groups are requested at once
+        RawRegs raw0, raw1;
+        load_raw(raw0, a, item, w, lane, 0);
         load_raw(raw1, a, item, w, lane, 1);
         float ga[4], gb[4];
 #pragma unroll
@@ -604,8 +605,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
       __syncwarp();
       if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
-      // start the loads of the next item; they land while the output rows are written
-      if (next < a.total) load_raw(raw0, a, next, w, lane, 0);
       FRACSSM_MARK(12)
 
       // ---- output rows
