@@ -179,6 +179,57 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_seq_workload(args, rank, world, dev, dist):
+    """Config 3: batch 1, L 1,048,576, 24 heads, sequence split evenly over the ranks; per step one
+    segment-summary pass, one all-gather of (state, decay) per rank, one scan with the true state."""
+    from frac_ssm_b200 import parallel
+    Ltot, H, R, M, T = 1048576, CFG["H"], CFG["R"], CFG["M"], CFG["T"]
+    tok = parallel.shard_tokens(Ltot, T, rank, world)
+    Ll = tok.stop - tok.start
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    u = (0.25 * torch.randn(H, Ll, R, device=dev, generator=g)).bfloat16()
+    c = torch.softmax(torch.randn(H, Ll, M, device=dev, generator=g), -1).bfloat16()
+    tau = torch.linspace(0.0, math.log(65536.0), M, device=dev).exp()
+    dt = torch.nn.functional.softplus(torch.randn(H, Ll, 1, device=dev, generator=g) - 4.0)
+    rho = torch.exp(-dt * 4.0 / tau).clamp(1e-6, 1 - 1e-6)
+    kappa = ((1 - rho) * torch.softmax(torch.randn(H, Ll, M, device=dev, generator=g), -1)).bfloat16()
+
+    def step():
+        if world == 1:
+            return parallel.CudaStageOps.scan(u, c, kappa, rho, T, None)[0]
+        return parallel.seq_parallel_scan(u, c, kappa, rho, T, None, False)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        alg = algorithmic_bytes(H, Ltot, R, M)
+        print(json.dumps({"metric": "frac_scan fwd tokens/s, one 1,048,576-token sequence split by sequence",
+                          "value": Ltot / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "config 3: batch 1, L 1048576, 24 heads, R 64, M 128, chunk 256",
+                                     "sharding": f"sequence over {world} GPU(s), one all-gather of 790 KB per rank"},
+                          "algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def workload_config(n):
     return {"workload": "config 1: single-layer frac_scan forward + skip-mix/gated-RMSNorm epilogue, "
                         "batch 8 x 24 heads, L 8192, R 64, M 128, chunk 256, per GPU",
@@ -198,6 +249,9 @@ def main():
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
     ap.add_argument("--phases", action="store_true",
                     help="also print the single-pass kernel's per-phase cycle shares (diagnostic)")
+    ap.add_argument("--workload", default="layer", choices=["layer", "seq"],
+                    help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
+                         "tokens x 24 heads split over the ranks (secondary line, not the driver's metric)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -228,6 +282,9 @@ def main():
     from frac_ssm_b200.ops.b200 import frac_scan
 
     _cabi.lib()
+    if args.workload == "seq":
+        run_seq_workload(args, rank, world, dev, dist)
+        return
     d = device_inputs(dev, seed=rank)
     H, R, T = CFG["H"], CFG["R"], CFG["T"]
     BH, L, M = d["u"].shape[0], CFG["L"], CFG["M"]

@@ -126,3 +126,39 @@ def test_scan_epilogue_matches_unfused_pair():
     mixed = O.skip_mix(h, x, D, H, R, exact=True)
     ref = O.rmsnorm_gated(mixed, w, z.double() + 0.5, 1e-6, exact=True)
     close(y, ref, **TOL_BF16)
+
+
+def test_mixer_path_composition_matches_oracle():
+    """The whole layer path as FracMixer.forward strings it together (prep -> scan -> skip-mix ->
+    gated norm) on the CUDA ops, against the same composition on the CPU oracle."""
+    from frac_ssm_b200.layers import compute_params_from_projections, frac_skip_mix, scan_epilogue
+    from frac_ssm_b200.modules import rmsnorm_gated_fwd
+    from frac_ssm_b200.ops import frac_scan
+    B, L, H, R, M, T = 2, 600, 4, 64, 128, 256
+    g = torch.Generator().manual_seed(9)
+    dyn = torch.randn(B, L, 3 * H, generator=g).bfloat16()
+    rw = torch.randn(B, L, 2 * H * M, generator=g).bfloat16()
+    x_conv = torch.randn(B, L, H * R, generator=g).bfloat16()
+    gate = torch.randn(B, L, H * R, generator=g).bfloat16()
+    dt_bias = torch.randn(H, generator=g) - 2.0
+    log_tau = torch.linspace(0.0, 11.09, M)
+    D = torch.randn(H, R, generator=g)
+    w = (1 + 0.1 * torch.randn(H * R, generator=g)).bfloat16()
+    pargs = (H, R, M, 1.0, *CFG.values())
+
+    u, c, kappa, rho = compute_params_from_projections(
+        dyn.cuda(), rw.cuda(), x_conv.cuda(), None, dt_bias.cuda(), -2.0, -1.1, log_tau.cuda(), *pargs)
+    h = frac_scan(u, c, kappa, rho, T)                       # fp32 c / kappa with bf16 u: the model's case
+    mod = types.SimpleNamespace(D=D.cuda(), num_heads=H, head_dim=R)
+    mixed = frac_skip_mix(mod, h, x_conv.cuda())
+    y, _ = rmsnorm_gated_fwd(mixed, w.cuda(), gate.cuda(), 1e-6)
+    y_fused = scan_epilogue(h, x_conv.cuda(), gate.cuda(), D.cuda(), w.cuda(), H, R, 1e-6)
+
+    uo, co, ko, ro = O.compute_params(dyn.double(), rw.double(), x_conv, None, dt_bias, torch.tensor([-2.0]),
+                                      torch.tensor([-1.1]), log_tau, *pargs, exact=True)
+    ho = O.frac_scan_slabs(uo.float(), co.float(), ko.float(), ro.float(), T, None, False, exact=True, slab=2)
+    mo = O.skip_mix(ho, x_conv, D, H, R, exact=True)
+    yo = O.rmsnorm_gated(mo, w, gate, 1e-6, exact=True)
+    close(h, ho, **TOL_BF16)
+    close(y, yo, rtol=3e-2, atol=3e-2)       # two bf16 roundings (h, mixed) before the norm
+    close(y_fused, yo, **TOL_BF16)
