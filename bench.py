@@ -87,7 +87,8 @@ def device_inputs(dev, seed):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML in a thread of this
+    process (light; about every 10 ms), or `nvidia-smi -lms 100` when NVML cannot be loaded."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -95,8 +96,40 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.sm, self.mx, self.reasons = [], None, set()
+        self._stop, self._thread, self._nvml = threading.Event(), None, None
+
+    def _nvml_loop(self):
+        nv, h = self._nvml
+        names = (("hw_slowdown", nv.nvmlClocksThrottleReasonHwSlowdown),
+                 ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown),
+                 ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap))
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in names:
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            self._stop.wait(0.01)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[self.index]) if visible and visible.split(",")[0].isdigit() else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self._nvml = (nv, h)
+            self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -110,8 +143,13 @@ class ClockSampler:
             self.rows.append([f.strip() for f in line.split(",")])
 
     def stop(self):
+        if self._nvml is not None:
+            self._stop.set()
+            self._thread.join(timeout=1.0)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.mx,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": "nvml"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
         time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
@@ -126,7 +164,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def cpu_baseline_sample(slabs, threads=None):
@@ -328,7 +366,9 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = e0.elapsed_time(e1) / args.steps
-    scan_ms = statistics.mean(a.elapsed_time(b) for a, b in scan_evs)
+    scan_times = [a.elapsed_time(b) for a, b in scan_evs]
+    scan_ms = statistics.mean(scan_times)
+    scan_ms_median = statistics.median(scan_times)
     if dist is not None:
         t = torch.tensor([ms, scan_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -388,7 +428,7 @@ def main():
                     "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                     "kernel": "scan_fused_kernel" if use_fused else
                               "staged scan (chunk_cumsum + chunk_state + state_passing + chunk_readout<fused>)",
-                    "kernel_ms": scan_ms, "algorithmic_bytes": alg}
+                    "kernel_ms": scan_ms, "kernel_ms_median": scan_ms_median, "algorithmic_bytes": alg}
         cpu = None
         if not args.no_cpu_baseline:
             slabs = 8

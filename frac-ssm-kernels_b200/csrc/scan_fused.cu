@@ -172,7 +172,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
   // mbarriers: cb[0..4] / barH are completed by tcgen05.commit (each once per tile), barU by the TMA load,
   // full[0..5] by the 16 worker warps, item_bar and state_bar by the control warp.
-  uint64_t *cb = reinterpret_cast<uint64_t *>(smem + kOffMisc);  // cb[0..4]: one per MMA batch
+  uint64_t *cb = reinterpret_cast<uint64_t *>(smem + kOffMisc);  // cb[0..3]: one per MMA batch (cb[4] unused)
   uint64_t *barH = cb + 5, *barU = cb + 6, *full = cb + 7;
   uint64_t *item_bar = cb + 13, *state_bar = cb + 14, *out_bar = cb + 15;
   uint32_t *tmem_s = reinterpret_cast<uint32_t *>(cb + 16);
@@ -224,7 +224,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
                      uint32_t idesc, uint32_t acc_first) {
       const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
       const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, b_sbo);
-#pragma unroll 1
+#pragma unroll 4
       for (uint32_t s = 0; s < 8; ++s) {
         const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
         umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
@@ -287,46 +287,48 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         piece(kColL64, sS, false, sS, false, 1024, kIdKK64, 0u);                       // rows 0..63
         umma::mma_commit(cb + 2);
       }
-      // Sacc[m,r] = sum_k Khi[k,m] u[k,r]
+      // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
       FRACSSM_WAIT(full + 3, n);
       FRACSSM_WAIT(barU, n);
       umma::tc_fence_after();
       if (lane == 0) {
+        // the state left by the previous tile of this (batch, head) row: usually there already
+        const bool early = j == 0 || ld_acquire(a.flags + bh) >= j;
+        if (early) umma::mbar_arrive(state_bar);
         piece(kColS, sA0 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
+        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
         umma::mma_commit(cb + 3);
-        // the state left by the previous tile of this (batch, head) row: usually there already,
-        // so tell the workers before they ask
-        if (j > 0 && ok) {
-          const uint64_t t_start = umma::global_ns();
-          while (ld_acquire(a.flags + bh) < j) {
-            __nanosleep(100);
-            if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+        if (!early) {
+          if (ok) {
+            const uint64_t t_start = umma::global_ns();
+            while (ld_acquire(a.flags + bh) < j) {
+              __nanosleep(100);
+              if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+            }
           }
+          umma::mbar_arrive(state_bar);
         }
-        umma::mbar_arrive(state_bar);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      // Sacc += Klo^T u;  H = W u
-      FRACSSM_WAIT(full + 4, n);
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
-        umma::mma_commit(cb + 4);
-        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 0u);
-      }
-      // H += Chat S, both factors split into bf16 high and low parts (low x low dropped)
+      // publish the outgoing state as soon as the workers have stored it: their stores are ordered
+      // before their arrivals on out_bar, this release makes them visible to the next tile's CTA
+      FRACSSM_WAIT(out_bar, n);
+      if (lane == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
+      // H = Chat S, both factors split into bf16 high and low parts (low x low dropped)
       FRACSSM_WAIT(full + 5, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColH, sA0, false, sS, true, 1024, kIdKMn64, 1u);    // Chat(high) S(high)
+        piece(kColH, sA0, false, sS, true, 1024, kIdKMn64, 0u);    // Chat(high) S(high)
         piece(kColH, sA1, false, sS, true, 1024, kIdKMn64, 1u);    // Chat(low)  S(high)
         piece(kColH, sA0, false, sSlo, true, 1024, kIdKMn64, 1u);  // Chat(high) S(low)
+      }
+      // H += W u
+      FRACSSM_WAIT(full + 4, n);
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 1u);
         umma::mma_commit(barH);
       }
-      // publish the outgoing state: the workers' stores are ordered before their arrivals on
-      // out_bar, this release makes them visible to the CTA that takes the next tile of the row
-      FRACSSM_WAIT(out_bar, n);
-      if (lane == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
       __syncwarp();
       item = next;
     }
@@ -474,29 +476,99 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             cl[hf] = __fadd2_rn(chat, make_float2(-ch[hf].x, -ch[hf].y));
             const float2 full_k = __fmul2_rn(ks[i][hf], f[hf]);
             kh[hf] = bf16_round2(full_k);
-            ks[i][hf] = __fadd2_rn(full_k, make_float2(-kh[hf].x, -kh[hf].y));  // low part, next batch
+            ks[i][hf] = __fadd2_rn(full_k, make_float2(-kh[hf].x, -kh[hf].y));  // low part
           }
           emit_row(sArea0, th_off, c16, i, ch[0], ch[1]);
           emit_row(sArea1, th_off, c16, i, cl[0], cl[1]);
           emit_row(sArea0 + kTileBytes, th_off, c16, i, kh[0], kh[1]);
+          emit_row(sArea1 + kTileBytes, th_off, c16, i, ks[i][0], ks[i][1]);
         }
       }
       warp_arrive(full + 3, lane);
       FRACSSM_MARK(5)
 
-      // ---- Khat (low) -> area1 tile 1, W -> the Chat-low slot (after every level MMA has completed)
-      FRACSSM_WAIT(cb + 2, n);
-      umma::tc_fence_after();
-      FRACSSM_MARK(6)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) emit_row(sArea1 + kTileBytes, th_off, c16, i, ks[i][0], ks[i][1]);
-
       // the next item (published by the control warp at the start of this tile); it must be read
-      // here, before this warp's arrival lets the control warp move on and publish again
+      // here, before this warp's arrival on out_bar lets the control warp move on and publish again
       FRACSSM_WAIT(item_bar, n + 1);
       const int next = items[(n + 1) & 1];
       FRACSSM_MARK(7)
 
+      // ---- the chain first: incoming state -> outgoing state, published for the next tile of the row
+      FRACSSM_WAIT(state_bar, n);
+      umma::named_barrier(2, kWorkers);  // also orders warp 0's write of gt_s before its readers
+      FRACSSM_MARK(9)
+      const int m_row = 32 * Q + lane;
+      float sj[16];
+      {
+        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
+        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
+                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
+        if (j > 0) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float4 v = __ldcg(sp + x * kM);
+            sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
+          }
+        } else if (a.init) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
+        }
+      }
+      FRACSSM_WAIT(cb + 3, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
+      umma::tc_fence_after();
+      FRACSSM_MARK(11)
+      {
+        // S_next = Gt * S + Sacc
+        float acc[16];
+        umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
+        umma::tmem_ld_wait();
+        const float gt = gt_s[m_row];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) acc[x] = fmaf(gt, sj[x], acc[x]);
+        float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
+        if (j + 1 < a.ntiles) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x)
+            __stcg(sp + x * kM, make_float4(acc[4 * x], acc[4 * x + 1], acc[4 * x + 2], acc[4 * x + 3]));
+        } else if (a.fin) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, acc[x]);
+        }
+      }
+      umma::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
+      FRACSSM_MARK(12)
+
+      // ---- every level MMA has completed: the state slot and the W slot are free
+      FRACSSM_WAIT(cb + 2, n);
+      umma::tc_fence_after();
+      FRACSSM_MARK(6)
+      // incoming state as MMA operands, bf16 high / low parts
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float hi[8], lo[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
+          lo[x] = sj[8 * half + x] - hi[x];
+        }
+        uint4 pk, pl;
+        pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
+        pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
+        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+        *reinterpret_cast<uint4 *>(s_tile + off) = pk;
+        *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
+      }
+      warp_arrive(full + 5, lane);
+      FRACSSM_MARK(10)
+
+      // ---- W -> the Chat-low slot
       {
         uint8_t *wt = chat_lo;
         const int t = 32 * Q + lane;
@@ -536,76 +608,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
       warp_arrive(full + 4, lane);
       FRACSSM_MARK(8)
-
-      // ---- incoming state: float32 copy in registers, bf16 high / low copies as MMA operands
-      FRACSSM_WAIT(state_bar, n);
-      umma::named_barrier(2, kWorkers);  // also orders warp 0's write of gt_s before its readers
-      FRACSSM_MARK(9)
-      const int m_row = 32 * Q + lane;
-      float sj[16];
-      {
-        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
-        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
-                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (j > 0) {
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const float4 v = __ldcg(sp + x * kM);
-            sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
-          }
-        } else if (a.init) {
-#pragma unroll
-          for (int x = 0; x < 16; ++x)
-            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
-        } else {
-#pragma unroll
-          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
-        }
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float hi[8], lo[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
-            lo[x] = sj[8 * half + x] - hi[x];
-          }
-          uint4 pk, pl;
-          pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
-          pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
-          const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-          *reinterpret_cast<uint4 *>(s_tile + off) = pk;
-          *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
-        }
-      }
-      warp_arrive(full + 5, lane);
-      FRACSSM_MARK(10)
-
-      // ---- outgoing state: S_next = Gt * S + Sacc, published for the next tile of this row
-      FRACSSM_WAIT(cb + 3, n);  // Khat(high) MMAs
-      FRACSSM_WAIT(cb + 4, n);  // Khat(low) MMAs
-      umma::tc_fence_after();
-      FRACSSM_MARK(11)
-      {
-        float acc[16];
-        umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
-        umma::tmem_ld_wait();
-        const float gt = gt_s[m_row];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) sj[x] = fmaf(gt, sj[x], acc[x]);
-        float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (j + 1 < a.ntiles) {
-#pragma unroll
-          for (int x = 0; x < 4; ++x)
-            __stcg(sp + x * kM, make_float4(sj[4 * x], sj[4 * x + 1], sj[4 * x + 2], sj[4 * x + 3]));
-        } else if (a.fin) {
-#pragma unroll
-          for (int x = 0; x < 16; ++x)
-            st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, sj[x]);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
-      FRACSSM_MARK(12)
 
       // ---- output rows
       FRACSSM_WAIT(barH, n);
