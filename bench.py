@@ -114,7 +114,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 break
-            self._stop.wait(0.01)
+            self._stop.wait(0.005)
 
     def start(self):
         try:
@@ -125,6 +125,9 @@ class ClockSampler:
             h = nv.nvmlDeviceGetHandleByIndex(phys)
             self.mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
             self._nvml = (nv, h)
+            # first queries are slow (lazy set-up inside NVML): make them before the timed region
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
             self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
             self._thread.start()
             return
