@@ -1,7 +1,7 @@
 // Single-pass FRAC scan on sm_100a: every input is read once, the state stays on chip or
 // in L2, all contractions run on tcgen05 with accumulators in tensor memory.
 //
-// Shapes covered: R = 64, M = 128, bf16 u / c / kappa, fp32 rho, dense tensors, any L.
+// Shapes covered: R = 64, M = 128, bf16 u, bf16 or f32 c / kappa, fp32 rho, dense tensors, any L.
 //
 // Work item = (bh, tile of 128 tokens), handed out by an atomic ticket in tile-major order
 // (all bh of tile 0, then tile 1, ...).  The item (bh, j) needs the state left by (bh, j-1);
@@ -33,6 +33,7 @@
 // tile's start / end; Khat is split into bf16 high and low parts so that the state keeps
 // float32-level accuracy.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "tmap.cuh"
@@ -66,7 +67,7 @@ constexpr int kProfCtas = 256, kProfPhases = 16;
 constexpr size_t kCtrlBytes = 256, kProfBytes = kProfCtas * kProfPhases * sizeof(long long);
 
 struct FusedArgs {
-  const __nv_bfloat16 *c, *kappa;
+  const void *c, *kappa;  // bf16 or f32 [BH, L, 128], see the kernel's CKF32 parameter
   const float *rho, *init;
   __nv_bfloat16 *h;
   void *fin;
@@ -130,24 +131,39 @@ __device__ __forceinline__ void st_release(int *p, int v) {
 
 
 // Raw inputs of one item for one worker thread, one group of 4 tokens x 4 modes.
+// c and kappa arrive as bf16 (4 values in a uint2) or as f32 (a float4).
+template <bool CKF32>
 struct RawRegs {
+  using CK = typename std::conditional<CKF32, float4, uint2>::type;
   float4 r[4];
-  uint2 c[4], k[4];
+  CK c[4], k[4];
 };
 
-__device__ __forceinline__ void load_raw(RawRegs &raw, const FusedArgs &a, int item, int w, int lane, int grp) {
+__device__ __forceinline__ float ck_get(const uint2 &v, int q) {
+  const uint32_t wd = (q < 2) ? v.x : v.y;
+  return __uint_as_float((q & 1) ? (wd & 0xFFFF0000u) : (wd << 16));
+}
+__device__ __forceinline__ float ck_get(const float4 &v, int q) {
+  return q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w;
+}
+
+template <bool CKF32>
+__device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a, int item, int w, int lane,
+                                         int grp) {
+  using CK = typename RawRegs<CKF32>::CK;
   const int j = item / a.BH, bh = item - j * a.BH;
   const int t0 = j * kTile + 8 * w + 4 * grp;
   const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
+  const CK *cp = reinterpret_cast<const CK *>(a.c), *kp = reinterpret_cast<const CK *>(a.kappa);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     raw.r[i] = make_float4(1.f, 1.f, 1.f, 1.f);
-    raw.c[i] = make_uint2(0u, 0u);
-    raw.k[i] = make_uint2(0u, 0u);
+    raw.c[i] = CK{};
+    raw.k[i] = CK{};
     if (t0 + i < a.L) {
       raw.r[i] = __ldcs(reinterpret_cast<const float4 *>(a.rho + (tok0 + i) * kM) + lane);
-      raw.c[i] = __ldcs(reinterpret_cast<const uint2 *>(a.c + (tok0 + i) * kM) + lane);
-      raw.k[i] = __ldcs(reinterpret_cast<const uint2 *>(a.kappa + (tok0 + i) * kM) + lane);
+      raw.c[i] = __ldcs(cp + (tok0 + i) * 32 + lane);   // 32 pieces of 4 modes per token row
+      raw.k[i] = __ldcs(kp + (tok0 + i) * 32 + lane);
     }
   }
 }
@@ -161,6 +177,7 @@ __device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
   if (lane == 0) umma::mbar_arrive(bar);
 }
 
+template <bool CKF32>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -254,8 +271,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         const int ntok = min(kTile, a.L - nj * kTile);
         const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
         umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
-        umma::prefetch_l2(a.c + tok * kM, ntok * kM * 2);
-        umma::prefetch_l2(a.kappa + tok * kM, ntok * kM * 2);
+        constexpr int kCkBytes = CKF32 ? 4 : 2;
+        umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
+        umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
       }
       if (n > 0) { FRACSSM_WAIT(barH, n - 1); }  // every MMA of the previous tile has finished
       if (lane == 0) {
@@ -364,13 +382,13 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       float g8[4];
       {
         // the inputs were pulled into L2 a tile ahead; both groups are requested at once
-        RawRegs raw0, raw1;
+        RawRegs<CKF32> raw0, raw1;
         load_raw(raw0, a, item, w, lane, 0);
         load_raw(raw1, a, item, w, lane, 1);
         float ga[4], gb[4];
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
-          const RawRegs &raw = grp ? raw1 : raw0;
+          const RawRegs<CKF32> &raw = grp ? raw1 : raw0;
           float a0[4][4], b0[4][4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -388,10 +406,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             if (grp == 0) ga[q] = p4[3]; else gb[q] = p4[3];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint2 cu = raw.c[i], ku = raw.k[i];
-              const uint32_t cw = (q < 2) ? cu.x : cu.y, kw = (q < 2) ? ku.x : ku.y;
-              const float cf = __uint_as_float((q & 1) ? (cw & 0xFFFF0000u) : (cw << 16));
-              const float kf = __uint_as_float((q & 1) ? (kw & 0xFFFF0000u) : (kw << 16));
+              const float cf = ck_get(raw.c[i], q), kf = ck_get(raw.k[i], q);
               float &cpv = (q & 1) ? cp[4 * grp + i][q >> 1].y : cp[4 * grp + i][q >> 1].x;
               float &ksv = (q & 1) ? ks[4 * grp + i][q >> 1].y : ks[4 * grp + i][q >> 1].x;
               if (grp == 0) {  // base reference point: between token 3 and token 4 of the segment
@@ -654,27 +669,34 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
                       const float *initial_state, void *h, void *final_state, int final_dtype,
                       void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
                       int64_t M, int64_t T, void *stream) {
-  (void)T; (void)ck_dtype;
+  (void)T;
+  const bool ckf32 = ck_dtype == FRACSSM_F32;
   if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
     return fail(FRACSSM_ERR_ARG, "frac_scan: workspace too small");
   // per device, once: opt in to the large dynamic shared memory and remember the SM count
   static std::mutex mu;
   static int sm_count[64] = {};
+  auto prepare = [](const void *kernel) -> int {
+    cudaError_t ae = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
+    cudaFuncAttributes fa{};
+    ae = cudaFuncGetAttributes(&fa, kernel);
+    if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
+    if (fa.numRegs < kLaunchRegsNeeded)
+      return fail(FRACSSM_ERR_UNSUPPORTED,
+                  "frac_scan: the single-pass kernel was built with %d registers per thread, needs %d",
+                  fa.numRegs, kLaunchRegsNeeded);
+    return FRACSSM_OK;
+  };
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
     return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot identify the current device");
   {
     std::lock_guard<std::mutex> lock(mu);
     if (sm_count[dev] == 0) {
-      cudaError_t ae = cudaFuncSetAttribute(scan_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-      if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
-      cudaFuncAttributes fa{};
-      ae = cudaFuncGetAttributes(&fa, scan_fused_kernel);
-      if (ae != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(ae));
-      if (fa.numRegs < kLaunchRegsNeeded)
-        return fail(FRACSSM_ERR_UNSUPPORTED,
-                    "frac_scan: the single-pass kernel was built with %d registers per thread, needs %d",
-                    fa.numRegs, kLaunchRegsNeeded);
+      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true>));
+      if (prc) return prc;
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
       if (n <= 0) return fail(FRACSSM_ERR_CUDA, "frac_scan: cannot query the SM count");
@@ -685,8 +707,8 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
 
   char *ws = reinterpret_cast<char *>(workspace);
   FusedArgs a{};
-  a.c = reinterpret_cast<const __nv_bfloat16 *>(c);
-  a.kappa = reinterpret_cast<const __nv_bfloat16 *>(kappa);
+  a.c = c;
+  a.kappa = kappa;
   a.rho = rho;
   a.init = initial_state;
   a.h = reinterpret_cast<__nv_bfloat16 *>(h);
@@ -706,7 +728,8 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + kProfBytes + align256((size_t)B * 4), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
-  scan_fused_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
+  if (ckf32) scan_fused_kernel<true><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
+  else scan_fused_kernel<false><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
   return check_launch("frac_scan (single-pass kernel)");
 }
 
@@ -716,7 +739,8 @@ extern "C" int fracssm_scan_fused_supported(int64_t B, int64_t L, int64_t R, int
                                             int u_dtype, int ck_dtype) {
   (void)T;
   using namespace fracssm;
-  return B >= 1 && L >= 1 && R == kR && M == kM && u_dtype == FRACSSM_BF16 && ck_dtype == FRACSSM_BF16 &&
+  return B >= 1 && L >= 1 && R == kR && M == kM && u_dtype == FRACSSM_BF16 &&
+         (ck_dtype == FRACSSM_BF16 || ck_dtype == FRACSSM_F32) &&
          B * ceil_div(L, kTile) < (int64_t(1) << 30) && L < (int64_t(1) << 30);
 }
 
