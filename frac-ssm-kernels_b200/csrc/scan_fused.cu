@@ -241,7 +241,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
                      uint32_t idesc, uint32_t acc_first) {
       const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
       const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, b_sbo);
-#pragma unroll 4
+#pragma unroll
       for (uint32_t s = 0; s < 8; ++s) {
         const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
         umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
@@ -371,8 +371,32 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
+    int prev_bh = 0, prev_t0 = 0;
+    // Output rows of tile number n_done (its H accumulator is complete when barH fires).  It runs at
+    // the start of the next tile, after that tile's input loads have been issued, so the loads'
+    // latency is covered by this work.
+    auto write_rows = [&](uint32_t n_done) {
+      FRACSSM_WAIT(barH, n_done);
+      umma::tc_fence_after();
+      FRACSSM_MARK(13)
+      float acc[16];
+      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
+      umma::tmem_ld_wait();
+      const int t = prev_t0 + 32 * Q + lane;
+      if (t < a.L) {
+        uint4 lo, hi;
+        lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
+        hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
+        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
+        __stcs(dst, lo);
+        __stcs(dst + 1, hi);
+      }
+      umma::tc_fence_before();
+      FRACSSM_MARK(14)
+    };
 
-    for (uint32_t n = 0; item < a.total; ++n) {
+    uint32_t n_tiles_done = 0;
+    for (uint32_t n = 0; item < a.total; ++n, ++n_tiles_done) {
       const int j = item / a.BH, bh = item - j * a.BH;
       const int t0 = j * kTile;
 
@@ -385,6 +409,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         RawRegs<CKF32> raw0, raw1;
         load_raw(raw0, a, item, w, lane, 0);
         load_raw(raw1, a, item, w, lane, 1);
+        if (n > 0) write_rows(n - 1);  // the previous tile's output, while the loads are in flight
         float ga[4], gb[4];
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
@@ -624,28 +649,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       warp_arrive(full + 4, lane);
       FRACSSM_MARK(8)
 
-      // ---- output rows
-      FRACSSM_WAIT(barH, n);
-      umma::tc_fence_after();
-      FRACSSM_MARK(13)
-      {
-        float acc[16];
-        umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
-        umma::tmem_ld_wait();
-        const int t = t0 + 32 * Q + lane;
-        if (t < a.L) {
-          uint4 lo, hi;
-          lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
-          hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
-          uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(bh) * a.L + t) * kR + 16 * P);
-          __stcs(dst, lo);
-          __stcs(dst + 1, hi);
-        }
-      }
-      umma::tc_fence_before();
-      FRACSSM_MARK(14)
+      prev_bh = bh;
+      prev_t0 = t0;
       item = next;
     }
+    if (n_tiles_done > 0) write_rows(n_tiles_done - 1);
     if (tid == 0 && a.prof && blockIdx.x < kProfCtas) {
       for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
     }
