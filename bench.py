@@ -424,9 +424,9 @@ def main():
         alg = algorithmic_bytes(BH, L, R, M)
         achieved = alg / (scan_ms * 1e-3) / 1e9
         # DRAM bytes per launch from one ncu capture of the single-pass kernel on a 192 x 1024 case
-        # (dram read 228.0 MB + the 25.2 MB of h it writes), scaled by head-tokens; traffic grows in
+        # (dram read 227.0 MB + the 25.2 MB of h it writes), scaled by head-tokens; traffic grows in
         # proportion to the tiles processed.  Staged path: not captured.
-        traffic = int(253.2e6 / (192 * 1024) * BH * L) if use_fused else None
+        traffic = int(252.2e6 / (192 * 1024) * BH * L) if use_fused else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                     "kernel": "scan_fused_kernel" if use_fused else
@@ -434,7 +434,7 @@ def main():
                     "kernel_ms": scan_ms, "kernel_ms_median": scan_ms_median, "algorithmic_bytes": alg}
         cpu = None
         if not args.no_cpu_baseline:
-            slabs = 8
+            slabs = 32
             v, secs = cpu_baseline_sample(slabs)
             cpu = {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                    "sample": f"{slabs} of {BH} (batch, head) rows of the workload, {secs:.1f} s, "
