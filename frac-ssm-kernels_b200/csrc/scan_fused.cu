@@ -37,19 +37,19 @@
 
 #include "common.cuh"
 #include "tmap.cuh"
+#include "scan_tile.cuh"
 #include "umma.cuh"
 
 namespace fracssm {
 namespace {
 
-constexpr int kTile = 128, kR = 64, kM = 128, kWorkers = 512, kThreads = 640;
+using namespace tile;
+constexpr int kWorkers = 512, kThreads = 640;
 // Registers are re-divided after launch (setmaxnreg): the 16 worker warps grow to kWorkerRegs,
 // the control warp's group of four shrinks to kControlRegs.  The launch allocation per thread
 // (checked on the host) must cover both, or the growing warps would wait forever.
 constexpr int kWorkerRegs = 112, kControlRegs = 32;
 constexpr int kLaunchRegsNeeded = (kWorkers * kWorkerRegs + (kThreads - kWorkers) * kControlRegs + kThreads - 1) / kThreads;
-constexpr uint32_t kTileBytes = 32768;  // [128 x 128] bf16 operand tile
-constexpr uint32_t kAtom = 16384;       // one 64-column block of such a tile
 // shared memory map (bytes from the 1024-aligned base)
 constexpr uint32_t kOffArea0 = 0, kOffArea1 = 65536;
 constexpr uint32_t kOffChatLo = 131072;                  // low part of Chat, one operand tile
@@ -62,7 +62,6 @@ constexpr uint32_t kSmemBytes = kOffMisc + 192 + 128 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
 constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
                    kColL64 = 448;
-constexpr uint64_t kWaitNs = 2000000000ull;  // limit of every device-side wait
 constexpr int kProfCtas = 256, kProfPhases = 16;
 constexpr size_t kCtrlBytes = 256, kProfBytes = kProfCtas * kProfPhases * sizeof(long long);
 
@@ -79,57 +78,6 @@ struct FusedArgs {
   int BH, L, ntiles, total;
 };
 
-__device__ __forceinline__ void emit4(uint8_t *tile, int row, int lane, const float (&v)[4]) {
-  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-  uint2 pk;
-  pk.x = *reinterpret_cast<const uint32_t *>(&a);
-  pk.y = *reinterpret_cast<const uint32_t *>(&b);
-  const uint32_t off = (lane >> 4) * kAtom + row * 128 +
-                       (((((lane & 15) >> 1) ^ (row & 7)) << 4) | ((lane & 1) << 3));
-  *reinterpret_cast<uint2 *>(tile + off) = pk;
-}
-
-// Product of the segment decays seg[lo..hi) for this lane's four modes (as two packed pairs).
-__device__ __forceinline__ void seg_prod(const float *seg, int lo, int hi, int lane, float2 (&out)[2]) {
-  out[0] = out[1] = make_float2(1.f, 1.f);
-  for (int s = lo; s < hi; ++s) {
-    const float4 g = *reinterpret_cast<const float4 *>(seg + s * kM + 4 * lane);
-    out[0] = __fmul2_rn(out[0], make_float2(g.x, g.y));
-    out[1] = __fmul2_rn(out[1], make_float2(g.z, g.w));
-  }
-}
-
-// Store four consecutive modes of token row 8*w + i of an operand tile (32-bit shared address).
-// th_off = this thread's fixed part of the swizzled offset, c16 = its 16-byte chunk index << 4.
-__device__ __forceinline__ void emit_row(uint32_t tile_s, uint32_t th_off, uint32_t c16, int i, float2 v0,
-                                         float2 v1) {
-  const __nv_bfloat162 a = __floats2bfloat162_rn(v0.x, v0.y), b = __floats2bfloat162_rn(v1.x, v1.y);
-  const uint32_t addr = tile_s + th_off + i * 128 + (c16 ^ (static_cast<uint32_t>(i) << 4));
-  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(*reinterpret_cast<const uint32_t *>(&a)),
-               "r"(*reinterpret_cast<const uint32_t *>(&b))
-               : "memory");
-}
-__device__ __forceinline__ float2 bf16_round2(float2 v) {  // each component rounded to bf16, as floats
-  const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
-  const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
-  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
-}
-
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t *>(&t);
-}
-
-__device__ __forceinline__ int ld_acquire(const int *p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release(int *p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-
 // Raw inputs of one item for one worker thread, one group of 4 tokens x 4 modes.
 // c and kappa arrive as bf16 (4 values in a uint2) or as f32 (a float4).
 template <bool CKF32>
@@ -138,14 +86,6 @@ struct RawRegs {
   float4 r[4];
   CK c[4], k[4];
 };
-
-__device__ __forceinline__ float ck_get(const uint2 &v, int q) {
-  const uint32_t wd = (q < 2) ? v.x : v.y;
-  return __uint_as_float((q & 1) ? (wd & 0xFFFF0000u) : (wd << 16));
-}
-__device__ __forceinline__ float ck_get(const float4 &v, int q) {
-  return q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w;
-}
 
 template <bool CKF32>
 __device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a, int item, int w, int lane,
@@ -166,15 +106,6 @@ __device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a
       raw.k[i] = __ldcs(kp + (tok0 + i) * 32 + lane);
     }
   }
-}
-
-// One arrival per warp on a "full" barrier: every lane's shared-memory writes are fenced for
-// the async proxy and its TMEM reads are ordered before the control warp's next MMAs.
-__device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
-  umma::fence_async_smem();
-  umma::tc_fence_before();
-  __syncwarp();
-  if (lane == 0) umma::mbar_arrive(bar);
 }
 
 template <bool CKF32>

@@ -42,12 +42,32 @@ class CudaStageOps:
 
     @staticmethod
     def segment_summary(u, kappa, rho, chunk_size):
-        """(log-decay total [B, M], final state from a zero state [B, R, M]) of a segment."""
+        """(decay product [B, M], final state from a zero state [B, R, M]) of a segment, float32.
+
+        One kernel that reads u, kappa and rho once when the shape is covered (R = 64, M = 128,
+        bfloat16 u, dense); otherwise the staged kernels (cumsum -> chunk_state -> state_passing).
+        """
+        from . import _cabi as C
+        B, L, R = u.shape
+        M = kappa.shape[-1]
+        if (R == 64 and M == 128 and u.dtype == torch.bfloat16 and L > 0 and B > 0
+                and kappa.dtype in (torch.bfloat16, torch.float32)):
+            u, kappa, rho = u.contiguous(), kappa.contiguous(), rho.contiguous()
+            fin = torch.empty(B, R, M, device=u.device, dtype=torch.float32)
+            decay = torch.empty(B, M, device=u.device, dtype=torch.float32)
+            lib = C.lib()
+            with torch.cuda.device(u.device):
+                ws = torch.empty(lib.fracssm_segment_summary_workspace_bytes(B, R, M), device=u.device,
+                                 dtype=torch.uint8)
+                C.check(lib.fracssm_segment_summary(
+                    C.ptr(u), C.ptr(kappa), C.dt(kappa), C.ptr(rho), None, C.ptr(fin), C.ptr(decay),
+                    C.ptr(ws), ws.numel(), B, L, R, M, C.stream_of(u)), "segment_summary")
+            return decay, fin
         from .ops.b200 import stages
         lcr, cd = stages._cumsum(rho, chunk_size, True)
         states = stages.chunk_state(u, kappa, lcr, chunk_size, state_fp32=True)
         _, fin = stages._state_passing(states, cd, None, torch.float32, torch.float32)
-        return cd.sum(dim=1), fin
+        return torch.exp(cd.sum(dim=1)), fin
 
     @staticmethod
     def scan(u, c, kappa, rho, chunk_size, initial_state):
@@ -56,28 +76,44 @@ class CudaStageOps:
                          final_state_dtype=torch.float32)
 
 
-def incoming_state(log_decay_all, final_all, rank, initial_state=None):
+def incoming_state(decay_all, final_all, rank, initial_state=None):
     """State entering segment `rank`, from the gathered summaries of all segments.
 
-    log_decay_all [G, B, M], final_all [G, B, R, M]; segment g maps S -> exp(D_g) (.) S + F_g.
+    decay_all [G, B, M], final_all [G, B, R, M]; segment g maps S -> decay_g (.) S + final_g.
     """
     G = final_all.shape[0]
-    if log_decay_all.shape[0] != G:
+    if decay_all.shape[0] != G:
         raise ValueError("segment summaries disagree on the number of segments")
     state = torch.zeros_like(final_all[0]) if initial_state is None else initial_state.to(final_all.dtype)
     for g in range(rank):
-        state = torch.exp(log_decay_all[g])[:, None, :] * state + final_all[g]
+        state = decay_all[g][:, None, :] * state + final_all[g]
     return state
 
 
+def _auto_local_splits(B, L_local, chunk_size, world):
+    """How many sub-segments to cut this rank's segment into.  The scan kernels hand the state from
+    tile to tile of a row, so few rows mean few independent chains; sub-segments are extra rows.
+    Splitting costs one more read of u, kappa and rho, so a single rank does not split."""
+    if world == 1:
+        return 1
+    s = 1
+    while B * s < 148 and L_local % (2 * s * chunk_size) == 0 and L_local // (2 * s) >= 1024:
+        s *= 2
+    return s
+
+
 def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False,
-                      group=None, ops=None):
+                      group=None, ops=None, local_splits=None):
     """Scan a sequence whose tokens are split across the ranks of `group` (in rank order).
 
     Every rank passes ITS segment (`[B, L_local, ...]`; all segments but the last must be a
     multiple of `chunk_size` long) and the same `initial_state` (the state before token 0 of
     the whole sequence, or None).  Returns this rank's `h` and, if requested, the final state of
     the WHOLE sequence (broadcast from the last rank).
+
+    `local_splits` (a divisor of L_local / chunk_size, the same on every rank; default chosen from
+    the row count) cuts each rank's segment into that many sub-segments which are scanned as extra
+    rows: with few (batch x head) rows this is what keeps all SMs busy.
     """
     ops = CudaStageOps if ops is None else ops
     world = dist.get_world_size(group)
@@ -87,24 +123,46 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     if rank < world - 1 and L_local % chunk_size != 0:
         raise ValueError(
             f"segment of rank {rank} has {L_local} tokens, not a multiple of chunk_size {chunk_size}")
-    if world == 1:
+    S = _auto_local_splits(B, L_local, chunk_size, world) if local_splits is None else int(local_splits)
+    if S < 1 or L_local % S != 0 or (S > 1 and (L_local // S) % chunk_size != 0):
+        raise ValueError(f"local_splits={S} does not cut {L_local} tokens into whole chunks")
+    if world == 1 and S == 1:
         h, fin = ops.scan(u, c, kappa, rho, chunk_size, initial_state)
         return (h, fin) if return_final_state else h
 
-    log_decay, fin0 = ops.segment_summary(u, kappa, rho, chunk_size)
-    packed = torch.cat([fin0.reshape(B, R * M), log_decay.reshape(B, M)], dim=1).float().contiguous()
-    gathered = torch.empty(world * B, R * M + M, dtype=packed.dtype, device=packed.device)
-    dist.all_gather_into_tensor(gathered, packed, group=group)   # rank-major concatenation on dim 0
-    gathered = gathered.view(world, B, R * M + M)
-    final_all = gathered[:, :, : R * M].reshape(world, B, R, M)
-    decay_all = gathered[:, :, R * M:]
-    init = incoming_state(decay_all, final_all, rank, initial_state)
-    h, fin = ops.scan(u, c, kappa, rho, chunk_size, init)
+    Ls = L_local // S
+    rows = lambda t: t.contiguous().view(B * S, Ls, t.shape[-1])   # (b, s) becomes the row index
+    u_r, c_r, k_r, rho_r = rows(u), rows(c), rows(kappa), rows(rho)
+    decay, fin0 = ops.segment_summary(u_r, k_r, rho_r, chunk_size)
+    packed = torch.cat([fin0.reshape(B, S, R * M), decay.reshape(B, S, M)], dim=2).float().contiguous()
+    if world > 1:
+        gathered = torch.empty(world * B, S, R * M + M, dtype=packed.dtype, device=packed.device)
+        dist.all_gather_into_tensor(gathered, packed, group=group)   # rank-major concatenation on dim 0
+        gathered = gathered.view(world, B, S, R * M + M)
+    else:
+        gathered = packed[None]
+    # virtual segments in sequence order: (rank 0, sub 0), (rank 0, sub 1), ... ; walk them once and
+    # keep the states entering this rank's sub-segments
+    state = (torch.zeros(B, R, M, dtype=torch.float32, device=u.device) if initial_state is None
+             else initial_state.float().clone())
+    mine = torch.empty(B, S, R, M, dtype=torch.float32, device=u.device)
+    for g in range(rank + 1):
+        for sub in range(S):
+            if g == rank:
+                mine[:, sub] = state
+                if sub == S - 1:
+                    break
+            seg_fin = gathered[g, :, sub, : R * M].reshape(B, R, M)
+            seg_dec = gathered[g, :, sub, R * M:]
+            state = torch.addcmul(seg_fin, seg_dec[:, None, :], state)
+    h, fin = ops.scan(u_r, c_r, k_r, rho_r, chunk_size, mine.view(B * S, R, M))
+    h = h.view(B, L_local, R)
     if not return_final_state:
         return h
-    fin = fin.float().contiguous()
-    last = dist.get_global_rank(group, world - 1) if group is not None else world - 1
-    dist.broadcast(fin, src=last, group=group)
+    fin = fin.view(B, S, R, M)[:, S - 1].float().contiguous()
+    if world > 1:
+        last = dist.get_global_rank(group, world - 1) if group is not None else world - 1
+        dist.broadcast(fin, src=last, group=group)
     return h, fin
 
 

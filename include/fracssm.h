@@ -149,6 +149,21 @@ int fracssm_frac_scan_fwd_noalloc(const void *u, const void *c, const void *kapp
                                   void *stream);
 
 /*
+ * Segment summary for sequence sharding: for a segment of L tokens per row, the state it leaves
+ * from `initial_state` (or zero) and the product of its decays, so that it acts on any incoming
+ * state S as S -> decay (.) S + final_state.  u bf16 [B,L,64]; kappa bf16 or f32 [B,L,128]; rho f32;
+ * final_state f32 [B,64,128]; decay f32 [B,128]; dense tensors; workspace of
+ * fracssm_segment_summary_workspace_bytes bytes, 256-byte aligned.  Reads u, kappa, rho once.
+ * New with respect to the reference (it has no sequence parallelism); the composition rule is the
+ * segment summary of frac_ssm/ops/cute/state_passing.py:144-199.
+ */
+size_t fracssm_segment_summary_workspace_bytes(int64_t B, int64_t R, int64_t M);
+int fracssm_segment_summary(const void *u, const void *kappa, int k_dtype, const float *rho,
+                            const float *initial_state, float *final_state, float *decay,
+                            void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                            int64_t M, void *stream);
+
+/*
  * Reads back the error word of the last single-pass launch that used `workspace` (this call
  * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
  * (for a predecessor tile's state, a TMA load or an MMA) ran out and the results are invalid.

@@ -35,6 +35,22 @@ def test_segment_summaries_compose_on_one_gpu():
     close(fin, f_ref, **TOL_F32)
 
 
+@pytest.mark.parametrize("kdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,L", [(3, 1000), (24, 4096), (200, 129), (1, 128)])
+def test_segment_summary_kernel(kdtype, B, L):
+    """The one-pass summary kernel against the oracle: final state from a zero state, decay product."""
+    from frac_ssm_b200 import parallel
+    u, c, kappa, rho, _ = O.scan_inputs(B, L, 64, 128, gen="model_like", seed=B + L)
+    kappa = kappa.to(kdtype)
+    decay, fin = parallel.CudaStageOps.segment_summary(u.cuda(), kappa.cuda(), rho.cuda(), 256)
+    torch.cuda.synchronize()
+    lcr, cd = O.chunk_cumsum(O.log_decay(rho, True), 256, True)
+    st = O.chunk_state(u.float(), kappa.float(), lcr, 256, exact=True)
+    _, f_ref = O.state_passing(st, cd, None, exact=True)
+    close(fin, f_ref, **TOL_F32)
+    close(decay, torch.exp(cd.double().sum(1)).float(), **TOL_F32)
+
+
 def _nccl_worker(rank, world, port, out):
     import torch.distributed as dist
     from frac_ssm_b200 import parallel
