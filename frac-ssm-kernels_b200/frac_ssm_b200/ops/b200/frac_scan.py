@@ -6,6 +6,8 @@ Backend-module interface of the reference (`frac_ssm/ops/triton/frac_scan.py:102
 
 from __future__ import annotations
 
+from typing import Optional, Tuple
+
 import torch
 
 from ... import _cabi as C
@@ -74,15 +76,31 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
         final_state_dtype = torch.bfloat16 if u.dtype == torch.bfloat16 else torch.float32
     assert final_state_dtype in (torch.float32, torch.bfloat16)
 
+    path_code = _PATHS[path]
+    if check or keep_workspace:      # diagnostics bypass the registered op (they need the scratch)
+        h, fin = _launch(u, c, kappa, rho, chunk_size, initial_state, return_final_state,
+                         final_state_dtype == torch.float32, path_code, check, keep_workspace)
+    else:
+        h, fin = _frac_scan_fwd_op(u, c, kappa, rho, chunk_size, initial_state, return_final_state,
+                                   final_state_dtype == torch.float32, path_code)
+    if return_final_state:
+        return h, fin
+    return h
+
+
+def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code, check=False,
+            keep_workspace=False):
+    B, L, R = u.shape
+    M = c.shape[-1]
+    final_state_dtype = torch.float32 if final_fp32 else torch.bfloat16
     u, c, kappa, rho = C.rows(u), C.rows(c), C.rows(kappa), C.rows(rho)
     init = None if initial_state is None else initial_state.contiguous()
     h = torch.empty(B, L, R, device=u.device, dtype=u.dtype)
-    fin = torch.empty(B, R, M, device=u.device, dtype=final_state_dtype) if return_final_state else None
+    fin = torch.empty(B, R, M, device=u.device, dtype=final_state_dtype) if want_final else None
     if B > 0:
         lib = C.lib()
-        p = _PATHS[path]
         with torch.cuda.device(u.device):
-            nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, p)
+            nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, path_code)
             ws = torch.empty(max(nbytes, 256), device=u.device, dtype=torch.uint8)
             if keep_workspace:
                 global _last_ws
@@ -91,13 +109,39 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
                 C.ptr(u), C.dt(u), u.stride(0), u.stride(1), C.ptr(c), C.ptr(kappa), C.dt(c),
                 c.stride(0), c.stride(1), kappa.stride(0), kappa.stride(1), C.ptr(rho), rho.stride(0),
                 rho.stride(1), C.ptr(init), C.ptr(h), C.ptr(fin), C.dt_of(final_state_dtype),
-                C.ptr(ws), ws.numel(), B, L, R, M, chunk_size, p, C.stream_of(u)), "frac_scan")
-            if check and L > 0 and p != C.PATH_STAGED and u.is_contiguous() and lib.fracssm_scan_fused_supported(
-                    B, L, R, M, chunk_size, C.dt(u), C.dt(c)):
+                C.ptr(ws), ws.numel(), B, L, R, M, chunk_size, path_code, C.stream_of(u)), "frac_scan")
+            if check and L > 0 and path_code != C.PATH_STAGED and u.is_contiguous() and \
+                    lib.fracssm_scan_fused_supported(B, L, R, M, chunk_size, C.dt(u), C.dt(c)):
                 C.check(lib.fracssm_scan_fused_status(C.ptr(ws), C.stream_of(u)), "frac_scan")
-    if return_final_state:
-        return h, fin
-    return h
+    if fin is None:
+        fin = torch.empty(0, device=u.device, dtype=final_state_dtype)
+    return h, fin
+
+
+# Registered as a torch custom op (with a shape-only "fake" implementation) so that callers can put
+# the scan inside torch.compile(fullgraph=True), as the reference does for its ops
+# (frac_ssm/ops/triton/chunk_state.py:243-302).  Forward only: asking for gradients raises.
+@torch.library.custom_op("frac_ssm_b200::frac_scan_fwd", mutates_args=())
+def _frac_scan_fwd_op(u: torch.Tensor, c: torch.Tensor, kappa: torch.Tensor, rho: torch.Tensor,
+                      chunk_size: int, initial_state: Optional[torch.Tensor], want_final: bool,
+                      final_fp32: bool, path_code: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    return _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code)
+
+
+@_frac_scan_fwd_op.register_fake
+def _(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code):
+    B, L, R = u.shape
+    M = c.shape[-1]
+    fdt = torch.float32 if final_fp32 else torch.bfloat16
+    fin = torch.empty((B, R, M) if want_final else (0,), device=u.device, dtype=fdt)
+    return torch.empty(B, L, R, device=u.device, dtype=u.dtype), fin
+
+
+def _no_backward(ctx, *grads):
+    raise NotImplementedError("frac_ssm_b200 implements the forward pass only")
+
+
+_frac_scan_fwd_op.register_autograd(_no_backward)
 
 
 __all__ = ["frac_scan"]

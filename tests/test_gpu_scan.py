@@ -220,3 +220,21 @@ def test_fused_adversarial_decay(scan):
     rho[:, 40:400, 64:96] = 1.0
     rho[:, ::3, 96:] = 1e-6
     _check(scan, u, c, kappa, rho, 256, None, "fused")
+
+
+def test_scan_inside_torch_compile_fullgraph(scan):
+    """The scan is a registered custom op with a shape-only implementation, so a caller can compile
+    a graph around it (the reference checks the same for its ops)."""
+    u, c, kappa, rho, init = cuda(*O.scan_inputs(2, 512, 64, 128, gen="model_like", seed=17))
+
+    def fn(u, c, kappa, rho, init):
+        h, fin = scan(u * 1.0, c, kappa, rho, 256, init, True, final_state_dtype=torch.float32)
+        return h.float() * 2.0, fin + 1.0
+
+    eager = fn(u, c, kappa, rho, init)
+    compiled = torch.compile(fn, fullgraph=True)(u, c, kappa, rho, init)
+    torch.testing.assert_close(compiled[0], eager[0])
+    torch.testing.assert_close(compiled[1], eager[1])
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        ug = u.float().requires_grad_()          # forward only: gradients are refused
+        scan(ug, c.float(), kappa.float(), rho, 256).sum().backward()
