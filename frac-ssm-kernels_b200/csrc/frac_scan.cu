@@ -86,9 +86,13 @@ extern "C" int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, i
 
   const bool dense = u_sl == R && u_sb == L * R && c_sl == M && c_sb == L * M && k_sl == M &&
                      k_sb == L * M && r_sl == M && r_sb == L * M;
-  const bool fused_ok = dense && fracssm_scan_fused_supported(B, L, R, M, T, u_dtype, ck_dtype);
+  // the single-pass kernel moves its inputs with bulk copies and 16-byte accesses
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(c) |
+                           reinterpret_cast<uintptr_t>(kappa) | reinterpret_cast<uintptr_t>(rho) |
+                           reinterpret_cast<uintptr_t>(h)) & 15) == 0;
+  const bool fused_ok = dense && aligned16 && fracssm_scan_fused_supported(B, L, R, M, T, u_dtype, ck_dtype);
   if (path == 2 && !fused_ok)
-    return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan: shape, dtype or strides not covered by the single-pass kernel");
+    return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan: shape, dtype, strides or alignment not covered by the single-pass kernel");
   if (fused_ok && path != 1) {
     if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
       return fail(FRACSSM_ERR_ARG, "frac_scan: workspace too small");

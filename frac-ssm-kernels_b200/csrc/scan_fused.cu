@@ -147,15 +147,17 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   umma::tc_fence_after();
   const uint32_t tmem = *tmem_s;
   bool ok = true;  // cleared when a bounded wait runs out; later waits are then skipped
-#define FRACSSM_WAIT(bar, parity) \
-  if (ok) ok = umma::mbar_wait_parked(bar, (parity) & 1u, kWaitNs)
-
+  // Bounded waits.  The control warp polls (it is one warp and every hand-over of the tile passes
+  // through it: a parked wait wakes up several hundred cycles after the barrier completes); the 16
+  // worker warps park, which leaves the issue slots to the warps that have work.
   // (each setmaxnreg sits inside its role's branch: the register limit must not merge across roles)
   if (w > 16) {
     // spare warps of the control warp's register group: give the registers back, nothing else
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
   } else if (w == 16) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+#define FRACSSM_WAIT(bar, parity) \
+  if (ok) ok = umma::mbar_wait(bar, (parity) & 1u, kWaitNs)
     // =========================== control warp ===========================
     const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
     const uint32_t sS = umma::smem_u32(s_tile), sSlo = umma::smem_u32(slo_tile), sU = umma::smem_u32(u_tile);
@@ -283,6 +285,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     }
   } else {
     // =========================== worker warps ===========================
+#undef FRACSSM_WAIT
+#define FRACSSM_WAIT(bar, parity) \
+  if (ok) ok = umma::mbar_wait_parked(bar, (parity) & 1u, kWaitNs)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
     const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
     // operand-tile addressing of this thread: rows 8w..8w+7, modes 4*lane..4*lane+3

@@ -12,6 +12,7 @@ struct SelfTestArgs {
   float *D;             // [128][N]
   int *status;          // device word: 0 ok, 1 = MMA wait timed out
   int a_mn, b_mn, N, b_group0, b_sbo, b_tma;
+  int m_rows;           // 128, or 64 (then D holds all 128 TMEM lanes as they are)
 };
 
 __global__ void __launch_bounds__(128)
@@ -48,7 +49,7 @@ umma_selftest_kernel(const SelfTestArgs a, const __grid_constant__ CUtensorMap b
       umma::tma_load_3d(tileB, &b_map, &bar_tma, 0, 0, 0);
       ok = umma::mbar_wait(&bar_tma, 0, 1000000000ull);
     }
-    const uint32_t idesc = umma::make_idesc(128, a.N, a.a_mn != 0, a.b_mn != 0);
+    const uint32_t idesc = umma::make_idesc(a.m_rows, a.N, a.a_mn != 0, a.b_mn != 0);
     const uint32_t sa = umma::smem_u32(tileA), sb = umma::smem_u32(tileB);
     for (int ks = 0; ks < 8; ++ks) {
       const uint64_t da = a.a_mn ? umma::make_sdesc(sa + ks * 2048, 16384, 1024)
@@ -91,7 +92,7 @@ extern "C" int fracssm_selftest_umma(const float *A, const float *B, const void 
                       (int64_t)b_row_group0 * 1024 + (int64_t)(N / 8 - 1) * b_sbo_bytes + 1024 > 16384))
     return fail(FRACSSM_ERR_ARG, "selftest_umma: B row groups leave the tile");
   if (b_via_tma && (!b_mn_major || !B_bf16)) return fail(FRACSSM_ERR_ARG, "selftest_umma: TMA path loads the MN-major B");
-  SelfTestArgs a{A, B, D, status, a_mn_major, b_mn_major, N, b_row_group0, b_sbo_bytes, b_via_tma};
+  SelfTestArgs a{A, B, D, status, a_mn_major, b_mn_major, N, b_row_group0, b_sbo_bytes, b_via_tma, 128};
   CUtensorMap map{};
   if (b_via_tma) {
     int rc = make_tmap_bf16_3d(&map, B_bf16, 64, 128, 1, 64, 128);
@@ -102,4 +103,21 @@ extern "C" int fracssm_selftest_umma(const float *A, const float *B, const void 
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "selftest_umma: %s", cudaGetErrorString(e));
   umma_selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(a, map);
   return check_launch("selftest_umma");
+}
+
+// Diagnostic: the same tile with a 64-row MMA (A rows 0..63).  D [128][N] receives all 128 tensor-
+// memory lanes as they are after the MMA (lanes the MMA does not write keep what they held), which
+// shows where the hardware puts the 64 result rows.  No counterpart in the reference.
+extern "C" int fracssm_selftest_umma_m64(const float *A, const float *B, float *D, int *status, int N,
+                                         void *stream) {
+  using namespace fracssm;
+  if (!A || !B || !D || !status) return fail(FRACSSM_ERR_ARG, "selftest_umma_m64: null pointer");
+  if (N < 8 || N > 128 || N % 8) return fail(FRACSSM_ERR_ARG, "selftest_umma_m64: N must be a multiple of 8 in 8..128");
+  SelfTestArgs a{A, B, D, status, 0, 0, N, 0, 1024, 0, 64};
+  CUtensorMap map{};
+  const int smem = 65536 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "selftest_umma_m64: %s", cudaGetErrorString(e));
+  umma_selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(a, map);
+  return check_launch("selftest_umma_m64");
 }

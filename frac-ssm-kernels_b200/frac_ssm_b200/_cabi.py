@@ -49,6 +49,7 @@ _SIGNATURES = {
                                     vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "fracssm_skip_mix": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, vp, ci, i64, i64, i64, i64, vp]),
     "fracssm_rmsnorm_gated": (ci, [vp, i64, vp, i64, ci, vp, ci, cf, vp, vp, i64, i64, vp]),
+    "fracssm_selftest_umma_m64": (ci, [vp, vp, vp, vp, ci, vp]),
     "fracssm_selftest_umma": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "fracssm_scan_epilogue": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, vp, ci,
                                    cf, cf, vp, i64, i64, i64, i64, vp]),

@@ -237,6 +237,13 @@ int fracssm_selftest_umma(const float *A, const float *B, const void *B_bf16, fl
                           int a_mn_major, int b_mn_major, int N, int b_row_group0, int b_sbo_bytes,
                           int b_via_tma, void *stream);
 
+/*
+ * Diagnostic: as fracssm_selftest_umma with K-major operands but a 64-row MMA; D [128][N] receives
+ * all 128 tensor-memory lanes, which shows where the 64 result rows land.  No counterpart in the
+ * reference.
+ */
+int fracssm_selftest_umma_m64(const float *A, const float *B, float *D, int *status, int N, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

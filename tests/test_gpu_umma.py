@@ -52,3 +52,22 @@ def test_mn_major_a_and_b():
 def test_mn_major_b_via_tma():
     _run(False, True, 64, tma=True)
     _run(True, True, 64, tma=True, seed=3)
+
+
+def test_64_row_mma_lane_layout():
+    """A 64-row MMA puts result rows 16q..16q+15 into tensor-memory lanes 32q..32q+15."""
+    from frac_ssm_b200 import _cabi as C
+    g = torch.Generator().manual_seed(3)
+    A = torch.randn(128, 128, generator=g).bfloat16().float()
+    B = torch.randn(128, 128, generator=g).bfloat16().float()
+    Ad, Bd = A.cuda(), B.cuda()
+    for N in (64, 16):
+        D = torch.full((128, N), -777.0, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        C.check(C.lib().fracssm_selftest_umma_m64(C.ptr(Ad), C.ptr(Bd), C.ptr(D), C.ptr(status), N,
+                                                  C.stream_of(Ad)), "selftest_umma_m64")
+        torch.cuda.synchronize()
+        assert status.item() == 0, "the MMA completion wait timed out"
+        ref = A[:64] @ B[:N].t()
+        lanes = torch.cat([torch.arange(16) + 32 * q for q in range(4)])
+        torch.testing.assert_close(D.cpu()[lanes], ref, rtol=1e-4, atol=1e-3)
