@@ -141,6 +141,10 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def reset(self):
+        """Forget the samples taken so far (called at the start of the timed region)."""
+        self.sm, self.rows, self.reasons = [], [], set()
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([f.strip() for f in line.split(",")])
@@ -282,7 +286,7 @@ def workload_config(n):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "staged", "fused"])
@@ -293,6 +297,8 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "seq"],
                     help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
                          "tokens x 24 heads split over the ranks (secondary line, not the driver's metric)")
+    ap.add_argument("--step-times", action="store_true",
+                    help="also print every timed step's scan-kernel time to stderr (diagnostic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -349,12 +355,19 @@ def main():
         for _ in range(10):
             step()
         torch.cuda.synchronize()
-    for _ in range(args.warmup):
-        step()
-    barrier()
+    # the sampler starts before the warm-up: its thread's first queries stall kernel launches for
+    # several ms; what it collected so far is dropped when the timed region begins
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+        t_s = time.perf_counter()
+        while len(sampler.sm) + len(sampler.rows) < 2 and time.perf_counter() - t_s < 0.5:
+            step()
+            torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler.reset()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     scan_evs = []
     e0.record()
@@ -372,6 +385,8 @@ def main():
     scan_times = [a.elapsed_time(b) for a, b in scan_evs]
     scan_ms = statistics.mean(scan_times)
     scan_ms_median = statistics.median(scan_times)
+    if args.step_times and rank == 0:
+        print("scan ms per step:", " ".join(f"{t:.3f}" for t in scan_times), file=sys.stderr)
     if dist is not None:
         t = torch.tensor([ms, scan_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

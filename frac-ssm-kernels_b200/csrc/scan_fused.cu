@@ -239,13 +239,17 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         umma::mma_commit(cb + 2);
       }
       // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
+      // the state left by the previous tile of this (batch, head) row is usually there already:
+      // look before the wait for the workers, when this warp has nothing else to do
+      bool early = false;
+      if (lane == 0) {
+        early = j == 0 || ld_acquire(a.flags + bh) >= j;
+        if (early) umma::mbar_arrive(state_bar);
+      }
       FRACSSM_WAIT(full + 3, n);
       FRACSSM_WAIT(barU, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        // the state left by the previous tile of this (batch, head) row: usually there already
-        const bool early = j == 0 || ld_acquire(a.flags + bh) >= j;
-        if (early) umma::mbar_arrive(state_bar);
         piece(kColS, sA0 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
         piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
         umma::mma_commit(cb + 3);
