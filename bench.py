@@ -275,6 +275,88 @@ def run_seq_workload(args, rank, world, dev, dist):
         dist.destroy_process_group()
 
 
+def run_heads_workload(args, rank, world, dev, dist):
+    """Config 4: batch 4, L 16384, 64 heads in 8 groups, R 64, M 128, chunk 256, with the skip-mix and
+    gated-RMSNorm epilogue; the heads are spread over the ranks.  Per step and rank: one scan of its
+    own heads, one [batch, L] float32 all-reduce for the norm, the two epilogue passes."""
+    from frac_ssm_b200 import parallel
+    from frac_ssm_b200.layers import scan_epilogue
+    from frac_ssm_b200.ops.b200.frac_scan import frac_scan
+    batch, L, H, G, R, M, T = 4, 16384, 64, 8, CFG["R"], CFG["M"], CFG["T"]
+    if H % world:
+        raise SystemExit(f"--workload heads: {H} heads do not divide over {world} ranks")
+    hs = parallel.shard_heads(H, rank, world)
+    n = hs.stop - hs.start
+    # layer-level distributions mapped through the reference's prep math (seeded per head, so the
+    # data of a head does not depend on how many ranks there are)
+    log_tau = torch.linspace(0.0, math.log(65536.0), M, device=dev)
+    gg = torch.Generator(device=dev).manual_seed(7)
+    Bt = torch.randn(batch, L, G, M, device=dev, generator=gg)
+    Ct = torch.randn(batch, L, G, M, device=dev, generator=gg)
+    u = torch.empty(batch, n, L, R, device=dev, dtype=torch.bfloat16)
+    c = torch.empty(batch, n, L, M, device=dev, dtype=torch.bfloat16)
+    kappa = torch.empty_like(c)
+    rho = torch.empty(batch, n, L, M, device=dev, dtype=torch.float32)
+    D = torch.empty(n, R, device=dev)
+    for i, head in enumerate(range(hs.start, hs.stop)):
+        gh = torch.Generator(device=dev).manual_seed(1000 + head)
+        u[:, i] = torch.randn(batch, L, R, device=dev, generator=gh).bfloat16()
+        dt = torch.nn.functional.softplus(torch.randn(batch, L, 1, device=dev, generator=gh) - 4.0)
+        lam = torch.exp(torch.rand(1, device=dev, generator=gh) * math.log(16.0))
+        alpha = 0.3 + 0.6 * torch.rand(1, device=dev, generator=gh)
+        D[i] = torch.randn(1, device=dev, generator=gh)
+        grp = head // (H // G)
+        prior = -alpha * log_tau
+        r = torch.exp(-dt * lam ** (1.0 / alpha) / log_tau.exp()).clamp(1e-6, 1 - 1e-6)
+        rho[:, i] = r
+        c[:, i] = torch.softmax(prior + Ct[:, :, grp], -1).bfloat16()
+        kappa[:, i] = ((1 - r) * torch.softmax(prior + Bt[:, :, grp], -1)).bfloat16()
+    del Bt, Ct
+    u, c, kappa, rho = (t.view(batch * n, L, -1) for t in (u, c, kappa, rho))
+    x_conv = u.view(batch, n, L, R).permute(0, 2, 1, 3).reshape(batch, L, n * R).contiguous()
+    z = torch.randn(batch, L, n * R, device=dev, generator=gg).bfloat16()
+    w = torch.ones(n * R, device=dev, dtype=torch.bfloat16)
+
+    def step():
+        h = frac_scan(u, c, kappa, rho, T, None, False)
+        if world == 1:
+            return scan_epilogue(h, x_conv, z, D, w, n, R, 1e-6)
+        return parallel.head_parallel_epilogue(h, x_conv, z, D, w, n, R, H, 1e-6)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        alg = algorithmic_bytes(batch * H, L, R, M)
+        print(json.dumps({"metric": "layer forward tokens/s (scan + skip-mix + gated RMSNorm), heads sharded",
+                          "value": batch * L / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic",
+                          "config": {"workload": "config 4: batch 4, L 16384, 64 heads in 8 groups, R 64, M 128, "
+                                                 "chunk 256, with skip-mix and gated RMSNorm",
+                                     "sharding": f"heads over {world} GPU(s), one all-reduce of "
+                                                 f"{batch * L * 4 // 1024} KB per step for the norm"},
+                          "scan_algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def workload_config(n):
     return {"workload": "config 1: single-layer frac_scan forward + skip-mix/gated-RMSNorm epilogue, "
                         "batch 8 x 24 heads, L 8192, R 64, M 128, chunk 256, per GPU",
@@ -294,9 +376,10 @@ def main():
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
     ap.add_argument("--phases", action="store_true",
                     help="also print the single-pass kernel's per-phase cycle shares (diagnostic)")
-    ap.add_argument("--workload", default="layer", choices=["layer", "seq"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads"],
                     help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
-                         "tokens x 24 heads split over the ranks (secondary line, not the driver's metric)")
+                         "tokens x 24 heads split over the ranks; heads: config 4, one layer's 64 heads spread over the "
+                         "ranks (secondary lines, not the driver's metric)")
     ap.add_argument("--step-times", action="store_true",
                     help="also print every timed step's scan-kernel time to stderr (diagnostic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -329,6 +412,9 @@ def main():
     from frac_ssm_b200.ops.b200 import frac_scan
 
     _cabi.lib()
+    if args.workload == "heads":
+        run_heads_workload(args, rank, world, dev, dist)
+        return
     if args.workload == "seq":
         run_seq_workload(args, rank, world, dev, dist)
         return

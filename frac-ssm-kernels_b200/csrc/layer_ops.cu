@@ -136,6 +136,11 @@ rmsnorm_gated_kernel(const void *__restrict__ x, int64_t x_srow, const void *__r
   }
 }
 
+// Modes of the epilogue kernels.  With the heads of a layer spread over several GPUs the norm spans
+// columns on other GPUs: each GPU first computes its own sum of squares per (b, l) row (partial), the
+// sums are added across GPUs, and a second pass normalises with the total (apply).
+constexpr int kEpilogueFull = 0, kEpiloguePartial = 1, kEpilogueApply = 2;
+
 // One block per (b, l) row of width H*R: un-flatten h, add the D skip, gate, normalise.
 __global__ void __launch_bounds__(256)
 scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t h_sl,
@@ -143,12 +148,12 @@ scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t
                      const void *__restrict__ gate, int64_t g_sb, int64_t g_sl, int dt,
                      const float *__restrict__ Dp, const void *__restrict__ w, int w_dt,
                      float gate_bias, float eps, void *__restrict__ y, int64_t L, int64_t H,
-                     int64_t R) {
+                     int64_t R, int mode, float *__restrict__ sumsq, int64_t norm_width) {
   __shared__ float red[32];
   const int64_t HR = H * R;
   const int64_t row = blockIdx.x, b = row / L, l = row % L;
   float ss = 0.f;
-  for (int64_t j = threadIdx.x; j < HR; j += blockDim.x) {
+  for (int64_t j = threadIdx.x; mode != kEpilogueApply && j < HR; j += blockDim.x) {
     const int64_t hh = j / R, r = j % R;
     float v = ld_f32(h, (b * H + hh) * h_sb + l * h_sl + r, h_dt) +
               ld_f32(x, b * x_sb + l * x_sl + j, dt) * Dp[j];
@@ -156,8 +161,16 @@ scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t
     v *= z * sigmoidf_(z);
     ss = fmaf(v, v, ss);
   }
-  ss = block_sum(ss, red);
-  const float rs = rsqrtf(ss / (float)HR + eps);
+  if (mode == kEpilogueApply) {
+    ss = sumsq[row];
+  } else {
+    ss = block_sum(ss, red);
+    if (mode == kEpiloguePartial) {
+      if (threadIdx.x == 0) sumsq[row] = ss;
+      return;
+    }
+  }
+  const float rs = rsqrtf(ss / (float)norm_width + eps);
   for (int64_t j = threadIdx.x; j < HR; j += blockDim.x) {
     const int64_t hh = j / R, r = j % R;
     float v = ld_f32(h, (b * H + hh) * h_sb + l * h_sl + r, h_dt) +
@@ -185,7 +198,7 @@ scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int
                           const __nv_bfloat16 *__restrict__ gate, int64_t g_sb, int64_t g_sl,
                           const float *__restrict__ Dp, const void *__restrict__ w, int w_dt,
                           float gate_bias, float eps, __nv_bfloat16 *__restrict__ y, int64_t L, int64_t H,
-                          int64_t R) {
+                          int64_t R, int mode, float *__restrict__ sumsq, int64_t norm_width) {
   __shared__ float red[32];
   const int64_t HR = H * R;
   const int64_t row = blockIdx.x, b = row / L, l = row % L;
@@ -208,8 +221,16 @@ scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int
       ss = fmaf(v[i], v[i], ss);
     }
   }
-  ss = block_sum(ss, red);
-  const float rs = rsqrtf(ss / (float)HR + eps);
+  if (mode == kEpilogueApply) {
+    ss = sumsq[row];
+  } else {
+    ss = block_sum(ss, red);
+    if (mode == kEpiloguePartial) {
+      if (threadIdx.x == 0) sumsq[row] = ss;
+      return;
+    }
+  }
+  const float rs = rsqrtf(ss / (float)norm_width + eps);
   if (live) {
     uint32_t o[4];
 #pragma unroll
@@ -288,18 +309,21 @@ extern "C" int fracssm_rmsnorm_gated(const void *x, int64_t x_srow, const void *
   return check_launch("rmsnorm_gated");
 }
 
-extern "C" int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
-                                     const void *x_conv, int64_t x_sb, int64_t x_sl,
-                                     const void *gate, int64_t g_sb, int64_t g_sl, int xg_dtype,
-                                     const float *D, const void *weight, int w_dtype,
-                                     float gate_bias, float eps, void *y, int64_t Bt, int64_t L,
-                                     int64_t H, int64_t R, void *stream) {
-  using namespace fracssm;
-  if (Bt < 0 || L < 0 || H <= 0 || R <= 0) return fail(FRACSSM_ERR_ARG, "scan_epilogue: bad sizes");
-  if (!known_dtype(h_dtype) || !known_dtype(xg_dtype) || !known_dtype(w_dtype))
-    return fail(FRACSSM_ERR_ARG, "scan_epilogue: unsupported dtype");
+namespace fracssm {
+namespace {
+int scan_epilogue_launch(const char *who, const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                         const void *x_conv, int64_t x_sb, int64_t x_sl, const void *gate, int64_t g_sb,
+                         int64_t g_sl, int xg_dtype, const float *D, const void *weight, int w_dtype,
+                         float gate_bias, float eps, void *y, int64_t Bt, int64_t L, int64_t H, int64_t R,
+                         int mode, float *sumsq, int64_t norm_width, void *stream) {
+  if (Bt < 0 || L < 0 || H <= 0 || R <= 0) return fail(FRACSSM_ERR_ARG, "%s: bad sizes", who);
+  if (!known_dtype(h_dtype) || !known_dtype(xg_dtype) || (mode != kEpiloguePartial && !known_dtype(w_dtype)))
+    return fail(FRACSSM_ERR_ARG, "%s: unsupported dtype", who);
+  if (mode != kEpilogueFull && norm_width < H * R) return fail(FRACSSM_ERR_ARG, "%s: norm_width smaller than the local width", who);
   if (Bt == 0 || L == 0) return FRACSSM_OK;
-  if (!h || !x_conv || !gate || !D || !weight || !y) return fail(FRACSSM_ERR_ARG, "scan_epilogue: null pointer");
+  if (!h || !x_conv || !gate || !D) return fail(FRACSSM_ERR_ARG, "%s: null pointer", who);
+  if (mode != kEpiloguePartial && (!weight || !y)) return fail(FRACSSM_ERR_ARG, "%s: null pointer", who);
+  if (mode != kEpilogueFull && !sumsq) return fail(FRACSSM_ERR_ARG, "%s: null pointer", who);
   auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const int64_t HR = H * R;
   if (h_dtype == FRACSSM_BF16 && xg_dtype == FRACSSM_BF16 && R % 8 == 0 && HR <= 8192 && al16(h) && al16(x_conv) &&
@@ -309,11 +333,53 @@ extern "C" int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, i
     scan_epilogue_bf16_kernel<<<(unsigned)(Bt * L), threads, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const __nv_bfloat16 *>(h), h_sb, h_sl, reinterpret_cast<const __nv_bfloat16 *>(x_conv),
         x_sb, x_sl, reinterpret_cast<const __nv_bfloat16 *>(gate), g_sb, g_sl, D, weight, w_dtype, gate_bias,
-        eps, reinterpret_cast<__nv_bfloat16 *>(y), L, H, R);
-    return check_launch("scan_epilogue");
+        eps, reinterpret_cast<__nv_bfloat16 *>(y), L, H, R, mode, sumsq, norm_width);
+    return check_launch(who);
   }
   scan_epilogue_kernel<<<(unsigned)(Bt * L), 256, 0, (cudaStream_t)stream>>>(
       h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb, g_sl, xg_dtype, D, weight, w_dtype,
-      gate_bias, eps, y, L, H, R);
-  return check_launch("scan_epilogue");
+      gate_bias, eps, y, L, H, R, mode, sumsq, norm_width);
+  return check_launch(who);
+}
+}  // namespace
+}  // namespace fracssm
+
+extern "C" int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                     const void *x_conv, int64_t x_sb, int64_t x_sl,
+                                     const void *gate, int64_t g_sb, int64_t g_sl, int xg_dtype,
+                                     const float *D, const void *weight, int w_dtype,
+                                     float gate_bias, float eps, void *y, int64_t Bt, int64_t L,
+                                     int64_t H, int64_t R, void *stream) {
+  using namespace fracssm;
+  return scan_epilogue_launch("scan_epilogue", h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb, g_sl,
+                              xg_dtype, D, weight, w_dtype, gate_bias, eps, y, Bt, L, H, R, kEpilogueFull,
+                              nullptr, H * R, stream);
+}
+
+// Head-sharded layers, first pass: sumsq[b*L + l] = sum over the H local heads of
+// ((h + x_conv * D) * silu(gate + gate_bias))^2.
+extern "C" int fracssm_scan_epilogue_sumsq(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                           const void *x_conv, int64_t x_sb, int64_t x_sl,
+                                           const void *gate, int64_t g_sb, int64_t g_sl, int xg_dtype,
+                                           const float *D, float gate_bias, float *sumsq, int64_t Bt,
+                                           int64_t L, int64_t H, int64_t R, void *stream) {
+  using namespace fracssm;
+  return scan_epilogue_launch("scan_epilogue_sumsq", h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb,
+                              g_sl, xg_dtype, D, nullptr, FRACSSM_F32, gate_bias, 0.f, nullptr, Bt, L, H, R,
+                              kEpiloguePartial, sumsq, H * R, stream);
+}
+
+// Head-sharded layers, second pass: the local columns normalised with the row's total sum of squares
+// over all `norm_width` columns of the layer (sumsq after the sum across GPUs).
+extern "C" int fracssm_scan_epilogue_apply(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                           const void *x_conv, int64_t x_sb, int64_t x_sl,
+                                           const void *gate, int64_t g_sb, int64_t g_sl, int xg_dtype,
+                                           const float *D, const void *weight, int w_dtype,
+                                           float gate_bias, float eps, const float *sumsq,
+                                           int64_t norm_width, void *y, int64_t Bt, int64_t L, int64_t H,
+                                           int64_t R, void *stream) {
+  using namespace fracssm;
+  return scan_epilogue_launch("scan_epilogue_apply", h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb,
+                              g_sl, xg_dtype, D, weight, w_dtype, gate_bias, eps, y, Bt, L, H, R, kEpilogueApply,
+                              const_cast<float *>(sumsq), norm_width, stream);
 }

@@ -57,3 +57,51 @@ def scan_epilogue(h, x_conv, gate, D, weight, num_heads, head_dim, eps=1e-6, gat
             C.ptr(w), C.dt(w), float(gate_bias), float(eps), C.ptr(y), B, L, H, R,
             C.stream_of(x_conv)), "scan_epilogue")
     return y
+
+
+def _epilogue_args(h, x_conv, gate, D, num_heads, head_dim):
+    assert h.dim() == 3 and x_conv.dim() == 3 and gate.dim() == 3, "h, x_conv and gate must be 3D"
+    assert h.is_cuda and x_conv.is_cuda and gate.is_cuda, "inputs must be on CUDA"
+    H, R = num_heads, head_dim
+    B, L, HR = x_conv.shape
+    assert HR == H * R and gate.shape == x_conv.shape and h.shape == (B * H, L, R)
+    assert gate.dtype == x_conv.dtype, "gate and x_conv must have the same dtype"
+    Df = D.detach().to(device=x_conv.device, dtype=torch.float32).contiguous()
+    return C.rows(h), C.rows(x_conv), C.rows(gate), Df, B, L, H, R
+
+
+def scan_epilogue_sumsq(h, x_conv, gate, D, num_heads, head_dim, gate_bias=0.0):
+    """First pass of the epilogue of a head-sharded layer: per (b, l) row, the sum of squares of
+    (h_unflat + x_conv * D) * silu(gate + gate_bias) over the local heads, float32 [B, L]."""
+    h, x_conv, gate, Df, B, L, H, R = _epilogue_args(h, x_conv, gate, D, num_heads, head_dim)
+    sumsq = torch.zeros(B, L, device=x_conv.device, dtype=torch.float32)
+    if B == 0 or L == 0:
+        return sumsq
+    with torch.cuda.device(x_conv.device):
+        C.check(C.lib().fracssm_scan_epilogue_sumsq(
+            C.ptr(h), C.dt(h), h.stride(0), h.stride(1), C.ptr(x_conv), x_conv.stride(0),
+            x_conv.stride(1), C.ptr(gate), gate.stride(0), gate.stride(1), C.dt(x_conv), C.ptr(Df),
+            float(gate_bias), C.ptr(sumsq), B, L, H, R, C.stream_of(x_conv)), "scan_epilogue_sumsq")
+    return sumsq
+
+
+def scan_epilogue_apply(h, x_conv, gate, D, weight, num_heads, head_dim, sumsq, norm_width, eps=1e-6,
+                        gate_bias=0.0):
+    """Second pass: the local columns normalised with `sumsq` [B, L], the rows' sums of squares over
+    all `norm_width` columns of the layer (the first pass's result added across GPUs)."""
+    h, x_conv, gate, Df, B, L, H, R = _epilogue_args(h, x_conv, gate, D, num_heads, head_dim)
+    assert sumsq.shape == (B, L) and sumsq.dtype == torch.float32 and sumsq.is_cuda
+    assert norm_width >= H * R, "norm_width is the layer's full width"
+    w = weight.detach().contiguous()
+    assert w.numel() == H * R, "weight holds the local columns"
+    sumsq = sumsq.contiguous()
+    y = torch.empty(B, L, H * R, device=x_conv.device, dtype=x_conv.dtype)
+    if B == 0 or L == 0:
+        return y
+    with torch.cuda.device(x_conv.device):
+        C.check(C.lib().fracssm_scan_epilogue_apply(
+            C.ptr(h), C.dt(h), h.stride(0), h.stride(1), C.ptr(x_conv), x_conv.stride(0),
+            x_conv.stride(1), C.ptr(gate), gate.stride(0), gate.stride(1), C.dt(x_conv), C.ptr(Df),
+            C.ptr(w), C.dt(w), float(gate_bias), float(eps), C.ptr(sumsq), int(norm_width), C.ptr(y),
+            B, L, H, R, C.stream_of(x_conv)), "scan_epilogue_apply")
+    return y

@@ -1,6 +1,6 @@
 """Multi-GPU use of the scan: one process per GPU, `torch.distributed` for the plumbing.
 
-Two ways to shard, both new with respect to the reference (which has no distributed code):
+Three ways to shard, all new with respect to the reference (which has no distributed code):
 
 * rows — dim 0 (batch x heads) is split across ranks.  Every stage is independent across dim 0
   (`frac_ssm/ops/triton/chunk_cumsum.py:57` and every other grid starts with the row index), so
@@ -10,6 +10,11 @@ Two ways to shard, both new with respect to the reference (which has no distribu
   state; these pairs compose associatively (the segment summaries of
   `frac_ssm/ops/cute/state_passing.py:144-199`), so one all-gather of (D, F) per rank gives
   every rank its true incoming state, after which it scans its segment once.
+
+* heads of a whole layer — like rows for the scan itself, but the gated RMSNorm that follows spans
+  all heads of a (batch, token) row (`frac_ssm/modules/rmsnorm_gated.py:8-24`): each rank computes
+  the sum of squares over its own heads, one all-reduce of a [batch, L] float32 vector adds them,
+  and each rank normalises its own columns (`head_parallel_epilogue`).
 
 The stage functions are taken from an `ops` object so the host logic can be exercised on CPU
 ranks (gloo) with CPU stage functions supplied by the tests; the default is the CUDA extension.
@@ -167,3 +172,39 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
 
 
 __all__ = ["shard_rows", "shard_tokens", "CudaStageOps", "incoming_state", "seq_parallel_scan"]
+
+
+def shard_heads(num_heads: int, rank: int, world: int) -> slice:
+    """Heads owned by `rank` when a layer's heads are spread over `world` ranks."""
+    return shard_rows(num_heads, rank, world)
+
+
+class CudaEpilogueOps:
+    """The two passes of the head-sharded epilogue on the CUDA extension."""
+
+    @staticmethod
+    def sumsq(h, x_conv, gate, D, num_heads, head_dim, gate_bias):
+        from .layers.output_mix import scan_epilogue_sumsq
+        return scan_epilogue_sumsq(h, x_conv, gate, D, num_heads, head_dim, gate_bias)
+
+    @staticmethod
+    def apply(h, x_conv, gate, D, weight, num_heads, head_dim, sumsq, norm_width, eps, gate_bias):
+        from .layers.output_mix import scan_epilogue_apply
+        return scan_epilogue_apply(h, x_conv, gate, D, weight, num_heads, head_dim, sumsq, norm_width,
+                                   eps, gate_bias)
+
+
+def head_parallel_epilogue(h, x_conv, gate, D, weight, local_heads, head_dim, total_heads, eps=1e-6,
+                           gate_bias=0.0, group=None, ops=CudaEpilogueOps):
+    """Skip-mix + gated RMSNorm of a layer whose heads are spread over the ranks of `group`.
+
+    Every rank passes the slices for its own `local_heads` heads: h [batch*local_heads, L, R] (the
+    scan's output for those heads), x_conv / gate [batch, L, local_heads*R], D [local_heads, R],
+    weight [local_heads*R].  Returns the rank's own columns of the normalised output,
+    [batch, L, local_heads*R].  One all-reduce of batch*L float32 values is the only communication.
+    """
+    sumsq = ops.sumsq(h, x_conv, gate, D, local_heads, head_dim, gate_bias)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=group)
+    return ops.apply(h, x_conv, gate, D, weight, local_heads, head_dim, sumsq, total_heads * head_dim,
+                     eps, gate_bias)

@@ -238,6 +238,26 @@ int fracssm_selftest_umma(const float *A, const float *B, const void *B_bf16, fl
                           int b_via_tma, void *stream);
 
 /*
+ * The same epilogue for a layer whose heads are spread over several GPUs (the norm then spans columns
+ * held by other GPUs).  Pass 1 writes, per (b, l) row, the sum of squares of the gated values of the H
+ * local heads; the caller adds these [Bt*L] float32 vectors across GPUs (one all-reduce); pass 2
+ * normalises the local columns with the total over all `norm_width` columns of the layer.
+ * The reference has no head-sharded layer; single-GPU semantics are those of fracssm_scan_epilogue
+ * (frac_ssm/models/modeling_frac.py:213-214, frac_ssm/modules/rmsnorm_gated.py:8-24).
+ */
+int fracssm_scan_epilogue_sumsq(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                const void *x_conv, int64_t x_sb, int64_t x_sl, const void *gate,
+                                int64_t g_sb, int64_t g_sl, int xg_dtype, const float *D,
+                                float gate_bias, float *sumsq, int64_t Bt, int64_t L, int64_t H,
+                                int64_t R, void *stream);
+int fracssm_scan_epilogue_apply(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl,
+                                const void *x_conv, int64_t x_sb, int64_t x_sl, const void *gate,
+                                int64_t g_sb, int64_t g_sl, int xg_dtype, const float *D,
+                                const void *weight, int w_dtype, float gate_bias, float eps,
+                                const float *sumsq, int64_t norm_width, void *y, int64_t Bt, int64_t L,
+                                int64_t H, int64_t R, void *stream);
+
+/*
  * Diagnostic: as fracssm_selftest_umma with K-major operands but a 64-row MMA; D [128][N] receives
  * all 128 tensor-memory lanes, which shows where the 64 result rows land.  No counterpart in the
  * reference.

@@ -128,6 +128,38 @@ def test_scan_epilogue_matches_unfused_pair():
     close(y, ref, **TOL_BF16)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shards", [2, 3, 8])
+def test_head_sharded_epilogue_two_passes(dtype, shards):
+    """Partial sums of squares per head shard, added, then applied: same result as the one-pass
+    epilogue over all heads (the shards are emulated one after another on this GPU)."""
+    from frac_ssm_b200.layers import scan_epilogue, scan_epilogue_apply, scan_epilogue_sumsq
+    from frac_ssm_b200.parallel import shard_heads
+    B, L, H, R = 2, 37, 24, 64
+    g = torch.Generator().manual_seed(5)
+    h = torch.randn(B * H, L, R, generator=g).to(dtype).cuda()
+    x = torch.randn(B, L, H * R, generator=g).to(dtype).cuda()
+    z = torch.randn(B, L, H * R, generator=g).to(dtype).cuda()
+    D = torch.randn(H, R, generator=g).cuda()
+    w = (1 + 0.1 * torch.randn(H * R, generator=g)).to(dtype).cuda()
+    y_full = scan_epilogue(h, x, z, D, w, H, R, 1e-6, gate_bias=0.25)
+    parts, total = [], torch.zeros(B, L, device="cuda")
+    for r in range(shards):
+        hs = shard_heads(H, r, shards)
+        n, cols = hs.stop - hs.start, slice(hs.start * R, hs.stop * R)
+        h_loc = h.view(B, H, L, R)[:, hs].reshape(B * n, L, R)
+        args = (h_loc, x[..., cols], z[..., cols], D[hs])      # column slices stay strided views
+        parts.append((args, w[cols], n, cols))
+        total += scan_epilogue_sumsq(*args, n, R, gate_bias=0.25)
+    ref = O.rmsnorm_gated(O.skip_mix(h.cpu(), x.cpu(), D.cpu(), H, R, exact=True), w.cpu(),
+                          z.cpu().double() + 0.25, 1e-6, exact=True)
+    for args, w_loc, n, cols in parts:
+        y = scan_epilogue_apply(*args, w_loc, n, R, total, H * R, 1e-6, gate_bias=0.25)
+        close(y, ref[..., cols], **(TOL_BF16 if dtype == torch.bfloat16 else TOL_F32))
+        close(y, y_full[..., cols].float().cpu(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5,
+              atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
 def test_mixer_path_composition_matches_oracle():
     """The whole layer path as FracMixer.forward strings it together (prep -> scan -> skip-mix ->
     gated norm) on the CUDA ops, against the same composition on the CPU oracle."""

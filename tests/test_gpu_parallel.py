@@ -1,4 +1,4 @@
-"""Sequence sharding on real devices: emulated on one GPU, and over NCCL when two are present."""
+"""Sequence and head sharding on real devices: emulated on one GPU, and over NCCL when two are present."""
 
 import os
 import socket
@@ -82,4 +82,42 @@ def test_sequence_sharding_over_nccl():
     with mp.Manager() as mgr:
         out = mgr.dict()
         mp.spawn(_nccl_worker, args=(world, port, out), nprocs=world, join=True)
+        assert dict(out) == {0: 1, 1: 1}
+
+
+def _nccl_heads_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from frac_ssm_b200 import parallel
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        batch, L, H, R = 2, 300, 16, 64
+        g = torch.Generator().manual_seed(17)
+        h = torch.randn(batch * H, L, R, generator=g).bfloat16()
+        x = torch.randn(batch, L, H * R, generator=g).bfloat16()
+        z = torch.randn(batch, L, H * R, generator=g).bfloat16()
+        D = torch.randn(H, R, generator=g)
+        w = (1 + 0.1 * torch.randn(H * R, generator=g)).bfloat16()
+        ref = O.rmsnorm_gated(O.skip_mix(h, x, D, H, R, exact=True), w, z, 1e-6, exact=True)
+        hs = parallel.shard_heads(H, rank, world)
+        n, cols = hs.stop - hs.start, slice(hs.start * R, hs.stop * R)
+        h_loc = h.view(batch, H, L, R)[:, hs].reshape(batch * n, L, R).cuda()
+        y = parallel.head_parallel_epilogue(h_loc, x[..., cols].contiguous().cuda(), z[..., cols].contiguous().cuda(),
+                                            D[hs].cuda(), w[cols].cuda(), n, R, H, 1e-6)
+        out[rank] = int(torch.allclose(y.float().cpu().double(), ref[..., cols], rtol=2e-2, atol=2e-2))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_head_sharded_epilogue_over_nccl():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_nccl_heads_worker, args=(world, port, out), nprocs=world, join=True)
         assert dict(out) == {0: 1, 1: 1}

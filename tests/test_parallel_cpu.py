@@ -29,6 +29,24 @@ class OracleStageOps:
         return O.frac_scan(u.float(), c.float(), kappa.float(), rho, T, init, True, exact=True)
 
 
+class OracleEpilogueOps:
+    """The two passes of the head-sharded epilogue restated with the CPU oracle's pieces."""
+
+    @staticmethod
+    def _gated(h, x_conv, gate, D, H, R, gate_bias):
+        mixed = O.skip_mix(h, x_conv, D, H, R, out_dtype=torch.float64, exact=True)
+        return mixed * torch.nn.functional.silu(gate.double() + gate_bias)
+
+    @staticmethod
+    def sumsq(h, x_conv, gate, D, H, R, gate_bias):
+        return OracleEpilogueOps._gated(h, x_conv, gate, D, H, R, gate_bias).pow(2).sum(-1).float()
+
+    @staticmethod
+    def apply(h, x_conv, gate, D, weight, H, R, sumsq, norm_width, eps, gate_bias):
+        v = OracleEpilogueOps._gated(h, x_conv, gate, D, H, R, gate_bias)
+        return (v * torch.rsqrt(sumsq.double() / norm_width + eps)[..., None] * weight.double()).float()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -53,6 +71,22 @@ def _worker(rank, world, port, mode, out):
                                                 local_splits=4 if mode == "seq_split" else 1)
             ok = torch.allclose(h, h_ref[:, tok], rtol=1e-4, atol=1e-4) and \
                 torch.allclose(fin, f_ref, rtol=1e-4, atol=1e-4)
+        elif mode == "heads":       # a layer's heads spread over the ranks; the norm spans all heads
+            batch, H, Rh, Lh = 2, 6, 8, 40
+            g = torch.Generator().manual_seed(11)
+            hh = torch.randn(batch * H, Lh, Rh, generator=g)
+            x = torch.randn(batch, Lh, H * Rh, generator=g)
+            z = torch.randn(batch, Lh, H * Rh, generator=g)
+            Dk, wk = torch.randn(H, Rh, generator=g), torch.rand(H * Rh, generator=g) + 0.5
+            y_ref = O.rmsnorm_gated(O.skip_mix(hh, x, Dk, H, Rh, exact=True), wk, z, 1e-6, exact=True)
+            hs = parallel.shard_heads(H, rank, world)
+            cols = slice(hs.start * Rh, hs.stop * Rh)
+            nloc = hs.stop - hs.start
+            h_loc = hh.view(batch, H, Lh, Rh)[:, hs].reshape(batch * nloc, Lh, Rh)
+            y = parallel.head_parallel_epilogue(h_loc, x[..., cols].contiguous(), z[..., cols].contiguous(),
+                                                Dk[hs], wk[cols], nloc, Rh, H, 1e-6, 0.0,
+                                                ops=OracleEpilogueOps)
+            ok = torch.allclose(y.double(), y_ref[..., cols], rtol=1e-5, atol=1e-5)
         elif mode == "rows":
             rows = parallel.shard_rows(B, rank, world)
             h, fin = OracleStageOps.scan(u[rows], c[rows], kappa[rows], rho[rows], T, init[rows])
@@ -94,6 +128,11 @@ def test_sequence_sharding_with_local_sub_segments():
 
 def test_row_sharding_matches_single_scan():
     _run(2, "rows")
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_head_sharded_epilogue_matches_full_norm(world):
+    _run(world, "heads")
 
 
 def test_misaligned_segment_is_refused():
