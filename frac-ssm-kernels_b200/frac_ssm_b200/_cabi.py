@@ -53,6 +53,9 @@ _SIGNATURES = {
     "fracssm_selftest_umma": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "fracssm_scan_epilogue": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, vp, ci,
                                    cf, cf, vp, i64, i64, i64, i64, vp]),
+    "fracssm_causal_conv_silu": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, vp, ci, vp, ci, i64, i64, i64,
+                                      i64, vp]),
+    "fracssm_decode_step": (ci, [vp, ci, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]),
     "fracssm_scan_epilogue_sumsq": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, cf, vp,
                                          i64, i64, i64, i64, vp]),
     "fracssm_scan_epilogue_apply": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, vp, ci,

@@ -1,0 +1,233 @@
+"""The FRAC model on the B200 extension: same module tree and parameter names as the reference
+(`frac_ssm/models/modeling_frac.py:63-330`), so a reference state_dict loads unchanged.  Forward only.
+
+Per layer, prefill runs: in_proj (library GEMM) -> causal depthwise conv + SiLU (CUDA kernel) ->
+dyn_proj / rw_proj (library GEMMs) -> parameter prep (CUDA kernel) -> frac_scan (single-pass tcgen05
+kernel when the shape allows, else the staged kernels) -> skip-mix + gated RMSNorm (one CUDA kernel)
+-> out_proj (library GEMM).  Decode runs one token through the conv window, the same parameter prep
+with L = 1 and the state-update kernel.  The cache is the reference's: per layer
+(state [B, H, M, R] float32, conv_state [B, C, K-1]).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import _cabi as C
+from ..layers.compute_params import compute_params_from_projections
+from ..layers.output_mix import scan_epilogue
+from ..modules.rmsnorm_gated import MambaRMSNormGated as RMSNormGated
+from ..modules.rmsnorm_gated import rmsnorm_gated_fwd
+from ..ops.frac_scan import frac_scan
+from .configuration_frac import FracConfig
+
+LayerCache = tuple  # (state [B, H, M, R] float32, conv_state [B, C, K-1])
+
+
+def causal_conv_silu(x, weight, bias, attention_mask=None):
+    """silu(depthwise causal conv) over channels-last x [B, L, C]; weight [C, 1, K] or [C, K]."""
+    assert x.dim() == 3 and x.is_cuda, "x must be a 3D CUDA tensor"
+    B, L, Cn = x.shape
+    w = weight.detach().reshape(Cn, -1).contiguous()
+    K = w.shape[1]
+    b = None if bias is None else bias.detach().to(w.dtype).contiguous()
+    x = C.rows(x)
+    mask = None
+    if attention_mask is not None:
+        assert attention_mask.shape == (B, L), "attention_mask shape must be (B, L)"
+        mask = attention_mask.to(device=x.device, dtype=torch.float32)
+    y = torch.empty(B, L, Cn, device=x.device, dtype=x.dtype)
+    if B == 0 or L == 0:
+        return y
+    with torch.cuda.device(x.device):
+        C.check(C.lib().fracssm_causal_conv_silu(
+            C.ptr(x), C.dt(x), x.stride(0), x.stride(1), C.ptr(mask),
+            0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1), C.ptr(w),
+            C.ptr(b), C.dt(w), C.ptr(y), C.dt(y), B, L, Cn, K, C.stream_of(x)), "causal_conv_silu")
+    return y
+
+
+def decode_step(u, c, kappa, rho, D, state):
+    """One token: `state` [B, H, M, R] float32 is updated in place; returns mixed [B, H, R] float32
+    (the readout plus the D skip)."""
+    B, H, R = u.shape
+    M = c.shape[-1]
+    assert state.shape == (B, H, M, R) and state.dtype == torch.float32 and state.is_contiguous()
+    u = u.contiguous()
+    c, kappa, rho = (t.to(torch.float32).contiguous() for t in (c, kappa, rho))
+    Df = D.detach().to(device=u.device, dtype=torch.float32).contiguous()
+    out = torch.empty(B, H, R, device=u.device, dtype=torch.float32)
+    if B:
+        with torch.cuda.device(u.device):
+            C.check(C.lib().fracssm_decode_step(C.ptr(u), C.dt(u), C.ptr(c), C.ptr(kappa), C.ptr(rho),
+                                                C.ptr(Df), C.ptr(state), C.ptr(out), B, H, R, M,
+                                                C.stream_of(u)), "decode_step")
+    return out
+
+
+class RMSNorm(nn.Module):
+    """Plain RMSNorm (the reference's `frac_ssm/modules/rmsnorm.py:728-740`): float32 arithmetic,
+    output in the input dtype."""
+
+    def __init__(self, hidden_size, eps=1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states):
+        return rmsnorm_gated_fwd(hidden_states, self.weight, None, self.variance_epsilon)[0]
+
+
+class FracMixer(nn.Module):
+    def __init__(self, config: FracConfig):
+        super().__init__()
+        self.config = config
+        self.hidden_size, self.inner_dim = config.hidden_size, config.intermediate_size
+        self.num_heads, self.num_modes, self.head_dim = config.num_attention_heads, config.frac_num_modes, config.frac_head_dim
+        self.conv_kernel, self.chunk_size, self.read_temp = config.frac_conv_kernel, config.frac_chunk_size, 1.0
+        self.in_proj = nn.Linear(self.hidden_size, 2 * self.inner_dim, bias=False)
+        self.conv1d = nn.Conv1d(self.inner_dim, self.inner_dim, kernel_size=self.conv_kernel, groups=self.inner_dim,
+                                bias=config.frac_conv_bias, padding=self.conv_kernel - 1)
+        self.dyn_proj = nn.Linear(self.inner_dim, 3 * self.num_heads, bias=True)
+        self.dt_bias = nn.Parameter(torch.zeros(self.num_heads))
+        self.rw_proj = nn.Linear(self.inner_dim, 2 * self.num_heads * self.num_modes, bias=False)
+        self.read_residual_logit = nn.Parameter(torch.tensor([float(config.frac_residual_read_init)]))
+        p = min(max(float(config.frac_write_scale_init), 1e-4), 1.0 - 1e-4)
+        self.write_residual_scale = nn.Parameter(torch.tensor([math.log(p / (1.0 - p))], dtype=torch.float32))
+        self.register_buffer("base_log_tau", torch.linspace(math.log(config.frac_tau_min), math.log(config.frac_tau_max),
+                                                            self.num_modes, dtype=torch.float32), persistent=True)
+        self.out_norm = RMSNormGated(self.inner_dim, eps=config.rms_norm_eps)
+        self.out_proj = nn.Linear(self.inner_dim, self.hidden_size, bias=False)
+        self.D = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
+        self._gates = None  # (version key, read logit, write logit) as Python floats: no sync per call
+
+    def _gate_logits(self):
+        key = (self.read_residual_logit._version, self.write_residual_scale._version,
+               self.read_residual_logit.data_ptr(), self.write_residual_scale.data_ptr())
+        if self._gates is None or self._gates[0] != key:
+            self._gates = (key, float(self.read_residual_logit.item()), float(self.write_residual_scale.item()))
+        return self._gates[1], self._gates[2]
+
+    def _scan_params(self, x_conv, x, attention_mask):
+        cfg = self.config
+        dyn = F.linear(x, self.dyn_proj.weight, self.dyn_proj.bias)
+        rw = F.linear(x_conv, self.rw_proj.weight)
+        read_logit, write_logit = self._gate_logits()
+        return compute_params_from_projections(
+            dyn, rw, x_conv, attention_mask, self.dt_bias, read_logit, write_logit, self.base_log_tau,
+            self.num_heads, self.head_dim, self.num_modes, self.read_temp, cfg.frac_dt_min, cfg.frac_dt_max,
+            cfg.frac_alpha_min, cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max)
+
+    def _conv_state_after(self, x, attention_mask):
+        """The last K-1 (masked) inputs, channels first, zero-padded on the left."""
+        keep = self.conv_kernel - 1
+        xt = x if attention_mask is None else x * attention_mask[..., None].to(x.dtype)
+        tail = xt[:, max(x.shape[1] - keep, 0):].transpose(1, 2)
+        return F.pad(tail, (keep - tail.shape[-1], 0)).contiguous()
+
+    def forward(self, hidden_states, attention_mask=None, layer_past=None, use_cache=False):
+        B, L, _ = hidden_states.shape
+        H, R, M = self.num_heads, self.head_dim, self.num_modes
+        x, gate = self.in_proj(hidden_states).chunk(2, dim=-1)
+        gate_bias = float(self.config.frac_gate_bias_init)
+        if layer_past is None and L > 1:
+            x_conv = causal_conv_silu(x, self.conv1d.weight, self.conv1d.bias, attention_mask)
+            u, c, kappa, rho = self._scan_params(x_conv, x, attention_mask)
+            out = frac_scan(u, c, kappa, rho, self.chunk_size, None, use_cache)
+            next_cache = None
+            if use_cache:
+                mixed, final_state = out
+                state = final_state.view(B, H, R, M).permute(0, 1, 3, 2).float().contiguous()
+                next_cache = (state, self._conv_state_after(x, attention_mask))
+            else:
+                mixed = out
+            y = scan_epilogue(mixed, x_conv, gate, self.D, self.out_norm.weight, H, R,
+                              self.out_norm.variance_epsilon, gate_bias)
+            return self.out_proj(y), next_cache
+
+        # token by token, with or without a cache (a one-token prompt starts from an empty one)
+        state, conv_state = layer_past if layer_past is not None else (None, None)
+        if state is None:
+            state = torch.zeros(B, H, M, R, device=x.device, dtype=torch.float32)
+        else:
+            state = state.float().contiguous().clone()
+        keep = self.conv_kernel - 1
+        if conv_state is None:
+            conv_state = x.new_zeros(B, self.inner_dim, keep)
+        w = self.conv1d.weight[:, 0]
+        outs = []
+        for t in range(L):
+            xt = x[:, t]
+            mask_t = None if attention_mask is None else attention_mask[:, t:t + 1]
+            cin = xt if mask_t is None else xt * mask_t.to(xt.dtype)
+            window = torch.cat((conv_state, cin.unsqueeze(-1)), dim=-1)
+            pre = (window * w[None]).sum(-1)
+            if self.conv1d.bias is not None:
+                pre = pre + self.conv1d.bias[None]
+            x_conv = F.silu(pre)
+            conv_state = window[:, :, 1:].contiguous() if keep else conv_state
+            u, c, kappa, rho = self._scan_params(x_conv[:, None], xt[:, None], mask_t)
+            mixed = decode_step(u.view(B, H, R), c.view(B, H, M), kappa.view(B, H, M), rho.view(B, H, M),
+                                self.D, state)
+            mixed = mixed.reshape(B, self.inner_dim).to(hidden_states.dtype)
+            y = self.out_norm(mixed, gate=(gate[:, t] + gate_bias).contiguous())
+            outs.append(self.out_proj(y))
+        return torch.stack(outs, dim=1), ((state, conv_state) if use_cache else None)
+
+
+class FracBlock(nn.Module):
+    def __init__(self, config: FracConfig):
+        super().__init__()
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.mixer = FracMixer(config)
+
+    def forward(self, hidden_states, attention_mask=None, layer_past=None, use_cache=False):
+        y, cache = self.mixer(self.norm(hidden_states), attention_mask=attention_mask, layer_past=layer_past,
+                              use_cache=use_cache)
+        return hidden_states + y, cache
+
+
+class FracModel(nn.Module):
+    def __init__(self, config: FracConfig):
+        super().__init__()
+        self.config = config
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, padding_idx=config.pad_token_id)
+        self.layers = nn.ModuleList(FracBlock(config) for _ in range(config.num_hidden_layers))
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    @torch.no_grad()
+    def forward(self, input_ids=None, attention_mask=None, inputs_embeds=None, past_key_values=None,
+                use_cache=None):
+        """-> (last_hidden_state, past_key_values or None)."""
+        if (input_ids is None) == (inputs_embeds is None):
+            raise ValueError("You must specify exactly one of input_ids and inputs_embeds.")
+        use_cache = self.config.use_cache if use_cache is None else use_cache
+        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        past = (None,) * len(self.layers) if past_key_values is None else past_key_values
+        new_past = [] if use_cache else None
+        for layer, layer_past in zip(self.layers, past):
+            h, cache = layer(h, attention_mask=attention_mask, layer_past=layer_past, use_cache=use_cache)
+            if new_past is not None:
+                new_past.append(cache)
+        return self.norm(h), (tuple(new_past) if new_past is not None else None)
+
+
+class FracForCausalLM(nn.Module):
+    def __init__(self, config: FracConfig):
+        super().__init__()
+        self.config = config
+        self.model = FracModel(config)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        if config.tie_word_embeddings:
+            self.lm_head.weight = self.model.embed_tokens.weight
+
+    @torch.no_grad()
+    def forward(self, input_ids=None, attention_mask=None, inputs_embeds=None, past_key_values=None,
+                use_cache=None):
+        """-> (logits, past_key_values or None)."""
+        h, past = self.model(input_ids, attention_mask, inputs_embeds, past_key_values, use_cache)
+        return self.lm_head(h), past

@@ -258,6 +258,29 @@ int fracssm_scan_epilogue_apply(const void *h, int h_dtype, int64_t h_sb, int64_
                                 int64_t H, int64_t R, void *stream);
 
 /*
+ * Causal depthwise convolution + SiLU over channels-last activations:
+ *   y[b,l,ch] = silu(bias[ch] + sum_k weight[ch,k] * xm[b, l-(K-1)+k, ch]),  xm = x * mask (zero before
+ * the sequence start).  x [Bt,L,C] with batch / token strides in elements, mask float32 [Bt,L] or NULL,
+ * weight [C,K] and bias [C] (or NULL) of w_dtype, y [Bt,L,C] dense, K in 1..8.
+ * Replaces frac_ssm/models/modeling_frac.py:116-131 (`FracMixer._causal_conv_full`: nn.Conv1d with
+ * left padding K-1 followed by the activation, or causal_conv1d_fn).
+ */
+int fracssm_causal_conv_silu(const void *x, int x_dtype, int64_t x_sb, int64_t x_sl, const float *mask,
+                             int64_t m_sb, int64_t m_sl, const void *weight, const void *bias,
+                             int w_dtype, void *y, int y_dtype, int64_t Bt, int64_t L, int64_t C,
+                             int64_t K, void *stream);
+
+/*
+ * One decode token for every (batch, head): state [Bt*H, M, R] float32 is updated in place,
+ *   state[m,r] = rho[m] * state[m,r] + kappa[m] * u[r];  out[r] = sum_m c[m] * state[m,r] + u[r] * D[h,r].
+ * u [Bt*H, R] (u_dtype), c / kappa / rho [Bt*H, M] float32, D [H, R] float32, out [Bt*H, R] float32.
+ * Replaces frac_ssm/models/modeling_frac.py:159-179 (`FracMixer._update_state`) and the skip of :236.
+ */
+int fracssm_decode_step(const void *u, int u_dtype, const float *c, const float *kappa, const float *rho,
+                        const float *D, float *state, float *out, int64_t Bt, int64_t H, int64_t R,
+                        int64_t M, void *stream);
+
+/*
  * Diagnostic: as fracssm_selftest_umma with K-major operands but a 64-row MMA; D [128][N] receives
  * all 128 tensor-memory lanes, which shows where the 64 result rows land.  No counterpart in the
  * reference.

@@ -1,0 +1,101 @@
+"""The model path on the GPU against outputs of the reference model recorded on CPU
+(tests/golden/model_*.pt), plus the two mixer kernels next to the scan (conv, decode step)."""
+
+import os
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import frac_oracle as O
+from tests.helpers import close
+
+pytestmark = pytest.mark.gpu
+
+
+def _load(golden_dir, name, dtype=torch.float32):
+    from frac_ssm_b200.models import FracConfig, FracForCausalLM
+    g = torch.load(os.path.join(golden_dir, name + ".pt"), weights_only=False)
+    model = FracForCausalLM(FracConfig(**g["config"]))
+    model.load_state_dict(g["state_dict"], strict=True)
+    return g, model.to(device="cuda", dtype=dtype).eval()
+
+
+@pytest.mark.parametrize("name", ["model_tiny", "model_tiny_masked", "model_wide"])
+def test_prefill_and_decode_match_reference_model(golden_dir, name):
+    g, model = _load(golden_dir, name)
+    L = g["prefill_len"]
+    ids = g["input_ids"].cuda()
+    mask = None if g["attention_mask"] is None else g["attention_mask"].cuda()
+    scale = g["logits"].abs().max().item()
+    tol = dict(rtol=2e-3, atol=2e-3 * scale)
+    logits, past = model(ids[:, :L], attention_mask=mask, use_cache=True)
+    close(logits, g["logits"], **tol)
+    close(past[0][0], g["state0"], rtol=1e-3, atol=1e-3)
+    close(past[0][1], g["conv_state0"], rtol=1e-5, atol=1e-5)
+    logits_nc, none = model(ids[:, :L], attention_mask=mask, use_cache=False)
+    assert none is None
+    close(logits_nc, g["logits_nocache"], **tol)
+    steps = []
+    for t in range(g["decode_logits"].shape[1]):
+        lg, past = model(ids[:, L + t:L + t + 1], past_key_values=past, use_cache=True)
+        steps.append(lg)
+    close(torch.cat(steps, 1), g["decode_logits"], **tol)
+    close(past[0][0], g["state_after_decode"], rtol=1e-3, atol=1e-3)
+
+
+def test_bf16_model_takes_the_single_pass_scan(golden_dir):
+    """head_dim 64 / 128 modes in bf16 is the shape of the tcgen05 scan kernel; the logits stay within
+    bf16 accuracy of the float32 reference."""
+    from frac_ssm_b200 import _cabi as C
+    g, model = _load(golden_dir, "model_wide", torch.bfloat16)
+    cfg = model.config
+    assert C.lib().fracssm_scan_fused_supported(2 * cfg.num_attention_heads, g["prefill_len"], cfg.frac_head_dim,
+                                                cfg.frac_num_modes, cfg.frac_chunk_size, C.BF16, C.F32)
+    L = g["prefill_len"]
+    logits, past = model(g["input_ids"][:, :L].cuda(), use_cache=True)
+    ref = g["logits"]
+    err = (logits.float().cpu() - ref).abs().max().item()
+    assert err <= 0.03 * ref.abs().max().item(), err
+
+
+@pytest.mark.parametrize("dtype,C_,K", [(torch.bfloat16, 1536, 4), (torch.float32, 100, 4), (torch.bfloat16, 72, 3),
+                                        (torch.float32, 33, 1), (torch.float16, 64, 8)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_causal_conv_silu_matches_conv1d(dtype, C_, K, masked):
+    from frac_ssm_b200.models.modeling_frac import causal_conv_silu
+    B, L = 3, 150
+    g = torch.Generator().manual_seed(C_ + K)
+    both = torch.randn(B, L, 2 * C_, generator=g).to(dtype)       # x is a strided half, as after in_proj.chunk
+    x = both[..., :C_]
+    w = (0.5 * torch.randn(C_, 1, K, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(C_, generator=g)).to(dtype)
+    mask = None
+    if masked:
+        mask = torch.ones(B, L, dtype=torch.long)
+        mask[1, :40] = 0
+        mask[2, 100:] = 0
+    y = causal_conv_silu(both.cuda()[..., :C_], w.cuda(), b.cuda(), None if mask is None else mask.cuda())
+    xm = x.double() if mask is None else x.double() * mask[..., None].double()
+    ref = F.silu(F.conv1d(xm.transpose(1, 2), w.double(), b.double(), padding=K - 1, groups=C_)[..., :L]).transpose(1, 2)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    close(y, ref, **tol)
+
+
+@pytest.mark.parametrize("B,H,R,M", [(2, 24, 64, 128), (3, 2, 32, 16), (1, 5, 20, 7)])
+def test_decode_step_matches_token_recurrence(B, H, R, M):
+    from frac_ssm_b200.models.modeling_frac import decode_step
+    g = torch.Generator().manual_seed(B * H)
+    state = torch.randn(B, H, M, R, generator=g)
+    D = torch.randn(H, R, generator=g)
+    st = state.clone().cuda()
+    ref_state = state.double()
+    for t in range(3):
+        u = torch.randn(B, H, R, generator=g).bfloat16()
+        c, kappa = torch.rand(B, H, M, generator=g), torch.rand(B, H, M, generator=g)
+        rho = torch.rand(B, H, M, generator=g).clamp(1e-6, 1 - 1e-6)
+        out = decode_step(u.cuda(), c.cuda(), kappa.cuda(), rho.cuda(), D.cuda(), st)
+        ref_state = rho.double()[..., None] * ref_state + u.double()[:, :, None, :] * kappa.double()[..., None]
+        ref = (c.double()[..., None] * ref_state).sum(2) + u.double() * D.double()[None]
+        close(out, ref, rtol=1e-4, atol=1e-4)
+        close(st, ref_state, rtol=1e-5, atol=1e-5)
