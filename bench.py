@@ -357,6 +357,64 @@ def run_heads_workload(args, rank, world, dev, dist):
         dist.destroy_process_group()
 
 
+def run_model_workload(args, rank, world, dev, dist):
+    """Config 2: prefill of the whole model (24 layers, hidden 768, 24 heads of 64, 128 modes, chunk 256,
+    vocabulary 50280, bf16, random weights), batch 16 x 4096 uniform token ids split over the ranks by
+    batch; independent replicas, no communication."""
+    from frac_ssm_b200.models import FracConfig, FracForCausalLM
+    batch, L = 16, args.seq_len or 4096
+    if batch % world:
+        raise SystemExit(f"--workload model: batch {batch} does not divide over {world} ranks")
+    cfg = FracConfig(vocab_size=50280, hidden_size=768, num_hidden_layers=24, num_attention_heads=24,
+                     frac_expand=2.0, frac_num_modes=128, frac_chunk_size=256)
+    torch.manual_seed(0)
+    model = FracForCausalLM(cfg).to(device=dev, dtype=torch.bfloat16).eval()
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (batch // world, L), device=dev, generator=g)
+
+    def step():
+        return model(ids, use_cache=False)[0]
+
+    def timed():
+        for _ in range(max(args.warmup, 3)):
+            step()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t_ms = e0.elapsed_time(e1) / args.steps
+        if dist is not None:
+            t = torch.tensor([t_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = t.item()
+        return t_ms
+
+    ms_f32 = timed()              # float32 scan coefficients, as the reference's prep emits them
+    for layer in model.model.layers:
+        layer.mixer.coeff_dtype = torch.bfloat16
+    ms = timed()                  # bfloat16 coefficients: the benchmark's headline configuration
+    if rank == 0:
+        nparam = sum(p.numel() for p in model.parameters())
+        print(json.dumps({"metric": "model prefill tokens/s (all GPUs)", "value": batch * L / (ms * 1e-3),
+                          "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                          "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"config 2: 24-layer model prefill, batch {batch} x L {L}, hidden 768, "
+                                                 "24 heads x 64, 128 modes, chunk 256, vocabulary 50280",
+                                     "parameters": nparam, "scan_coefficients": "bf16",
+                                     "ms_per_step_with_f32_scan_coefficients": ms_f32,
+                                     "sharding": f"batch over {world} GPU(s), replicas, no collective"}}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def workload_config(n):
     return {"workload": "config 1: single-layer frac_scan forward + skip-mix/gated-RMSNorm epilogue, "
                         "batch 8 x 24 heads, L 8192, R 64, M 128, chunk 256, per GPU",
@@ -376,15 +434,21 @@ def main():
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
     ap.add_argument("--phases", action="store_true",
                     help="also print the single-pass kernel's per-phase cycle shares (diagnostic)")
-    ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads", "model"],
                     help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
                          "tokens x 24 heads split over the ranks; heads: config 4, one layer's 64 heads spread over the "
-                         "ranks (secondary lines, not the driver's metric)")
+                         "ranks; model: config 2, prefill of the 24-layer model, batch 16 x 4096 "
+                         "split over the ranks (secondary lines, not the driver's metric)")
     ap.add_argument("--step-times", action="store_true",
                     help="also print every timed step's scan-kernel time to stderr (diagnostic)")
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds after which a stalled run dumps its Python stacks and exits (0 = off)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
+    if args.watchdog > 0:      # a stalled run must end with a traceback, not run until someone kills it
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
 
     if args.seq_len:
         CFG["L"] = args.seq_len
@@ -414,6 +478,9 @@ def main():
     _cabi.lib()
     if args.workload == "heads":
         run_heads_workload(args, rank, world, dev, dist)
+        return
+    if args.workload == "model":
+        run_model_workload(args, rank, world, dev, dist)
         return
     if args.workload == "seq":
         run_seq_workload(args, rank, world, dev, dist)

@@ -24,7 +24,7 @@ struct ParamArgs {
   const float *mask; int64_t m_sb, m_sl;
   const float *dt_bias, *log_tau;
   float read_gate, write_gate, inv_read_temp, dt_min, dt_max, a_min, a_max, l_min, l_max;
-  void *u; float *c, *kappa, *rho;
+  void *u, *c, *kappa; int ck_dt; float *rho;
   int64_t L, H, R, M;
 };
 
@@ -72,13 +72,107 @@ __global__ void __launch_bounds__(128) compute_params_kernel(const ParamArgs a) 
     rho = fminf(fmaxf(rho, 1e-6f), 1.f - 1e-6f);
     float kap = (1.f - rho) * ww;
     if (a.mask) { kap *= keep; rho = rho * keep + (1.f - keep); }
-    a.c[obase + m] = cw;
-    a.kappa[obase + m] = kap;
+    st_f32(a.c, obase + m, a.ck_dt, cw);
+    st_f32(a.kappa, obase + m, a.ck_dt, kap);
     a.rho[obase + m] = rho;
   }
   const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
   for (int64_t r = lane; r < R; r += 32)
     st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+}
+
+// The same prep for M = 128 with bf16 projections: one warp walks kPrepTokens tokens of one (b, h);
+// each lane owns four consecutive modes, so a token's read / write residuals are one 8-byte load per
+// lane each, everything stays in registers (one pass), and c / kappa / rho go out as 8- or 16-byte
+// stores.  Same formulas, in the same order, as compute_params_kernel.
+constexpr int kPrepTokens = 8;
+
+__device__ __forceinline__ void unpack4(const uint2 &p, float (&f)[4]) {
+  f[0] = __uint_as_float(p.x << 16);
+  f[1] = __uint_as_float(p.x & 0xFFFF0000u);
+  f[2] = __uint_as_float(p.y << 16);
+  f[3] = __uint_as_float(p.y & 0xFFFF0000u);
+}
+
+__global__ void __launch_bounds__(128) compute_params_m128_kernel(const ParamArgs a) {
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int64_t l0 = ((int64_t)blockIdx.x * 4 + warp) * kPrepTokens;
+  const int64_t bh = blockIdx.y;
+  if (l0 >= a.L) return;
+  const int64_t b = bh / a.H, h = bh % a.H;
+  const int64_t H = a.H, R = a.R;
+  constexpr int64_t M = 128;
+  float lt[4], inv_tau[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lt[i] = a.log_tau[4 * lane + i];
+    inv_tau[i] = 1.f / fmaxf(expf(lt[i]), 1e-6f);
+  }
+  const float dtb = a.dt_bias[h];
+  const __nv_bfloat16 *rw = reinterpret_cast<const __nv_bfloat16 *>(a.rw);
+  const int64_t l1 = min(l0 + kPrepTokens, a.L);
+  for (int64_t l = l0; l < l1; ++l) {
+    const int64_t dbase = b * a.dyn_sb + l * a.dyn_sl;
+    float dt = softplusf_(ld_f32(a.dyn, dbase + h, a.dyn_dt) + dtb);
+    dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
+    const float alpha = a.a_min + sigmoidf_(ld_f32(a.dyn, dbase + H + h, a.dyn_dt)) * (a.a_max - a.a_min);
+    const float lam = a.l_min + sigmoidf_(ld_f32(a.dyn, dbase + 2 * H + h, a.dyn_dt)) * (a.l_max - a.l_min);
+    const float rate = powf(fmaxf(lam, 1e-4f), 1.f / fmaxf(alpha, 1e-4f));
+    const float keep = a.mask ? a.mask[b * a.m_sb + l * a.m_sl] : 1.f;
+
+    const __nv_bfloat16 *rp = rw + b * a.rw_sb + l * a.rw_sl + h * M + 4 * lane;
+    float rres[4], wres[4], rl[4], wl[4];
+    unpack4(__ldcs(reinterpret_cast<const uint2 *>(rp)), rres);
+    unpack4(__ldcs(reinterpret_cast<const uint2 *>(rp + H * M)), wres);
+    float rmax = -INFINITY, wmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float prior = -alpha * lt[i];
+      rl[i] = (prior + a.read_gate * rres[i]) * a.inv_read_temp;
+      wl[i] = prior + a.write_gate * wres[i];
+      rmax = fmaxf(rmax, rl[i]);
+      wmax = fmaxf(wmax, wl[i]);
+    }
+    rmax = warp_max(rmax);
+    wmax = warp_max(wmax);
+    float rsum = 0.f, wsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rl[i] = __expf(rl[i] - rmax);
+      wl[i] = __expf(wl[i] - wmax);
+      rsum += rl[i];
+      wsum += wl[i];
+    }
+    const float rinv = 1.f / warp_sum(rsum), winv = 1.f / warp_sum(wsum);
+    float cw[4], kap[4], rho[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      cw[i] = rl[i] * rinv;
+      float r = expf(-dt * (rate * inv_tau[i]));
+      r = fminf(fmaxf(r, 1e-6f), 1.f - 1e-6f);
+      float k = (1.f - r) * (wl[i] * winv);
+      if (a.mask) { k *= keep; r = r * keep + (1.f - keep); }
+      kap[i] = k;
+      rho[i] = r;
+    }
+    const int64_t obase = (bh * a.L + l) * M + 4 * lane;
+    __stcs(reinterpret_cast<float4 *>(a.rho + obase), make_float4(rho[0], rho[1], rho[2], rho[3]));
+    if (a.ck_dt == FRACSSM_F32) {
+      __stcs(reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.c) + obase), make_float4(cw[0], cw[1], cw[2], cw[3]));
+      __stcs(reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.kappa) + obase),
+             make_float4(kap[0], kap[1], kap[2], kap[3]));
+    } else {  // bf16
+      const __nv_bfloat162 c0 = __floats2bfloat162_rn(cw[0], cw[1]), c1 = __floats2bfloat162_rn(cw[2], cw[3]);
+      const __nv_bfloat162 k0 = __floats2bfloat162_rn(kap[0], kap[1]), k1 = __floats2bfloat162_rn(kap[2], kap[3]);
+      __stcs(reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(a.c) + obase),
+             make_uint2(*reinterpret_cast<const uint32_t *>(&c0), *reinterpret_cast<const uint32_t *>(&c1)));
+      __stcs(reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(a.kappa) + obase),
+             make_uint2(*reinterpret_cast<const uint32_t *>(&k0), *reinterpret_cast<const uint32_t *>(&k1)));
+    }
+    const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
+    for (int64_t r = lane; r < R; r += 32)
+      st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -252,12 +346,12 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
                                       const float *dt_bias, const float *base_log_tau,
                                       float read_gate_logit, float write_gate_logit, float read_temp,
                                       float dt_min, float dt_max, float alpha_min, float alpha_max,
-                                      float lambda_min, float lambda_max, void *u, float *c,
-                                      float *kappa, float *rho, int64_t Bt, int64_t L, int64_t H,
-                                      int64_t R, int64_t M, void *stream) {
+                                      float lambda_min, float lambda_max, void *u, void *c,
+                                      void *kappa, int ck_dtype, float *rho, int64_t Bt, int64_t L,
+                                      int64_t H, int64_t R, int64_t M, void *stream) {
   using namespace fracssm;
   if (Bt < 0 || L < 0 || H <= 0 || R <= 0 || M <= 0) return fail(FRACSSM_ERR_ARG, "compute_params: bad sizes");
-  if (!known_dtype(dyn_dtype) || !known_dtype(rw_dtype) || !known_dtype(x_dtype))
+  if (!known_dtype(dyn_dtype) || !known_dtype(rw_dtype) || !known_dtype(x_dtype) || !known_dtype(ck_dtype))
     return fail(FRACSSM_ERR_ARG, "compute_params: unsupported dtype");
   if (Bt == 0 || L == 0) return FRACSSM_OK;
   if (!dyn || !rw || !x_conv || !dt_bias || !base_log_tau || !u || !c || !kappa || !rho)
@@ -274,8 +368,15 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
   a.inv_read_temp = 1.f / read_temp;
   a.dt_min = dt_min; a.dt_max = dt_max; a.a_min = alpha_min; a.a_max = alpha_max;
   a.l_min = lambda_min; a.l_max = lambda_max;
-  a.u = u; a.c = c; a.kappa = kappa; a.rho = rho;
+  a.u = u; a.c = c; a.kappa = kappa; a.ck_dt = ck_dtype; a.rho = rho;
   a.L = L; a.H = H; a.R = R; a.M = M;
+  auto al = [](const void *p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+  if (M == 128 && rw_dtype == FRACSSM_BF16 && (ck_dtype == FRACSSM_F32 || ck_dtype == FRACSSM_BF16) && al(rw, 8) &&
+      rw_sb % 4 == 0 && rw_sl % 4 == 0 && al(c, 16) && al(kappa, 16) && al(rho, 16)) {
+    dim3 grid((unsigned)ceil_div(L, 4 * kPrepTokens), (unsigned)(Bt * H));
+    compute_params_m128_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    return check_launch("compute_params");
+  }
   dim3 grid((unsigned)ceil_div(L, 4), (unsigned)(Bt * H));
   compute_params_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(a);
   return check_launch("compute_params");

@@ -46,7 +46,7 @@ _SIGNATURES = {
     "fracssm_scan_fused_phase_cycles": (ci, [vp, vp, vp]),
     "fracssm_compute_params": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, ci, i64, i64,
                                     vp, i64, i64, vp, vp, cf, cf, cf, cf, cf, cf, cf, cf, cf,
-                                    vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
+                                    vp, vp, vp, ci, vp, i64, i64, i64, i64, i64, vp]),
     "fracssm_skip_mix": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, vp, ci, i64, i64, i64, i64, vp]),
     "fracssm_rmsnorm_gated": (ci, [vp, i64, vp, i64, ci, vp, ci, cf, vp, vp, i64, i64, vp]),
     "fracssm_selftest_umma_m64": (ci, [vp, vp, vp, vp, ci, vp]),

@@ -15,9 +15,10 @@ from .. import _cabi as C
 def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, read_residual_logit,
                                     write_residual_scale, base_log_tau, num_heads, head_dim,
                                     num_modes, read_temp, dt_min, dt_max, alpha_min, alpha_max,
-                                    lambda_min, lambda_max):
+                                    lambda_min, lambda_max, coeff_dtype=torch.float32):
     """Elementwise part: dyn [B,L,3H], rw [B,L,2HM], x_conv [B,L,HR] ->
-    (u [BH,L,R] in x_conv.dtype, c, kappa, rho [BH,L,M] float32), head-major."""
+    (u [BH,L,R] in x_conv.dtype, c, kappa [BH,L,M] in `coeff_dtype`, rho [BH,L,M] float32),
+    head-major.  The reference emits float32 coefficients; bfloat16 halves what the scan reads."""
     assert dyn.dim() == 3 and rw.dim() == 3 and x_conv.dim() == 3, "dyn, rw and x_conv must be 3D"
     assert dyn.is_cuda and rw.is_cuda and x_conv.is_cuda, "inputs must be on CUDA"
     B, L, _ = x_conv.shape
@@ -32,9 +33,9 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
         assert attention_mask.shape == (B, L), "attention_mask shape must be (B, L)"
         mask = attention_mask.to(device=dev, dtype=torch.float32)
     u = torch.empty(B * H, L, R, device=dev, dtype=x_conv.dtype)
-    c = torch.empty(B * H, L, M, device=dev, dtype=torch.float32)
+    c = torch.empty(B * H, L, M, device=dev, dtype=coeff_dtype)
     kappa = torch.empty_like(c)
-    rho = torch.empty_like(c)
+    rho = torch.empty(B * H, L, M, device=dev, dtype=torch.float32)
     if B == 0 or L == 0:
         return u, c, kappa, rho
     dtb = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
@@ -46,7 +47,7 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
             C.ptr(mask), 0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1),
             C.ptr(dtb), C.ptr(ltau), float(read_residual_logit), float(write_residual_scale),
             float(read_temp), float(dt_min), float(dt_max), float(alpha_min), float(alpha_max),
-            float(lambda_min), float(lambda_max), C.ptr(u), C.ptr(c), C.ptr(kappa), C.ptr(rho),
+            float(lambda_min), float(lambda_max), C.ptr(u), C.ptr(c), C.ptr(kappa), C.dt(c), C.ptr(rho),
             B, L, H, R, M, C.stream_of(x_conv)), "compute_params")
     return u, c, kappa, rho
 

@@ -104,6 +104,9 @@ class FracMixer(nn.Module):
         self.out_proj = nn.Linear(self.inner_dim, self.hidden_size, bias=False)
         self.D = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
         self._gates = None  # (version key, read logit, write logit) as Python floats: no sync per call
+        # dtype of the scan coefficients c / kappa: None = float32 as in the reference; torch.bfloat16
+        # halves the scan's coefficient traffic (the benchmark's headline configuration)
+        self.coeff_dtype = None
 
     def _gate_logits(self):
         key = (self.read_residual_logit._version, self.write_residual_scale._version,
@@ -120,13 +123,17 @@ class FracMixer(nn.Module):
         return compute_params_from_projections(
             dyn, rw, x_conv, attention_mask, self.dt_bias, read_logit, write_logit, self.base_log_tau,
             self.num_heads, self.head_dim, self.num_modes, self.read_temp, cfg.frac_dt_min, cfg.frac_dt_max,
-            cfg.frac_alpha_min, cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max)
+            cfg.frac_alpha_min, cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max,
+            coeff_dtype=torch.float32 if self.coeff_dtype is None else self.coeff_dtype)
 
     def _conv_state_after(self, x, attention_mask):
         """The last K-1 (masked) inputs, channels first, zero-padded on the left."""
         keep = self.conv_kernel - 1
-        xt = x if attention_mask is None else x * attention_mask[..., None].to(x.dtype)
-        tail = xt[:, max(x.shape[1] - keep, 0):].transpose(1, 2)
+        first = max(x.shape[1] - keep, 0)
+        tail = x[:, first:]
+        if attention_mask is not None:
+            tail = tail * attention_mask[:, first:, None].to(x.dtype)
+        tail = tail.transpose(1, 2)
         return F.pad(tail, (keep - tail.shape[-1], 0)).contiguous()
 
     def forward(self, hidden_states, attention_mask=None, layer_past=None, use_cache=False):

@@ -183,7 +183,8 @@ int fracssm_scan_fused_phase_cycles(const void *workspace, long long *out16, voi
  * dyn [Bt, L, 3H] (dt, alpha, lambda logits), rw [Bt, L, 2*H*M] (read then write residuals),
  * x_conv [Bt, L, H*R]; mask [Bt, L] f32 or NULL; dt_bias [H], base_log_tau [M] f32;
  * read_gate_logit, write_gate_logit: the two scalar parameters (sigmoid is applied here).
- * Outputs head-major: u [Bt*H, L, R] (x dtype), c, kappa, rho [Bt*H, L, M] f32.
+ * Outputs head-major: u [Bt*H, L, R] (x dtype), rho [Bt*H, L, M] f32, c and kappa [Bt*H, L, M] in
+ * ck_dtype (f32 is what the reference emits; bf16 halves the scan's coefficient traffic).
  * Replaces the kernel behind frac_ssm/layers/compute_params.py:583
  * `frac_compute_scan_params(model, x_conv, x, attention_mask)` (:165-213).
  */
@@ -194,8 +195,8 @@ int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64
                            const float *base_log_tau, float read_gate_logit,
                            float write_gate_logit, float read_temp, float dt_min, float dt_max,
                            float alpha_min, float alpha_max, float lambda_min, float lambda_max,
-                           void *u, float *c, float *kappa, float *rho, int64_t Bt, int64_t L,
-                           int64_t H, int64_t R, int64_t M, void *stream);
+                           void *u, void *c, void *kappa, int ck_dtype, float *rho, int64_t Bt,
+                           int64_t L, int64_t H, int64_t R, int64_t M, void *stream);
 
 /*
  * out[b, l, h*R + r] = mixed_flat[b*H + h, l, r] + x_conv[b, l, h*R + r] * D[h, r].

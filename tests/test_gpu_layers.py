@@ -72,6 +72,38 @@ def test_compute_params_larger(dtype):
         assert_ref_error(a, b, c_, 1e-4)
 
 
+@pytest.mark.parametrize("coeff", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("masked", [False, True])
+def test_compute_params_128_modes_one_pass_kernel(coeff, masked):
+    """bf16 projections with 128 modes take the vectorised one-pass kernel; L = 77 leaves a ragged
+    group of tokens; the projections are strided views (as slices of a wider buffer)."""
+    from frac_ssm_b200.layers import compute_params_from_projections
+    B, L, H, R, M = 3, 77, 5, 64, 128
+    g = torch.Generator().manual_seed(9)
+    dyn = torch.randn(B, L, 3 * H, generator=g).bfloat16()
+    rw_wide = torch.randn(B, L, 2 * H * M + 8, generator=g).bfloat16()
+    rw = rw_wide[..., :2 * H * M]
+    x = torch.randn(B, L, H * R, generator=g).bfloat16()
+    mask = None
+    if masked:
+        mask = torch.ones(B, L)
+        mask[0, :10] = 0
+        mask[2, 50:] = 0
+    dt_bias = torch.randn(H, generator=g)
+    log_tau = torch.linspace(0.0, 11.09, M)
+    args = (dt_bias, torch.tensor([-2.0]), torch.tensor([-1.1]), log_tau, H, R, M, 1.0, *CFG.values())
+    out = compute_params_from_projections(dyn.cuda(), rw_wide.cuda()[..., :2 * H * M], x.cuda(),
+                                          None if mask is None else mask.cuda(), dt_bias.cuda(), -2.0, -1.1,
+                                          log_tau.cuda(), H, R, M, 1.0, *CFG.values(), coeff_dtype=coeff)
+    ref = O.compute_params(dyn.double(), rw.double(), x, mask, *args, exact=True)
+    assert out[1].dtype == coeff and out[2].dtype == coeff and out[3].dtype == torch.float32
+    assert torch.equal(out[0].cpu(), x.view(B, L, H, R).permute(0, 2, 1, 3).reshape(B * H, L, R))
+    tol = TOL_F32 if coeff == torch.float32 else dict(rtol=1e-2, atol=1e-4)
+    close(out[1], ref[1], **tol)
+    close(out[2], ref[2], **tol)
+    close(out[3], ref[3], **TOL_F32)
+
+
 def test_skip_mix_on_golden(golden_dir):
     from frac_ssm_b200.layers import frac_skip_mix
     g = _golden(golden_dir)

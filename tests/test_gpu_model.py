@@ -57,6 +57,12 @@ def test_bf16_model_takes_the_single_pass_scan(golden_dir):
     ref = g["logits"]
     err = (logits.float().cpu() - ref).abs().max().item()
     assert err <= 0.03 * ref.abs().max().item(), err
+    # bfloat16 scan coefficients (the benchmark's configuration): same bound
+    for layer in model.model.layers:
+        layer.mixer.coeff_dtype = torch.bfloat16
+    logits2, _ = model(g["input_ids"][:, :L].cuda(), use_cache=True)
+    err2 = (logits2.float().cpu() - ref).abs().max().item()
+    assert err2 <= 0.03 * ref.abs().max().item(), err2
 
 
 @pytest.mark.parametrize("dtype,C_,K", [(torch.bfloat16, 1536, 4), (torch.float32, 100, 4), (torch.bfloat16, 72, 3),
