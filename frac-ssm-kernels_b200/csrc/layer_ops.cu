@@ -111,14 +111,22 @@ __global__ void __launch_bounds__(128) compute_params_m128_kernel(const ParamArg
   const float dtb = a.dt_bias[h];
   const __nv_bfloat16 *rw = reinterpret_cast<const __nv_bfloat16 *>(a.rw);
   const int64_t l1 = min(l0 + kPrepTokens, a.L);
-  for (int64_t l = l0; l < l1; ++l) {
-    const int64_t dbase = b * a.dyn_sb + l * a.dyn_sl;
-    float dt = softplusf_(ld_f32(a.dyn, dbase + h, a.dyn_dt) + dtb);
-    dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
-    const float alpha = a.a_min + sigmoidf_(ld_f32(a.dyn, dbase + H + h, a.dyn_dt)) * (a.a_max - a.a_min);
+  // the per-token scalars (step, alpha, rate, mask) are computed once, by lane t for token l0 + t,
+  // and handed to the other lanes by shuffles
+  float dt_l = 0.f, alpha_l = 0.f, rate_l = 0.f, keep_l = 1.f;
+  if (lane < kPrepTokens && l0 + lane < l1) {
+    const int64_t l = l0 + lane, dbase = b * a.dyn_sb + l * a.dyn_sl;
+    dt_l = softplusf_(ld_f32(a.dyn, dbase + h, a.dyn_dt) + dtb);
+    dt_l = fminf(fmaxf(dt_l, a.dt_min), a.dt_max);
+    alpha_l = a.a_min + sigmoidf_(ld_f32(a.dyn, dbase + H + h, a.dyn_dt)) * (a.a_max - a.a_min);
     const float lam = a.l_min + sigmoidf_(ld_f32(a.dyn, dbase + 2 * H + h, a.dyn_dt)) * (a.l_max - a.l_min);
-    const float rate = powf(fmaxf(lam, 1e-4f), 1.f / fmaxf(alpha, 1e-4f));
-    const float keep = a.mask ? a.mask[b * a.m_sb + l * a.m_sl] : 1.f;
+    rate_l = powf(fmaxf(lam, 1e-4f), 1.f / fmaxf(alpha_l, 1e-4f));
+    if (a.mask) keep_l = a.mask[b * a.m_sb + l * a.m_sl];
+  }
+  for (int64_t l = l0; l < l1; ++l) {
+    const int src = static_cast<int>(l - l0);
+    const float dt = __shfl_sync(0xffffffffu, dt_l, src), alpha = __shfl_sync(0xffffffffu, alpha_l, src);
+    const float rate = __shfl_sync(0xffffffffu, rate_l, src), keep = __shfl_sync(0xffffffffu, keep_l, src);
 
     const __nv_bfloat16 *rp = rw + b * a.rw_sb + l * a.rw_sl + h * M + 4 * lane;
     float rres[4], wres[4], rl[4], wl[4];

@@ -192,22 +192,32 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 #pragma unroll 1
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
+      // The next ticket is taken a tile ahead (the workers read it in the second half of this tile,
+      // and its inputs are pulled into L2 now) and published through item_bar.  In the first tile of
+      // a CTA this has to wait until the workers have read the first item, i.e. until their arrival
+      // on full[0]: two completions of item_bar in a row would flip its parity twice, and a worker
+      // that had not looked yet would wait for a phase that never comes.  From the second tile on
+      // every worker has read item n before the control warp can get here (the read precedes the
+      // worker's arrival on out_bar of the previous tile).
       int next = 0;
-      if (lane == 0) {  // take the next ticket now: the workers prefetch it during this tile
-        next = atomicAdd(&a.ctrl[0], 1);
-        items[(n + 1) & 1] = next;
-        umma::mbar_arrive(item_bar);
-      }
-      next = __shfl_sync(0xffffffffu, next, 0);
-      if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
-        const int nj = next / a.BH, nb = next - nj * a.BH;
-        const int ntok = min(kTile, a.L - nj * kTile);
-        const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
-        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
-        constexpr int kCkBytes = CKF32 ? 4 : 2;
-        umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
-        umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
-      }
+      auto take_next = [&]() {
+        if (lane == 0) {
+          next = atomicAdd(&a.ctrl[0], 1);
+          items[(n + 1) & 1] = next;
+          umma::mbar_arrive(item_bar);
+        }
+        next = __shfl_sync(0xffffffffu, next, 0);
+        if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
+          const int nj = next / a.BH, nb = next - nj * a.BH;
+          const int ntok = min(kTile, a.L - nj * kTile);
+          const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
+          umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
+          constexpr int kCkBytes = CKF32 ? 4 : 2;
+          umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
+          umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
+        }
+      };
+      if (n > 0) take_next();
       if (n > 0) { FRACSSM_WAIT(barH, n - 1); }  // every MMA of the previous tile has finished
       if (lane == 0) {
         umma::mbar_expect_tx(barU, kTile * kR * 2);
@@ -220,6 +230,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         piece(kColBase, sA0, false, sA0 + kTileBytes, false, 1024, kIdKK128, 0u);
         umma::mma_commit(cb + 0);
       }
+      if (n == 0) take_next();
       // levels 8 and 16 (area1): first halves are picked by the B descriptor's row-group stride
       FRACSSM_WAIT(full + 1, n);
       umma::tc_fence_after();

@@ -92,27 +92,36 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
 #pragma unroll 1
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
+      // The next ticket is taken a tile ahead and published through item_bar.  For the first tile it
+      // has to wait until the workers have read the first item (their arrival on `full`): two
+      // completions of item_bar in a row would flip its parity twice, and a worker that had not
+      // looked yet would wait for a phase that never comes.  From the second tile on the workers have
+      // read item n before the control warp can get here (their out_bar arrival comes after it).
       int next = 0;
-      if (lane == 0) {
-        next = atomicAdd(&a.ctrl[0], 1);
-        items[(n + 1) & 1] = next;
-        umma::mbar_arrive(item_bar);
-      }
-      next = __shfl_sync(0xffffffffu, next, 0);
-      if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
-        const int nj = next / a.BH, nb = next - nj * a.BH;
-        const int ntok = min(kTile, a.L - nj * kTile);
-        const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
-        constexpr int kKb = KF32 ? 4 : 2;
-        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
-        umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kKb, ntok * kM * kKb);
-      }
+      auto take_next = [&]() {
+        if (lane == 0) {
+          next = atomicAdd(&a.ctrl[0], 1);
+          items[(n + 1) & 1] = next;
+          umma::mbar_arrive(item_bar);
+        }
+        next = __shfl_sync(0xffffffffu, next, 0);
+        if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
+          const int nj = next / a.BH, nb = next - nj * a.BH;
+          const int ntok = min(kTile, a.L - nj * kTile);
+          const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
+          constexpr int kKb = KF32 ? 4 : 2;
+          umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
+          umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kKb, ntok * kM * kKb);
+        }
+      };
+      if (n > 0) take_next();
       if (n > 0) { FRACSSM_WAIT(cb, n - 1); }  // the previous tile's MMAs no longer read u
       if (lane == 0) {
         umma::mbar_expect_tx(barU, kTile * kR * 2);
         umma::tma_load_3d(u_tile, &u_map, barU, 0, j * kTile, bh);
       }
       FRACSSM_WAIT(full, n);
+      if (n == 0) take_next();
       FRACSSM_WAIT(barU, n);
       umma::tc_fence_after();
       if (lane == 0) {

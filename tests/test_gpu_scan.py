@@ -238,3 +238,31 @@ def test_scan_inside_torch_compile_fullgraph(scan):
     with pytest.raises((NotImplementedError, RuntimeError)):
         ug = u.float().requires_grad_()          # forward only: gradients are refused
         scan(ug, c.float(), kappa.float(), rho, 256).sum().backward()
+
+
+@pytest.mark.parametrize("B,L,ckdt", [(148, 256, torch.bfloat16), (16, 128, torch.bfloat16),
+                                      (300, 257, torch.bfloat16), (96, 1024, torch.float32)])
+def test_no_device_wait_runs_out_in_back_to_back_launches(B, L, ckdt):
+    """Many launches queued without a host synchronisation, with other kernels in between (as inside
+    a model): afterwards no launch may have recorded a device-side wait that ran out.  Guards the
+    hand-over protocol of the single-pass kernel at CTA start-up, where a barrier once completed
+    twice before a slow warp had looked at it."""
+    import importlib
+    FS = importlib.import_module("frac_ssm_b200.ops.b200.frac_scan")
+    g = torch.Generator(device="cuda").manual_seed(B + L)
+    u = (0.25 * torch.randn(B, L, 64, device="cuda", generator=g)).bfloat16()
+    c = torch.softmax(torch.randn(B, L, 128, device="cuda", generator=g), -1).to(ckdt)
+    k = (0.1 * torch.softmax(torch.randn(B, L, 128, device="cuda", generator=g), -1)).to(ckdt)
+    rho = torch.rand(B, L, 128, device="cuda", generator=g).clamp(1e-6, 1 - 1e-6)
+    filler = torch.randn(2048, 2048, device="cuda", dtype=torch.bfloat16)
+    spaces, first = [], None
+    for it in range(120):
+        h = FS.frac_scan(u, c, k, rho, 256, None, False, path="fused", keep_workspace=True)
+        spaces.append(FS._last_ws)
+        first = h if first is None else first
+        if it % 3 == 0:
+            filler = (filler @ filler) * 1e-3
+    torch.cuda.synchronize()
+    failed = sum(int(ws[:8].view(torch.int32)[1].item() != 0) for ws in spaces)
+    assert failed == 0, f"{failed} of {len(spaces)} launches had a device-side wait run out"
+    assert torch.equal(h, first)
