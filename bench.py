@@ -443,9 +443,13 @@ def main():
                     help="also print every timed step's scan-kernel time to stderr (diagnostic)")
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a stalled run dumps its Python stacks and exits (0 = off)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch the timed steps one by one instead of replaying a captured CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
+    if args.phases:             # selects the kernel build that records per-phase cycles (about 7 % slower)
+        os.environ["FRACSSM_SCAN_PROFILE"] = "1"
     if args.watchdog > 0:      # a stalled run must end with a traceback, not run until someone kills it
         import faulthandler
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
@@ -520,21 +524,53 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
+    # One step captured as a CUDA graph (workspace clear + scan kernel + epilogue kernel), replayed
+    # K times in the timed region: host-side jitter (other processes on the box, the sampler thread)
+    # then cannot starve the GPU between launches.  If capture is not possible the K steps are
+    # launched one by one, as in the per-kernel pass below.
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y = step()
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:      # noqa: BLE001 - any capture problem falls back to plain launches
+            print(f"bench: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    barrier()
     sampler.reset()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    scan_evs = []
     e0.record()
     for _ in range(args.steps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        h = frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path)
-        b.record()
-        scan_evs.append((a, b))
-        y = scan_epilogue(h, d["x_conv"], d["z"], d["D"], d["w"], H, R, 1e-6)
+        if graph is not None:
+            graph.replay()
+        else:
+            y = step()
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = e0.elapsed_time(e1) / args.steps
+    # per-kernel pass (plain launches, CUDA events around the scan kernel of every step)
+    scan_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for _ in range(args.steps)]
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for a, b in scan_evs:
+        a.record()
+        h = frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path)
+        b.record()
+        y = scan_epilogue(h, d["x_conv"], d["z"], d["D"], d["w"], H, R, 1e-6)
+    p1.record()
+    barrier()
+    ms_plain = p0.elapsed_time(p1) / args.steps
     scan_times = [a.elapsed_time(b) for a, b in scan_evs]
     scan_ms = statistics.mean(scan_times)
     scan_ms_median = statistics.median(scan_times)
@@ -612,7 +648,10 @@ def main():
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
                 "tokens_per_s_per_gpu": value / world, "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-                "scan_path": "fused" if use_fused else "staged"}
+                "scan_path": "fused" if use_fused else "staged",
+                "timed_launch": ("CUDA graph of one step, replayed once per step" if graph is not None
+                                 else "plain launches"),
+                "ms_per_step_plain_launches": ms_plain}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -32,6 +32,7 @@
 // accumulator of the one level that holds it.  Chat / Khat are the same factors taken to the
 // tile's start / end; Khat is split into bf16 high and low parts so that the state keeps
 // float32-level accuracy.
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -108,7 +109,10 @@ __device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a
   }
 }
 
-template <bool CKF32>
+// PROF: worker thread 0 of each CTA also charges its cycles to 16 phases of the tile loop (a
+// diagnostic build of the same kernel: the bookkeeping costs about 7 % of the run time, because the
+// one warp that does it is on every hand-over's critical path).
+template <bool CKF32, bool PROF>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -314,7 +318,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     // worker thread 0 charges the cycles since the last mark to a phase (diagnostic)
     long long t_mark = clock64();
 #define FRACSSM_MARK(phase)                         \
-  if (tid == 0) {                                   \
+  if (PROF && tid == 0) {                           \
     const long long now_ = clock64();               \
     prof[phase] += now_ - t_mark;                   \
     t_mark = now_;                                  \
@@ -605,7 +609,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       item = next;
     }
     if (n_tiles_done > 0) write_rows(n_tiles_done - 1);
-    if (tid == 0 && a.prof && blockIdx.x < kProfCtas) {
+    if (PROF && tid == 0 && a.prof && blockIdx.x < kProfCtas) {
       for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
     }
   }
@@ -653,8 +657,10 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   {
     std::lock_guard<std::mutex> lock(mu);
     if (sm_count[dev] == 0) {
-      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true>));
+      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, true>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, true>));
       if (prc) return prc;
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -687,8 +693,14 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + kProfBytes + align256((size_t)B * 4), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
-  if (ckf32) scan_fused_kernel<true><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
-  else scan_fused_kernel<false><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
+  // FRACSSM_SCAN_PROFILE=1 in the environment selects the build that records per-phase cycles
+  const char *pe = getenv("FRACSSM_SCAN_PROFILE");
+  const bool prof = pe && pe[0] != '\0' && pe[0] != '0';
+  const cudaStream_t st = (cudaStream_t)stream;
+  if (ckf32 && prof) scan_fused_kernel<true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  else if (ckf32) scan_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  else if (prof) scan_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  else scan_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
   return check_launch("frac_scan (single-pass kernel)");
 }
 
