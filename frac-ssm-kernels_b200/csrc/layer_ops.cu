@@ -238,6 +238,62 @@ rmsnorm_gated_kernel(const void *__restrict__ x, int64_t x_srow, const void *__r
   }
 }
 
+__device__ __forceinline__ void unpack8(const uint4 &p, float (&f)[8]) {
+  const uint32_t wds[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(wds[i] << 16);
+    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
+  }
+}
+
+// bf16 fast path: one warp per row, the row (up to 2048 elements) held in registers as 16-byte
+// pieces, so x and the gate are read once; four rows per block.
+__global__ void __launch_bounds__(128)
+rmsnorm_gated_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_srow,
+                          const __nv_bfloat16 *__restrict__ gate, int64_t g_srow, const void *__restrict__ w,
+                          int w_dt, float eps, __nv_bfloat16 *__restrict__ y, float *__restrict__ rstd,
+                          int64_t rows, int64_t D) {
+  const int lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 4 + threadIdx.x / 32;
+  if (row >= rows) return;
+  const int chunks = static_cast<int>(D / 8);
+  float v[8][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = lane + 32 * i;
+    if (ch < chunks) {
+      unpack8(__ldcs(reinterpret_cast<const uint4 *>(x + row * x_srow) + ch), v[i]);
+      if (gate) {
+        float z[8];
+        unpack8(__ldcs(reinterpret_cast<const uint4 *>(gate + row * g_srow) + ch), z);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] *= z[e] * sigmoidf_(z[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[i][e], v[i][e], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / (float)D + eps);
+  if (rstd && lane == 0) rstd[row] = rs;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = lane + 32 * i;
+    if (ch < chunks) {
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(v[i][2 * e] * rs * ld_f32(w, 8 * ch + 2 * e, w_dt),
+                                                       v[i][2 * e + 1] * rs * ld_f32(w, 8 * ch + 2 * e + 1, w_dt));
+        o[e] = *reinterpret_cast<const uint32_t *>(&t);
+      }
+      __stcs(reinterpret_cast<uint4 *>(y + row * D) + ch, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+}
+
 // Modes of the epilogue kernels.  With the heads of a layer spread over several GPUs the norm spans
 // columns on other GPUs: each GPU first computes its own sum of squares per (b, l) row (partial), the
 // sums are added across GPUs, and a second pass normalises with the total (apply).
@@ -285,14 +341,6 @@ scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t
 
 // bf16 fast path of the epilogue: one block per (b, l) row, 8 elements (16 bytes) per thread held
 // in registers, so every tensor is read once and written once.
-__device__ __forceinline__ void unpack8(const uint4 &p, float (&f)[8]) {
-  const uint32_t wds[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(wds[i] << 16);
-    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
-  }
-}
 
 __global__ void __launch_bounds__(1024)
 scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int64_t h_sl,
@@ -413,6 +461,14 @@ extern "C" int fracssm_rmsnorm_gated(const void *x, int64_t x_srow, const void *
   if (!known_dtype(xg_dtype) || !known_dtype(w_dtype)) return fail(FRACSSM_ERR_ARG, "rmsnorm_gated: unsupported dtype");
   if (rows == 0) return FRACSSM_OK;
   if (!x || !weight || !y) return fail(FRACSSM_ERR_ARG, "rmsnorm_gated: null pointer");
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (xg_dtype == FRACSSM_BF16 && D % 8 == 0 && D <= 2048 && al16(x) && al16(y) && x_srow % 8 == 0 &&
+      (!gate || (al16(gate) && g_srow % 8 == 0))) {
+    rmsnorm_gated_bf16_kernel<<<(unsigned)ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16 *>(x), x_srow, reinterpret_cast<const __nv_bfloat16 *>(gate), g_srow,
+        weight, w_dtype, eps, reinterpret_cast<__nv_bfloat16 *>(y), rstd, rows, D);
+    return check_launch("rmsnorm_gated");
+  }
   rmsnorm_gated_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
       x, x_srow, gate, g_srow, xg_dtype, weight, w_dtype, eps, y, rstd, D);
   return check_launch("rmsnorm_gated");

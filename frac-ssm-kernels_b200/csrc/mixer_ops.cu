@@ -12,7 +12,7 @@ namespace {
 __device__ __forceinline__ float silu_(float x) { return x / (1.f + __expf(-x)); }
 
 constexpr int kConvMaxK = 8;     // kernel widths 1..8
-constexpr int kConvTokens = 64;  // tokens per thread: the window slides in registers
+constexpr int kConvTokens = 16;  // tokens per thread: the window slides in registers
 
 // General path: one channel per thread, any dtype.  grid (ceil(C/128), ceil(L/kConvTokens), B).
 __global__ void __launch_bounds__(128)

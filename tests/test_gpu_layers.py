@@ -145,6 +145,24 @@ def test_rmsnorm_gated_shapes(rows, D):
     close(rstd, torch.rsqrt(v.pow(2).mean(-1) + 1e-5), **TOL_F32)
 
 
+@pytest.mark.parametrize("rows,D,gated", [(1, 768, False), (37, 768, True), (130, 1536, True), (5, 2048, False),
+                                          (9, 8, True), (3, 2056, True)])
+def test_rmsnorm_bf16_row_in_registers(rows, D, gated):
+    """Widths up to 2048 in bf16 take the warp-per-row kernel (2056 falls back to the general one);
+    x and the gate are strided row views."""
+    from frac_ssm_b200.modules import rmsnorm_gated_fwd
+    g = torch.Generator().manual_seed(rows + D)
+    both = torch.randn(rows, 2 * D, generator=g).bfloat16()
+    x, z = both[:, :D], both[:, D:]
+    w = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16()
+    bc = both.cuda()
+    y, rstd = rmsnorm_gated_fwd(bc[:, :D], w.cuda(), bc[:, D:] if gated else None, 1e-6)
+    ref = O.rmsnorm_gated(x, w, z if gated else None, 1e-6, exact=True)
+    close(y, ref, **TOL_BF16)
+    v = x.double() * F.silu(z.double()) if gated else x.double()
+    close(rstd, torch.rsqrt(v.pow(2).mean(-1) + 1e-6), **TOL_F32)
+
+
 def test_scan_epilogue_matches_unfused_pair():
     from frac_ssm_b200.layers import scan_epilogue
     B, L, H, R = 2, 50, 24, 64
