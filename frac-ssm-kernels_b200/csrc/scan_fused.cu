@@ -463,20 +463,21 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
               make_float4(g8[0] * f[0].x, g8[1] * f[0].y, g8[2] * f[1].x, g8[3] * f[1].y);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float2 ch[2], cl[2], kh[2];
+          float2 cl[2], kl[2];
+          uint32_t pch[2], pkh[2];  // the high parts, already packed
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             const float2 chat = __fmul2_rn(cp[i][hf], e[hf]);
-            ch[hf] = bf16_round2(chat);
-            cl[hf] = __fadd2_rn(chat, make_float2(-ch[hf].x, -ch[hf].y));
+            const float2 ch = bf16_round2(chat, pch[hf]);
+            cl[hf] = __fadd2_rn(chat, make_float2(-ch.x, -ch.y));
             const float2 full_k = __fmul2_rn(ks[i][hf], f[hf]);
-            kh[hf] = bf16_round2(full_k);
-            ks[i][hf] = __fadd2_rn(full_k, make_float2(-kh[hf].x, -kh[hf].y));  // low part
+            const float2 kh = bf16_round2(full_k, pkh[hf]);
+            kl[hf] = __fadd2_rn(full_k, make_float2(-kh.x, -kh.y));
           }
-          emit_row(sArea0, th_off, c16, i, ch[0], ch[1]);
+          emit_row_packed(sArea0, th_off, c16, i, pch[0], pch[1]);
           emit_row(sArea1, th_off, c16, i, cl[0], cl[1]);
-          emit_row(sArea0 + kTileBytes, th_off, c16, i, kh[0], kh[1]);
-          emit_row(sArea1 + kTileBytes, th_off, c16, i, ks[i][0], ks[i][1]);
+          emit_row_packed(sArea0 + kTileBytes, th_off, c16, i, pkh[0], pkh[1]);
+          emit_row(sArea1 + kTileBytes, th_off, c16, i, kl[0], kl[1]);
         }
       }
       warp_arrive(full + 3, lane);
@@ -547,18 +548,16 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       // incoming state as MMA operands, bf16 high / low parts
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        float hi[8], lo[8];
+        uint32_t ph[4], pl[4];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          hi[x] = __bfloat162float(__float2bfloat16_rn(sj[8 * half + x]));
-          lo[x] = sj[8 * half + x] - hi[x];
+        for (int x = 0; x < 4; ++x) {
+          const float2 v = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
+          const float2 hi = bf16_round2(v, ph[x]);
+          pl[x] = pack2(v.x - hi.x, v.y - hi.y);
         }
-        uint4 pk, pl;
-        pk.x = pack2(hi[0], hi[1]); pk.y = pack2(hi[2], hi[3]); pk.z = pack2(hi[4], hi[5]); pk.w = pack2(hi[6], hi[7]);
-        pl.x = pack2(lo[0], lo[1]); pl.y = pack2(lo[2], lo[3]); pl.z = pack2(lo[4], lo[5]); pl.w = pack2(lo[6], lo[7]);
         const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-        *reinterpret_cast<uint4 *>(s_tile + off) = pk;
-        *reinterpret_cast<uint4 *>(slo_tile + off) = pl;
+        *reinterpret_cast<uint4 *>(s_tile + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+        *reinterpret_cast<uint4 *>(slo_tile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
       }
       warp_arrive(full + 5, lane);
       FRACSSM_MARK(10)

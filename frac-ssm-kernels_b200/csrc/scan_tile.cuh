@@ -35,6 +35,18 @@ __device__ __forceinline__ void emit_row(uint32_t tile_s, uint32_t th_off, uint3
                "r"(*reinterpret_cast<const uint32_t *>(&b))
                : "memory");
 }
+// Store four consecutive modes that are already packed bf16 pairs (no second conversion).
+__device__ __forceinline__ void emit_row_packed(uint32_t tile_s, uint32_t th_off, uint32_t c16, int i, uint32_t w0,
+                                                uint32_t w1) {
+  const uint32_t addr = tile_s + th_off + i * 128 + (c16 ^ (static_cast<uint32_t>(i) << 4));
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(w0), "r"(w1) : "memory");
+}
+// Both components rounded to bf16: the packed pair, and the same values as floats.
+__device__ __forceinline__ float2 bf16_round2(float2 v, uint32_t &packed) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
+  packed = *reinterpret_cast<const uint32_t *>(&t);
+  return make_float2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xFFFF0000u));
+}
 __device__ __forceinline__ float2 bf16_round2(float2 v) {  // each component rounded to bf16, as floats
   const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
   const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
