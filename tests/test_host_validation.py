@@ -46,3 +46,28 @@ def test_stage_messages(fn, args, pattern):
 def test_cute_backend_is_reported_absent():
     ok, why = ops.cute_supported()
     assert not ok and "b200" in why
+
+
+def test_layer_and_mixer_wrappers_refuse_cpu_tensors():
+    """No CPU fallback anywhere: the layer / mixer wrappers refuse host tensors before touching the library."""
+    from frac_ssm_b200.layers import scan_epilogue, scan_epilogue_apply, scan_epilogue_sumsq
+    from frac_ssm_b200.models.modeling_frac import causal_conv_silu
+    h, x = torch.zeros(2, 4, 8), torch.zeros(1, 4, 16)
+    D, w = torch.zeros(2, 8), torch.ones(16)
+    for call in (lambda: scan_epilogue(h, x, x, D, w, 2, 8),
+                 lambda: scan_epilogue_sumsq(h, x, x, D, 2, 8),
+                 lambda: scan_epilogue_apply(h, x, x, D, w, 2, 8, torch.zeros(1, 4), 16)):
+        with pytest.raises(AssertionError, match="CUDA"):
+            call()
+    with pytest.raises(AssertionError, match="CUDA"):
+        causal_conv_silu(x, torch.zeros(16, 1, 4), None)
+
+
+def test_shard_heads_covers_every_head_once():
+    from frac_ssm_b200 import parallel
+    for heads, world in ((64, 8), (24, 5), (3, 4)):
+        seen = []
+        for r in range(world):
+            sl = parallel.shard_heads(heads, r, world)
+            seen.extend(range(sl.start, sl.stop))
+        assert seen == list(range(heads))
