@@ -400,6 +400,21 @@ def run_model_workload(args, rank, world, dev, dist):
     for layer in model.model.layers:
         layer.mixer.coeff_dtype = torch.bfloat16
     ms = timed()                  # bfloat16 coefficients: the benchmark's headline configuration
+    # decode: one prefill with the cache kept, then single-token steps through the state-update kernel
+    _, past = model(ids, use_cache=True)
+    nxt = torch.randint(0, cfg.vocab_size, (batch // world, 1), device=dev, generator=g)
+    for _ in range(3):
+        _, past = model(nxt, past_key_values=past, use_cache=True)
+    torch.cuda.synchronize()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_dec = 16
+    d0.record()
+    for _ in range(n_dec):
+        _, past = model(nxt, past_key_values=past, use_cache=True)
+    d1.record()
+    torch.cuda.synchronize()
+    dec_ms = d0.elapsed_time(d1) / n_dec
+    del past
     if rank == 0:
         nparam = sum(p.numel() for p in model.parameters())
         print(json.dumps({"metric": "model prefill tokens/s (all GPUs)", "value": batch * L / (ms * 1e-3),
@@ -410,6 +425,8 @@ def run_model_workload(args, rank, world, dev, dist):
                                                  "24 heads x 64, 128 modes, chunk 256, vocabulary 50280",
                                      "parameters": nparam, "scan_coefficients": "bf16",
                                      "ms_per_step_with_f32_scan_coefficients": ms_f32,
+                                     "decode_ms_per_token_step_rank0": dec_ms,
+                                     "decode_batch_per_gpu": batch // world,
                                      "sharding": f"batch over {world} GPU(s), replicas, no collective"}}), flush=True)
     if dist is not None:
         dist.destroy_process_group()
