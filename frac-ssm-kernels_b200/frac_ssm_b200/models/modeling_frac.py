@@ -22,7 +22,7 @@ from ..layers.compute_params import compute_params_from_projections
 from ..layers.output_mix import scan_epilogue
 from ..modules.rmsnorm_gated import MambaRMSNormGated as RMSNormGated
 from ..modules.rmsnorm_gated import rmsnorm_gated_fwd
-from ..ops.frac_scan import frac_scan
+from ..ops.b200.frac_scan import frac_scan
 from .configuration_frac import FracConfig
 
 LayerCache = tuple  # (state [B, H, M, R] float32, conv_state [B, C, K-1])
@@ -144,11 +144,12 @@ class FracMixer(nn.Module):
         if layer_past is None and L > 1:
             x_conv = causal_conv_silu(x, self.conv1d.weight, self.conv1d.bias, attention_mask)
             u, c, kappa, rho = self._scan_params(x_conv, x, attention_mask)
-            out = frac_scan(u, c, kappa, rho, self.chunk_size, None, use_cache)
+            # (the backend's own entry point: it can hand back the final state in float32, as carried)
+            out = frac_scan(u, c, kappa, rho, self.chunk_size, None, use_cache, final_state_dtype=torch.float32)
             next_cache = None
             if use_cache:
                 mixed, final_state = out
-                state = final_state.view(B, H, R, M).permute(0, 1, 3, 2).float().contiguous()
+                state = final_state.view(B, H, R, M).permute(0, 1, 3, 2).contiguous()
                 next_cache = (state, self._conv_state_after(x, attention_mask))
             else:
                 mixed = out
