@@ -9,7 +9,6 @@ outputs are freshly allocated on the input device, kernels run on the current st
 
 from __future__ import annotations
 
-import math
 
 import torch
 
