@@ -159,3 +159,38 @@ def test_incoming_state_composition():
         s = D[r][:, None, :] * s + F[r]
     with pytest.raises(ValueError):
         parallel.incoming_state(D[:2], F, 1)
+
+
+def _leaver_worker(rank, world, port, out):
+    """Rank 1 leaves between steps (no collective of its own in flight); rank 0's next exchange must
+    end with an error within the process group's short time-out, not hang."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    B, L, R, M, T = 2, 64, 8, 16, 16
+    u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, dtype=torch.float32, gen="model_like", seed=21)
+    tok = parallel.shard_tokens(L, T, rank, world)
+    args = (u[:, tok], c[:, tok], kappa[:, tok], rho[:, tok], T, init, True)
+    parallel.seq_parallel_scan(*args, ops=OracleStageOps)          # step 1: everybody is there
+    dist.barrier()
+    if rank == 1:
+        out[rank] = 1
+        os._exit(0)                                                  # leaves without a word
+    try:
+        parallel.seq_parallel_scan(*args, ops=OracleStageOps)      # step 2: the peer is gone
+        out[rank] = 0
+    except Exception:                                                # noqa: BLE001 - any error is the point
+        out[rank] = 1
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_ends_the_others_exchange_with_an_error():
+    port = _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        ctx = mp.spawn(_leaver_worker, args=(2, port, out), nprocs=2, join=False)
+        import time
+        t0 = time.time()
+        while not ctx.join(timeout=1.0):
+            assert time.time() - t0 < 120, "the remaining rank hung instead of failing"
+        assert dict(out) == {0: 1, 1: 1}
