@@ -6,6 +6,7 @@ every call checks the returned status and raises with the library's error text.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 import threading
@@ -120,3 +121,14 @@ def check(status: int, what: str) -> None:
     if status != 0:
         msg = lib().fracssm_last_error().decode("utf-8", "replace")
         raise FracSsmError(f"{what} failed (status {status}): {msg}")
+
+
+_NVTX = os.environ.get("FRACSSM_NVTX", "") not in ("", "0")
+
+
+def trace(name: str):
+    """NVTX range around a host-side stage when FRACSSM_NVTX=1 (for nsys / ncu timelines; the
+    reference marks its stages the same way, `frac_ssm/ops/utils.py:6-23`); a no-op otherwise."""
+    if not _NVTX:
+        return contextlib.nullcontext()
+    return torch.cuda.nvtx.range(name)

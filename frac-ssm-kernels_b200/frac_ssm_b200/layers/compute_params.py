@@ -40,7 +40,7 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
         return u, c, kappa, rho
     dtb = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
     ltau = base_log_tau.detach().to(device=dev, dtype=torch.float32).contiguous()
-    with torch.cuda.device(dev):
+    with C.trace("frac_compute_scan_params"), torch.cuda.device(dev):
         C.check(C.lib().fracssm_compute_params(
             C.ptr(dyn), C.dt(dyn), dyn.stride(0), dyn.stride(1), C.ptr(rw), C.dt(rw), rw.stride(0),
             rw.stride(1), C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1),

@@ -23,7 +23,7 @@ def skip_mix(mixed_flat, x_conv, D, num_heads, head_dim, out_dtype=None):
     out = torch.empty(B, L, HR, device=x_conv.device, dtype=out_dtype)
     if B == 0 or L == 0:
         return out
-    with torch.cuda.device(x_conv.device):
+    with C.trace("frac_skip_mix"), torch.cuda.device(x_conv.device):
         C.check(C.lib().fracssm_skip_mix(
             C.ptr(mixed_flat), C.dt(mixed_flat), mixed_flat.stride(0), mixed_flat.stride(1),
             C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1), C.ptr(Df), C.ptr(out),
@@ -50,7 +50,7 @@ def scan_epilogue(h, x_conv, gate, D, weight, num_heads, head_dim, eps=1e-6, gat
     y = torch.empty(B, L, HR, device=x_conv.device, dtype=x_conv.dtype)
     if B == 0 or L == 0:
         return y
-    with torch.cuda.device(x_conv.device):
+    with C.trace("scan_epilogue"), torch.cuda.device(x_conv.device):
         C.check(C.lib().fracssm_scan_epilogue(
             C.ptr(h), C.dt(h), h.stride(0), h.stride(1), C.ptr(x_conv), x_conv.stride(0),
             x_conv.stride(1), C.ptr(gate), gate.stride(0), gate.stride(1), C.dt(x_conv), C.ptr(Df),

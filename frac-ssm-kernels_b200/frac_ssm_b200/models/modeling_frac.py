@@ -43,7 +43,7 @@ def causal_conv_silu(x, weight, bias, attention_mask=None):
     y = torch.empty(B, L, Cn, device=x.device, dtype=x.dtype)
     if B == 0 or L == 0:
         return y
-    with torch.cuda.device(x.device):
+    with C.trace("causal_conv_silu"), torch.cuda.device(x.device):
         C.check(C.lib().fracssm_causal_conv_silu(
             C.ptr(x), C.dt(x), x.stride(0), x.stride(1), C.ptr(mask),
             0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1), C.ptr(w),

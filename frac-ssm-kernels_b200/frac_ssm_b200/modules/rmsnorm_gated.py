@@ -30,7 +30,7 @@ def rmsnorm_gated_fwd(hidden_states, weight, gate=None, eps=1e-6):
     y = torch.empty(rows, D, device=x.device, dtype=x.dtype)
     rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
     if rows > 0:
-        with torch.cuda.device(x.device):
+        with C.trace("rmsnorm_gated"), torch.cuda.device(x.device):
             C.check(C.lib().fracssm_rmsnorm_gated(
                 C.ptr(x), x.stride(0), C.ptr(g), 0 if g is None else g.stride(0), C.dt(x), C.ptr(w),
                 C.dt(w), float(eps), C.ptr(y), C.ptr(rstd), rows, D, C.stream_of(x)), "rmsnorm_gated")

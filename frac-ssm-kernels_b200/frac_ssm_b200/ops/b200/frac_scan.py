@@ -99,7 +99,7 @@ def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32,
     fin = torch.empty(B, R, M, device=u.device, dtype=final_state_dtype) if want_final else None
     if B > 0:
         lib = C.lib()
-        with torch.cuda.device(u.device):
+        with C.trace("frac_scan"), torch.cuda.device(u.device):
             nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, path_code)
             ws = torch.empty(max(nbytes, 256), device=u.device, dtype=torch.uint8)
             if keep_workspace:
