@@ -224,7 +224,71 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_seq_workload(args, rank, world, dev, dist):
+def _timed(step, steps, warmup, dev, dist):
+    """W untimed + K timed calls of `step` between two events, barrier + synchronise on both sides,
+    max over ranks; returns ms per step."""
+    for _ in range(warmup):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    return ms
+
+
+def _all_ok(ok, dev, dist):
+    """True when `ok` holds on every rank."""
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    if dist is not None:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
+def scan_inputs_device(B, L, R, M, dev, seed):
+    """Seeded scan-level inputs made on the device (the same on every rank that uses the same seed):
+    u, c, kappa ~ 0.25 N(0,1) bf16, model-like decay in [1e-6, 1 - 1e-6], initial state 0.25 N(0,1)."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rn = lambda *sh: torch.randn(*sh, device=dev, generator=g)
+    u, c, kappa = (0.25 * rn(B, L, R)).bfloat16(), (0.25 * rn(B, L, M)).bfloat16(), (0.25 * rn(B, L, M)).bfloat16()
+    tau = torch.linspace(0.0, math.log(65536.0), M, device=dev).exp()
+    dt = torch.nn.functional.softplus(rn(B, L, 1) - 2.0)
+    rho = torch.exp(-dt * 2.0 / tau).clamp(1e-6, 1 - 1e-6)
+    return u, c, kappa, rho, 0.25 * rn(B, R, M)
+
+
+def seq_parity(rank, world, dev, dist):
+    """Small case of the sequence-sharded scan against the single-GPU scan of the whole sequence
+    (every rank builds the same inputs from one seed): h within 2e-2, final state within 1e-3."""
+    from frac_ssm_b200 import parallel
+    B, R, M, T = 6, CFG["R"], CFG["M"], CFG["T"]
+    L = 4096 * max(world, 2)
+    u, c, kappa, rho, init = scan_inputs_device(B, L, R, M, dev, seed=5)
+    h_ref, f_ref = parallel.CudaStageOps.scan(u, c, kappa, rho, T, init)
+    if world == 1:      # one rank: the same composition with the segment cut into two sub-segments
+        h, fin = parallel.seq_parallel_scan(u, c, kappa, rho, T, init, True, local_splits=2)
+        tok = slice(0, L)
+    else:
+        tok = parallel.shard_tokens(L, T, rank, world)
+        h, fin = parallel.seq_parallel_scan(u[:, tok].contiguous(), c[:, tok].contiguous(),
+                                            kappa[:, tok].contiguous(), rho[:, tok].contiguous(), T, init, True)
+    ok = torch.allclose(h.float(), h_ref[:, tok].float(), rtol=2e-2, atol=2e-2) and \
+        torch.allclose(fin, f_ref, rtol=1e-3, atol=1e-3)
+    return _all_ok(ok, dev, dist)
+
+
+def measure_seq(args, rank, world, dev, dist, steps, warmup):
     """Config 3: batch 1, L 1,048,576, 24 heads, sequence split evenly over the ranks; per step one
     segment-summary pass, one all-gather of (state, decay) per rank, one scan with the true state."""
     from frac_ssm_b200 import parallel
@@ -238,44 +302,50 @@ def run_seq_workload(args, rank, world, dev, dist):
     dt = torch.nn.functional.softplus(torch.randn(H, Ll, 1, device=dev, generator=g) - 4.0)
     rho = torch.exp(-dt * 4.0 / tau).clamp(1e-6, 1 - 1e-6)
     kappa = ((1 - rho) * torch.softmax(torch.randn(H, Ll, M, device=dev, generator=g), -1)).bfloat16()
+    del dt
+    # the sub-segment count is fixed here (the same on every rank), so no step synchronises the host
+    S = 1
+    while world > 1 and H * S < 148 and Ll % (2 * S * T) == 0 and Ll // (2 * S) >= 1024:
+        S *= 2
 
     def step():
         if world == 1:
             return parallel.CudaStageOps.scan(u, c, kappa, rho, T, None)[0]
-        return parallel.seq_parallel_scan(u, c, kappa, rho, T, None, False)
+        return parallel.seq_parallel_scan(u, c, kappa, rho, T, None, False, local_splits=S)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+    ms = _timed(step, steps, warmup, dev, dist)
+    del u, c, kappa, rho
+    torch.cuda.empty_cache()
+    parity_ok = seq_parity(rank, world, dev, dist)
+    peak, peak_kind = measured_peak_gbs()
+    alg = algorithmic_bytes(H, Ltot, R, M)
+    gathered = 0 if world == 1 else H * S * (R * M + M) * 4
+    return {"workload": "config 3: batch 1, L 1048576, 24 heads, R 64, M 128, chunk 256, bf16",
+            "sharding": f"sequence over {world} GPU(s)", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+            "tokens_per_s": Ltot / (ms * 1e-3), "algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak_per_gpu": alg / (ms * 1e-3) / 1e9 / world / peak, "peak_kind": f"of {peak_kind}",
+            "collective": ("none" if world == 1 else
+                           f"one all_gather_into_tensor per step, {gathered} bytes sent per rank "
+                           f"({S} sub-segment(s) per rank), NCCL"),
+            "collective_bytes_per_rank": gathered, "parity_ok": parity_ok,
+            "parity_case": f"6 rows, L {4096 * max(world, 2)}, sharded scan vs the single-GPU scan, "
+                           "h within 2e-2, final state within 1e-3"}
+
+
+def run_seq_workload(args, rank, world, dev, dist):
+    res = measure_seq(args, rank, world, dev, dist, args.steps, max(args.warmup, 3))
     if rank == 0:
-        alg = algorithmic_bytes(H, Ltot, R, M)
         print(json.dumps({"metric": "frac_scan fwd tokens/s, one 1,048,576-token sequence split by sequence",
-                          "value": Ltot / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-                          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": "config 3: batch 1, L 1048576, 24 heads, R 64, M 128, chunk 256",
-                                     "sharding": f"sequence over {world} GPU(s), one all-gather of 790 KB per rank"},
-                          "algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
+                          "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"],
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic", "config": {"workload": res["workload"], "sharding": res["sharding"]},
+                          "config3": res}), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
 
-def run_heads_workload(args, rank, world, dev, dist):
+def measure_heads(args, rank, world, dev, dist, steps, warmup):
     """Config 4: batch 4, L 16384, 64 heads in 8 groups, R 64, M 128, chunk 256, with the skip-mix and
     gated-RMSNorm epilogue; the heads are spread over the ranks.  Per step and rank: one scan of its
     own heads, one [batch, L] float32 all-reduce for the norm, the two epilogue passes."""
@@ -323,36 +393,71 @@ def run_heads_workload(args, rank, world, dev, dist):
             return scan_epilogue(h, x_conv, z, D, w, n, R, 1e-6)
         return parallel.head_parallel_epilogue(h, x_conv, z, D, w, n, R, H, 1e-6)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+    ms = _timed(step, steps, warmup, dev, dist)
+    del u, c, kappa, rho, x_conv, z
+    torch.cuda.empty_cache()
+    parity_ok = heads_parity(rank, world, dev, dist)
+    peak, peak_kind = measured_peak_gbs()
+    alg = algorithmic_bytes(batch * H, L, R, M) + 4 * batch * L * H * R * 2     # scan + epilogue (h, x, z in, y out)
+    return {"workload": "config 4: batch 4, L 16384, 64 heads in 8 groups, R 64, M 128, chunk 256, bf16, "
+                        "with skip-mix and gated RMSNorm",
+            "sharding": f"heads over {world} GPU(s)", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+            "tokens_per_s": batch * L / (ms * 1e-3), "algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak_per_gpu": alg / (ms * 1e-3) / 1e9 / world / peak, "peak_kind": f"of {peak_kind}",
+            "collective": ("none" if world == 1 else
+                           f"one all_reduce (sum) of a [batch, L] float32 vector per step, {batch * L * 4} bytes, NCCL"),
+            "collective_bytes_per_rank": 0 if world == 1 else batch * L * 4, "parity_ok": parity_ok,
+            "parity_case": "batch 2, L 512, 64 heads: head-sharded two-pass epilogue vs the one-pass epilogue "
+                           "over all heads, within 1e-3 (relative and absolute, bf16 outputs compared as float)"}
+
+
+def heads_parity(rank, world, dev, dist):
+    """Small case at config 4's head count: the head-sharded epilogue (partial sums of squares,
+    all-reduce, second pass) against the one-pass epilogue over all 64 heads (same seed on every rank)."""
+    from frac_ssm_b200 import parallel
+    from frac_ssm_b200.layers import scan_epilogue
+    batch, L, H, R = 2, 512, 64, CFG["R"]
+    g = torch.Generator(device=dev).manual_seed(77)
+    h = torch.randn(batch * H, L, R, device=dev, generator=g).bfloat16()
+    x = torch.randn(batch, L, H * R, device=dev, generator=g).bfloat16()
+    z = torch.randn(batch, L, H * R, device=dev, generator=g).bfloat16()
+    D = torch.randn(H, R, device=dev, generator=g)
+    w = (torch.rand(H * R, device=dev, generator=g) + 0.5).bfloat16()
+    y_ref = scan_epilogue(h, x, z, D, w, H, R, 1e-6)
+    parts = max(world, 2)       # one rank: two shards in turn, the partial sums added by hand
+    ok = True
+    if world == 1:
+        from frac_ssm_b200.layers import scan_epilogue_apply, scan_epilogue_sumsq
+        shards = [parallel.shard_heads(H, r, parts) for r in range(parts)]
+        loc = lambda hs: (h.view(batch, H, L, R)[:, hs].reshape(-1, L, R).contiguous(),
+                          x[..., hs.start * R:hs.stop * R].contiguous(), z[..., hs.start * R:hs.stop * R].contiguous(),
+                          D[hs].contiguous())
+        total = sum(scan_epilogue_sumsq(*loc(hs), hs.stop - hs.start, R, 0.0) for hs in shards)
+        for hs in shards:
+            hl, xl, zl, Dl = loc(hs)
+            y = scan_epilogue_apply(hl, xl, zl, Dl, w[hs.start * R:hs.stop * R].contiguous(), hs.stop - hs.start, R,
+                                    total, H * R, 1e-6, 0.0)
+            ok = ok and torch.allclose(y.float(), y_ref[..., hs.start * R:hs.stop * R].float(), rtol=1e-3, atol=1e-3)
+    else:
+        hs = parallel.shard_heads(H, rank, world)
+        cols = slice(hs.start * R, hs.stop * R)
+        nl = hs.stop - hs.start
+        y = parallel.head_parallel_epilogue(h.view(batch, H, L, R)[:, hs].reshape(-1, L, R).contiguous(),
+                                            x[..., cols].contiguous(), z[..., cols].contiguous(), D[hs].contiguous(),
+                                            w[cols].contiguous(), nl, R, H, 1e-6)
+        ok = torch.allclose(y.float(), y_ref[..., cols].float(), rtol=1e-3, atol=1e-3)
+    return _all_ok(ok, dev, dist)
+
+
+def run_heads_workload(args, rank, world, dev, dist):
+    res = measure_heads(args, rank, world, dev, dist, args.steps, max(args.warmup, 3))
     if rank == 0:
-        alg = algorithmic_bytes(batch * H, L, R, M)
         print(json.dumps({"metric": "layer forward tokens/s (scan + skip-mix + gated RMSNorm), heads sharded",
-                          "value": batch * L / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                          "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"],
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-                          "data": "synthetic",
-                          "config": {"workload": "config 4: batch 4, L 16384, 64 heads in 8 groups, R 64, M 128, "
-                                                 "chunk 256, with skip-mix and gated RMSNorm",
-                                     "sharding": f"heads over {world} GPU(s), one all-reduce of "
-                                                 f"{batch * L * 4 // 1024} KB per step for the norm"},
-                          "scan_algorithmic_GBps_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
+                          "data": "synthetic", "config": {"workload": res["workload"], "sharding": res["sharding"]},
+                          "config4": res}), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -440,6 +545,25 @@ def workload_config(n):
             "l2": "inputs (2.2 GB per step) exceed the 126 MB L2; no flush needed"}
 
 
+def profiled_traffic(head_tokens):
+    """DRAM bytes per launch of the single-pass kernel, from profiles/scan_fused_kernel_small_case.md.
+    That file records `traffic_bytes_per_head_token` and the hash of the kernel source it was captured
+    from (`kernel_source_sha256`); a capture of another build does not describe this one."""
+    import hashlib
+    import re
+    here = os.path.dirname(os.path.abspath(__file__))
+    try:
+        text = open(os.path.join(here, "profiles", "scan_fused_kernel_small_case.md")).read()
+        src = open(os.path.join(here, "frac-ssm-kernels_b200", "csrc", "scan_fused.cu"), "rb").read()
+    except OSError:
+        return None
+    per = re.search(r"traffic_bytes_per_head_token:\s*([0-9.]+)", text)
+    sha = re.search(r"kernel_source_sha256:\s*([0-9a-f]{64})", text)
+    if not per or not sha or sha.group(1) != hashlib.sha256(src).hexdigest():
+        return None
+    return int(float(per.group(1)) * head_tokens)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -449,8 +573,6 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "staged", "fused"])
     ap.add_argument("--seq-len", type=int, default=None,
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
-    ap.add_argument("--phases", action="store_true",
-                    help="also print the single-pass kernel's per-phase cycle shares (diagnostic)")
     ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads", "model"],
                     help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
                          "tokens x 24 heads split over the ranks; heads: config 4, one layer's 64 heads spread over the "
@@ -465,8 +587,6 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    if args.phases:             # selects the kernel build that records per-phase cycles (about 7 % slower)
-        os.environ["FRACSSM_SCAN_PROFILE"] = "1"
     if args.watchdog > 0:      # a stalled run must end with a traceback, not run until someone kills it
         import faulthandler
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
@@ -653,21 +773,14 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": ems, "steps": k2}
         del host, y_host
 
-    if rank == 0 and args.phases and use_fused:
-        from frac_ssm_b200.ops.b200.frac_scan import last_phase_cycles
-        frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path, keep_workspace=True)
-        cyc = last_phase_cycles()
-        tot = max(1, sum(cyc))
-        print("phase shares:", " ".join(f"{i}:{100.0 * v / tot:.1f}%" for i, v in enumerate(cyc)),
-              f"| cycles per tile {tot / (BH * ((L + 127) // 128)):.0f}", file=sys.stderr, flush=True)
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         alg = algorithmic_bytes(BH, L, R, M)
         achieved = alg / (scan_ms * 1e-3) / 1e9
-        # DRAM bytes per launch from one ncu capture of the single-pass kernel on a 192 x 1024 case
-        # (dram read 227.0 MB + the 25.2 MB of h it writes), scaled by head-tokens; traffic grows in
-        # proportion to the tiles processed.  Staged path: not captured.
-        traffic = int(252.2e6 / (192 * 1024) * BH * L) if use_fused else None
+        # DRAM bytes per launch come from the committed ncu summary of the kernel (a small case,
+        # scaled by head-tokens: traffic grows in proportion to the tiles processed); null when that
+        # summary was taken from another build of the kernel than the one loaded here.
+        traffic = profiled_traffic(BH * L) if use_fused else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                     "kernel": "scan_fused_kernel" if use_fused else

@@ -3,7 +3,9 @@
     python frac-ssm-kernels_b200/build.py [--force] [--verbose]
 
 Each csrc/*.cu is compiled to an object file under build/ (skipped when newer than its
-sources) and linked into frac_ssm_b200/lib/libfracssm.so.  No GPU is needed to build.
+sources) and linked into frac_ssm_b200/lib/libfracssm.so.  The same objects plus
+csrc/selftest/*.cu give frac_ssm_b200/lib/libfracssm_selftest.so, which only the tests load
+(include/fracssm_selftest.h).  No GPU is needed to build.
 """
 
 from __future__ import annotations
@@ -22,6 +24,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "frac_ssm_b200", "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libfracssm.so")
+SELFTEST_LIB = os.path.join(OUT_DIR, "libfracssm_selftest.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -50,10 +53,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    objs, jobs = [], []
-    for src in sources:
+    test_sources = sorted(glob.glob(os.path.join(CSRC, "selftest", "*.cu")))
+    objs, test_objs, jobs = [], [], []
+    for src in sources + test_sources:
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
-        objs.append(obj)
+        (test_objs if src in test_sources else objs).append(obj)
         if force or _stale(obj, [src] + headers):
             cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
             if verbose:
@@ -70,13 +74,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
             if r.returncode:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
-    if jobs or force or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xcompiler", "-fPIC", "-cudart", "static"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("link failed")
+    for lib, members in ((LIB, objs), (SELFTEST_LIB, objs + test_objs)):
+        if jobs or force or _stale(lib, members):
+            cmd = [nvcc, "-shared", "-o", lib, *members, "-gencode", "arch=compute_100a,code=sm_100a",
+                   "-Xcompiler", "-fPIC", "-cudart", "static"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError("link failed")
     return LIB
 
 

@@ -9,12 +9,12 @@
 // by a running CTA (one item ahead of the one it is working on) and dependencies point to
 // lower tickets, so the lowest unfinished item is always being worked on and never waits.
 //
-// One CTA per SM, 20 warps (three of them only pad the control warp's register group).  Warps 0-15 ("workers") turn the raw inputs into bf16 operand tiles
-// in shared memory and run the epilogues; warp 16 ("control") takes tickets, issues the TMA
-// load of u and every tcgen05.mma, and polls the state counter.  Workers hand a batch of tiles
-// over by arriving on a "full" mbarrier (one arrival per warp, after a proxy fence); the
-// control warp hands buffers and accumulators back through tcgen05.commit mbarriers.  The next
-// ticket is taken a whole tile ahead, so its inputs can be pulled into L2 exactly.
+// One CTA per SM, 20 warps (three of them only pad the control warp's register group).  Warps
+// 0-15 ("workers") turn the raw inputs into bf16 operand tiles in shared memory and run the
+// epilogues; warp 16 ("control") takes tickets, issues the TMA load of u and every tcgen05.mma,
+// and polls the state counter.  Workers hand a batch of tiles over by arriving on a "full"
+// mbarrier (one arrival per warp, after a proxy fence); the control warp hands buffers and
+// accumulators back through tcgen05.commit mbarriers.
 //
 // Math per tile (tokens t, k in 0..127; modes m; rho floored at 1e-6, 1 beyond L):
 //   h[t]   = sum_m Chat[t,m] S[m,:]  +  sum_{k<=t} W[t,k] u[k,:]
@@ -25,13 +25,22 @@
 //   * sibling levels s = 64, 32, 16, 8: for t in the second half and k in the first half of a
 //     block of 2s tokens, the reference point is the boundary between the halves:
 //       A_s[t] = c[t] prod_{bnd<=j<=t} rho[j],  B_s[k] = kappa[k] prod_{k<j<bnd} rho[j]
-//     A-role and B-role rows share one operand tile X_s (every token has exactly one role);
+//     Every token has exactly one role per level.  The A rows of two levels are stacked into one
+//     128-row operand tile and their B rows into another, so one 128 x 128 product serves two
+//     levels (its two diagonal 64 x 64 quadrants; the other two are never read);
 //   * base: the 8x8 diagonal blocks use the middle of the block as reference, which keeps
 //     the reciprocal products below 1e24.
-// Every piece is a bf16 tcgen05 GEMM over the modes; an epilogue picks, for each (t, k), the
-// accumulator of the one level that holds it.  Chat / Khat are the same factors taken to the
-// tile's start / end; Khat is split into bf16 high and low parts so that the state keeps
-// float32-level accuracy.
+// Every piece is a bf16 tcgen05 GEMM over the modes; an epilogue copies each block of accumulators
+// to its place in W.  Chat / Khat are the same factors taken to the tile's start / end, split into
+// bf16 high and low parts so that the state keeps float32-level accuracy.
+//
+// Shared memory: six 32 KB operand slots, each used twice per tile:
+//   slot 0 / 1: base A / B factors        -> Khat high / low   (after the base product)
+//   slot 2 / 3: levels 8+16, A / B rows   -> Chat high / low   (after the level-8/16 product)
+//   slot 4 / 5: levels 64+32, A / B rows  -> W / incoming state high|low (after that product)
+// Tensor memory (fp32 columns): base 0..127, tile's own state contribution 128..191, levels 8+16
+// 192..319, levels 64+32 320..447; the output accumulator H re-uses 320..447 (columns 384..447
+// take the product with the state's low part and are added when the rows are written).
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -47,24 +56,24 @@ namespace {
 using namespace tile;
 constexpr int kWorkers = 512, kThreads = 640;
 // Registers are re-divided after launch (setmaxnreg): the 16 worker warps grow to kWorkerRegs,
-// the control warp's group of four shrinks to kControlRegs.  The launch allocation per thread
-// (checked on the host) must cover both, or the growing warps would wait forever.
+// the control warp's group of four shrinks to kControlRegs.  Each SM sub-partition holds four
+// worker warps and one warp of the control group: 4 * 112 + 32 = 5 * 96, the launch allocation
+// (checked on the host: it must cover both, or the growing warps would wait forever).
 constexpr int kWorkerRegs = 112, kControlRegs = 32;
 constexpr int kLaunchRegsNeeded = (kWorkers * kWorkerRegs + (kThreads - kWorkers) * kControlRegs + kThreads - 1) / kThreads;
 // shared memory map (bytes from the 1024-aligned base)
-constexpr uint32_t kOffArea0 = 0, kOffArea1 = 65536;
-constexpr uint32_t kOffChatLo = 131072;                  // low part of Chat, one operand tile
-constexpr uint32_t kOffS = 163840, kOffSlo = 180224;     // incoming state, bf16 high and low parts
-constexpr uint32_t kOffU = 196608;
-constexpr uint32_t kOffSeg = 212992;    // float [16][128]: decay product of each 8-token segment
-constexpr uint32_t kOffGt = 221184;     // float [128]: decay product of the whole tile
-constexpr uint32_t kOffMisc = 221696;   // mbarriers, TMEM base, tickets
-constexpr uint32_t kSmemBytes = kOffMisc + 192 + 128 + 1024;
+constexpr uint32_t kSlot = 32768;
+constexpr uint32_t kOffA0 = 0, kOffB0 = kSlot, kOffY1 = 2 * kSlot, kOffZ1 = 3 * kSlot, kOffY2 = 4 * kSlot,
+                   kOffZ2 = 5 * kSlot;
+constexpr uint32_t kOffKhi = kOffA0, kOffKlo = kOffB0, kOffChi = kOffY1, kOffClo = kOffZ1, kOffW = kOffY2,
+                   kOffS = kOffZ2;              // second use of each slot
+constexpr uint32_t kOffU = 6 * kSlot;           // u tile, 128 tokens x 64 bf16
+constexpr uint32_t kOffSeg = kOffU + 16384;     // float [16][128]: decay product of each 8-token segment
+constexpr uint32_t kOffMisc = kOffSeg + 8192;   // mbarriers, TMEM base, tickets, failure flag
+constexpr uint32_t kSmemBytes = kOffMisc + 256 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
-constexpr uint32_t kColH = 0, kColS = 64, kColBase = 128, kColL8 = 256, kColL16 = 320, kColL32 = 384,
-                   kColL64 = 448;
-constexpr int kProfCtas = 256, kProfPhases = 16;
-constexpr size_t kCtrlBytes = 256, kProfBytes = kProfCtas * kProfPhases * sizeof(long long);
+constexpr uint32_t kColBase = 0, kColS = 128, kColL1 = 192, kColL2 = 320, kColH = 320;
+constexpr size_t kCtrlBytes = 256;
 
 struct FusedArgs {
   const void *c, *kappa;  // bf16 or f32 [BH, L, 128], see the kernel's CKF32 parameter
@@ -73,10 +82,11 @@ struct FusedArgs {
   void *fin;
   int fin_dt;
   int *ctrl;     // [0] ticket counter, [1] error word
-  long long *prof;  // [kProfCtas][16] cycles spent per phase by worker thread 0 of each CTA
   int *flags;    // [BH] tiles finished per bh
   float *state;  // running state per row, 128 m x 64 r floats in the order the workers access it
   int BH, L, ntiles, total;
+  int first_tile;              // tile index of the first ticket (0 except in the wait-limit self-test)
+  unsigned long long wait_ns;  // limit of every device-side wait
 };
 
 // Raw inputs of one item for one worker thread, one group of 4 tokens x 4 modes.
@@ -93,7 +103,7 @@ __device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a
                                          int grp) {
   using CK = typename RawRegs<CKF32>::CK;
   const int j = item / a.BH, bh = item - j * a.BH;
-  const int t0 = j * kTile + 8 * w + 4 * grp;
+  const int t0 = (j + a.first_tile) * kTile + 8 * w + 4 * grp;
   const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
   const CK *cp = reinterpret_cast<const CK *>(a.c), *kp = reinterpret_cast<const CK *>(a.kappa);
 #pragma unroll
@@ -109,75 +119,78 @@ __device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a
   }
 }
 
-// PROF: worker thread 0 of each CTA also charges its cycles to 16 phases of the tile loop (a
-// diagnostic build of the same kernel: the bookkeeping costs about 7 % of the run time, because the
-// one warp that does it is on every hand-over's critical path).
-template <bool CKF32, bool PROF>
+// The two floored decay pairs of one token.
+__device__ __forceinline__ void rho_pairs(const float4 &v, f2 (&out)[2]) {
+  out[0] = mk2(fmaxf(v.x, kRhoFloor), fmaxf(v.y, kRhoFloor));
+  out[1] = mk2(fmaxf(v.z, kRhoFloor), fmaxf(v.w, kRhoFloor));
+}
+
+template <bool CKF32>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t *area0 = smem + kOffArea0, *area1 = smem + kOffArea1;
-  uint8_t *s_tile = smem + kOffS, *slo_tile = smem + kOffSlo, *u_tile = smem + kOffU;
-  uint8_t *chat_lo = smem + kOffChatLo;
-  float *seg = reinterpret_cast<float *>(smem + kOffSeg);
-  float *gt_s = reinterpret_cast<float *>(smem + kOffGt);
-  // mbarriers: cb[0..4] / barH are completed by tcgen05.commit (each once per tile), barU by the TMA load,
-  // full[0..5] by the 16 worker warps, item_bar and state_bar by the control warp.
-  uint64_t *cb = reinterpret_cast<uint64_t *>(smem + kOffMisc);  // cb[0..3]: one per MMA batch (cb[4] unused)
-  uint64_t *barH = cb + 5, *barU = cb + 6, *full = cb + 7;
-  uint64_t *item_bar = cb + 13, *state_bar = cb + 14, *out_bar = cb + 15;
-  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(cb + 16);
+  // mbarriers, each completed exactly once per tile:
+  //   cb0 / cb1 / cb2 / cbK / barH by tcgen05.commit, barU by the TMA load,
+  //   fA / fL1 / fL2 / fK / fW / fS / out_bar by the 16 worker warps, item_bar / state_bar by the control warp
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffMisc);
+  uint64_t *cb0 = bars + 0, *cb1 = bars + 1, *cb2 = bars + 2, *cbK = bars + 3, *barH = bars + 4, *barU = bars + 5;
+  uint64_t *fA = bars + 6, *fL1 = bars + 7, *fL2 = bars + 8, *fK = bars + 9, *fW = bars + 10, *fS = bars + 11;
+  uint64_t *item_bar = bars + 12, *state_bar = bars + 13, *out_bar = bars + 14;
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 15);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
-  long long *prof = reinterpret_cast<long long *>(smem + kOffMisc + 192);  // worker thread 0 only
+  volatile int *failed = reinterpret_cast<volatile int *>(tmem_s + 3);  // a wait of this CTA ran out
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) umma::mbar_init(cb + i, 1);
-    umma::mbar_init(barH, 1);
-    umma::mbar_init(barU, 1);
-    for (int i = 0; i < 6; ++i) umma::mbar_init(full + i, 16);
+    for (int i = 0; i < 6; ++i) umma::mbar_init(bars + i, 1);
+    for (int i = 6; i < 12; ++i) umma::mbar_init(bars + i, 16);
     umma::mbar_init(item_bar, 1);
     umma::mbar_init(state_bar, 1);
     umma::mbar_init(out_bar, 16);
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
-    for (int i = 0; i < kProfPhases; ++i) prof[i] = 0;
+    *failed = 0;
   }
   if (w == 0) umma::tmem_alloc(tmem_s, 512);
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
   const uint32_t tmem = *tmem_s;
+  const uint64_t wait_ns = a.wait_ns;
   bool ok = true;  // cleared when a bounded wait runs out; later waits are then skipped
   // Bounded waits.  The control warp polls (it is one warp and every hand-over of the tile passes
   // through it: a parked wait wakes up several hundred cycles after the barrier completes); the 16
-  // worker warps park, which leaves the issue slots to the warps that have work.
+  // worker warps park, which leaves the issue slots to the warps that have work.  A wait that runs
+  // out marks the CTA as failed: its remaining outputs are written as NaN and the error word is set.
   // (each setmaxnreg sits inside its role's branch: the register limit must not merge across roles)
   if (w > 16) {
     // spare warps of the control warp's register group: give the registers back, nothing else
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
   } else if (w == 16) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-#define FRACSSM_WAIT(bar, parity) \
-  if (ok) ok = umma::mbar_wait(bar, (parity) & 1u, kWaitNs)
+#define FRACSSM_WAIT(bar, parity)                                  \
+  if (ok) {                                                        \
+    ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
+    if (!ok) *failed = 1;                                          \
+  }
     // =========================== control warp ===========================
-    const uint32_t sA0 = umma::smem_u32(area0), sA1 = umma::smem_u32(area1);
-    const uint32_t sS = umma::smem_u32(s_tile), sSlo = umma::smem_u32(slo_tile), sU = umma::smem_u32(u_tile);
-    const uint32_t sClo = umma::smem_u32(chat_lo);
+    const uint32_t sb = umma::smem_u32(smem);
+    const uint32_t sA0 = sb + kOffA0, sB0 = sb + kOffB0, sY1 = sb + kOffY1, sZ1 = sb + kOffZ1, sY2 = sb + kOffY2,
+                   sZ2 = sb + kOffZ2, sU = sb + kOffU;
+    const uint32_t sKhi = sb + kOffKhi, sKlo = sb + kOffKlo, sChi = sb + kOffChi, sClo = sb + kOffClo,
+                   sW = sb + kOffW, sS = sb + kOffS;
     constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
-    constexpr uint32_t kIdKK64 = umma::make_idesc(128, 64, false, false);
-    constexpr uint32_t kIdKK32 = umma::make_idesc(128, 32, false, false);
     constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
+    constexpr uint32_t kIdKMn128 = umma::make_idesc(128, 128, false, true);
     constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
     // One GEMM piece = 8 contraction steps of 16.  A K-major 128-column tile advances by 32 bytes
     // inside a 64-column atom and by one atom after 4 steps; an MN-major tile by 16 rows (2048 B).
-    // The loop is kept rolled so the control warp needs few registers.
-    auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t b_sbo,
-                     uint32_t idesc, uint32_t acc_first) {
+    auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t idesc,
+                     uint32_t acc_first) {
       const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
-      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, b_sbo);
+      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, 1024);
 #pragma unroll
       for (uint32_t s = 0; s < 8; ++s) {
         const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
@@ -196,13 +209,14 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 #pragma unroll 1
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
+      const int jt = j + a.first_tile;  // tile index inside the row
       // The next ticket is taken a tile ahead (the workers read it in the second half of this tile,
       // and its inputs are pulled into L2 now) and published through item_bar.  In the first tile of
       // a CTA this has to wait until the workers have read the first item, i.e. until their arrival
-      // on full[0]: two completions of item_bar in a row would flip its parity twice, and a worker
+      // on fA: two completions of item_bar in a row would flip its parity twice, and a worker
       // that had not looked yet would wait for a phase that never comes.  From the second tile on
       // every worker has read item n before the control warp can get here (the read precedes the
-      // worker's arrival on out_bar of the previous tile).
+      // worker's arrival on fW of the previous tile).
       int next = 0;
       auto take_next = [&]() {
         if (lane == 0) {
@@ -213,8 +227,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         next = __shfl_sync(0xffffffffu, next, 0);
         if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
           const int nj = next / a.BH, nb = next - nj * a.BH;
-          const int ntok = min(kTile, a.L - nj * kTile);
-          const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
+          const int tk0 = (nj + a.first_tile) * kTile;
+          const int ntok = min(kTile, a.L - tk0);
+          const int64_t tok = static_cast<int64_t>(nb) * a.L + tk0;
           umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
           constexpr int kCkBytes = CKF32 ? 4 : 2;
           umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
@@ -222,82 +237,81 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         }
       };
       if (n > 0) take_next();
-      if (n > 0) { FRACSSM_WAIT(barH, n - 1); }  // every MMA of the previous tile has finished
-      if (lane == 0) {
-        umma::mbar_expect_tx(barU, kTile * kR * 2);
-        umma::tma_load_3d(u_tile, &u_map, barU, 0, j * kTile, bh);
-      }
       // base: D[t,k] = A0[t,:] . B0[k,:]
-      FRACSSM_WAIT(full + 0, n);
+      FRACSSM_WAIT(fA, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColBase, sA0, false, sA0 + kTileBytes, false, 1024, kIdKK128, 0u);
-        umma::mma_commit(cb + 0);
+        piece(kColBase, sA0, false, sB0, false, kIdKK128, 0u);
+        umma::mma_commit(cb0);
       }
       if (n == 0) take_next();
-      // levels 8 and 16 (area1): first halves are picked by the B descriptor's row-group stride
-      FRACSSM_WAIT(full + 1, n);
+      // the u tile is free once every MMA of the previous tile has finished
+      if (n > 0) { FRACSSM_WAIT(barH, n - 1); }
+      if (lane == 0) {
+        umma::mbar_expect_tx(barU, kTile * kR * 2);
+        umma::tma_load_3d(smem + kOffU, &u_map, barU, 0, jt * kTile, bh);
+      }
+      // levels 8 + 16, then 64 + 32: A rows x B rows of the stacked tiles
+      FRACSSM_WAIT(fL1, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColL8, sA1, false, sA1, false, 2048, kIdKK64, 0u);                      // every other 8-row group
-        piece(kColL16, sA1 + kTileBytes, false, sA1 + kTileBytes, false, 4096, kIdKK32, 0u);   // groups 0,4,8,12
-        piece(kColL16 + 32, sA1 + kTileBytes, false, sA1 + kTileBytes + 1024, false, 4096, kIdKK32, 0u);  // 1,5,9,13
-        umma::mma_commit(cb + 1);
+        piece(kColL1, sY1, false, sZ1, false, kIdKK128, 0u);
+        umma::mma_commit(cb1);
       }
-      // levels 32 and 64 (the Chat-low and state slots, idle until late in the tile)
-      FRACSSM_WAIT(full + 2, n);
+      FRACSSM_WAIT(fL2, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColL32, sClo, false, sClo, false, 1024, kIdKK32, 0u);                   // rows 0..31
-        piece(kColL32 + 32, sClo, false, sClo + 8192, false, 1024, kIdKK32, 0u);       // rows 64..95
-        piece(kColL64, sS, false, sS, false, 1024, kIdKK64, 0u);                       // rows 0..63
-        umma::mma_commit(cb + 2);
+        piece(kColL2, sY2, false, sZ2, false, kIdKK128, 0u);
+        umma::mma_commit(cb2);
       }
-      // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
       // the state left by the previous tile of this (batch, head) row is usually there already:
       // look before the wait for the workers, when this warp has nothing else to do
       bool early = false;
       if (lane == 0) {
-        early = j == 0 || ld_acquire(a.flags + bh) >= j;
+        early = jt == 0 || ld_acquire(a.flags + bh) >= jt;
         if (early) umma::mbar_arrive(state_bar);
       }
-      FRACSSM_WAIT(full + 3, n);
+      // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
+      FRACSSM_WAIT(fK, n);
       FRACSSM_WAIT(barU, n);
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColS, sA0 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 0u);
-        piece(kColS, sA1 + kTileBytes, true, sU, true, 1024, kIdMnMn64, 1u);
-        umma::mma_commit(cb + 3);
+        piece(kColS, sKhi, true, sU, true, kIdMnMn64, 0u);
+        piece(kColS, sKlo, true, sU, true, kIdMnMn64, 1u);
+        umma::mma_commit(cbK);
         if (!early) {
           if (ok) {
             const uint64_t t_start = umma::global_ns();
-            while (ld_acquire(a.flags + bh) < j) {
+            while (ld_acquire(a.flags + bh) < jt) {
               __nanosleep(100);
-              if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+              if (umma::global_ns() - t_start > wait_ns) { ok = false; *failed = 1; break; }
             }
           }
           umma::mbar_arrive(state_bar);
         }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      // publish the outgoing state as soon as the workers have stored it: their stores are ordered
-      // before their arrivals on out_bar, this release makes them visible to the next tile's CTA
-      FRACSSM_WAIT(out_bar, n);
-      if (lane == 0 && j + 1 < a.ntiles) st_release(a.flags + bh, j + 1);
-      // H = Chat S, both factors split into bf16 high and low parts (low x low dropped)
-      FRACSSM_WAIT(full + 5, n);
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColH, sA0, false, sS, true, 1024, kIdKMn64, 0u);    // Chat(high) S(high)
-        piece(kColH, sA1, false, sS, true, 1024, kIdKMn64, 1u);    // Chat(low)  S(high)
-        piece(kColH, sA0, false, sSlo, true, 1024, kIdKMn64, 1u);  // Chat(high) S(low)
+      FRACSSM_WAIT(fW, n);
+      FRACSSM_WAIT(fS, n);
+      // Publish the outgoing state as soon as the workers have stored it: their stores are ordered
+      // before their arrivals on out_bar, this release makes them visible to the next tile's CTA.
+      // If they are not done yet, the output MMAs go first.
+      bool released = false;
+      if (umma::mbar_test(out_bar, n & 1u)) {
+        if (lane == 0 && jt + 1 < a.ntiles) st_release(a.flags + bh, jt + 1);
+        released = true;
       }
-      // H += W u
-      FRACSSM_WAIT(full + 4, n);
+      // H = Chat S (both split into bf16 high and low parts, low x low dropped) + W u
       umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColH, sClo, false, sU, true, 1024, kIdKMn64, 1u);
+        piece(kColH, sChi, false, sS, true, kIdKMn128, 0u);   // Chat(high) [S(high) | S(low)], 128 columns
+        piece(kColH, sClo, false, sS, true, kIdKMn64, 1u);    // Chat(low) S(high)
+        piece(kColH, sW, false, sU, true, kIdKMn64, 1u);      // W u
         umma::mma_commit(barH);
+      }
+      if (!released) {
+        FRACSSM_WAIT(out_bar, n);
+        if (lane == 0 && jt + 1 < a.ntiles) st_release(a.flags + bh, jt + 1);
       }
       __syncwarp();
       item = next;
@@ -305,205 +319,340 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   } else {
     // =========================== worker warps ===========================
 #undef FRACSSM_WAIT
-#define FRACSSM_WAIT(bar, parity) \
-  if (ok) ok = umma::mbar_wait_parked(bar, (parity) & 1u, kWaitNs)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
-    const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its column part
-    // operand-tile addressing of this thread: rows 8w..8w+7, modes 4*lane..4*lane+3
-    const uint32_t th_off = (lane >> 4) * kAtom + ((lane & 1) << 3) + w * 1024;
-    const uint32_t c16 = ((lane & 15) >> 1) << 4;
-    const uint32_t sArea0 = umma::smem_u32(area0), sArea1 = umma::smem_u32(area1);
-    const uint32_t sChatLo = umma::smem_u32(chat_lo), sSt = umma::smem_u32(s_tile);
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
-    // worker thread 0 charges the cycles since the last mark to a phase (diagnostic)
-    long long t_mark = clock64();
-#define FRACSSM_MARK(phase)                         \
-  if (PROF && tid == 0) {                           \
-    const long long now_ = clock64();               \
-    prof[phase] += now_ - t_mark;                   \
-    t_mark = now_;                                  \
+#define FRACSSM_WAIT(bar, parity)                                         \
+  if (ok) {                                                               \
+    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);             \
+    if (!ok) *failed = 1;                                                 \
   }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
+    const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its share of the columns
+    const uint32_t sb = umma::smem_u32(smem);
+    // operand-tile addressing of this thread: modes 4*lane..4*lane+3 of a row; the row group and the
+    // row inside it are added per store (emit_words)
+    const uint32_t th_fix = (lane >> 4) * kAtom + ((lane & 1) << 3) + (((lane & 15) >> 1) << 4);
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
+    const uint32_t seg_s = sb + kOffSeg + 16 * lane;  // this lane's four modes of segment 0
+    const float kNaN = __int_as_float(0x7fc00000);
 
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
     int prev_bh = 0, prev_t0 = 0;
-    // Output rows of tile number n_done (its H accumulator is complete when barH fires).  It runs at
-    // the start of the next tile, after that tile's input loads have been issued, so the loads'
-    // latency is covered by this work.
+    // Output rows of the previous tile (its H accumulator is complete when barH fires).  It runs in
+    // the middle of the next tile, so that tile's first phase overlaps the output MMAs.
     auto write_rows = [&](uint32_t n_done) {
       FRACSSM_WAIT(barH, n_done);
       umma::tc_fence_after();
-      FRACSSM_MARK(13)
-      float acc[16];
-      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
-      umma::tmem_ld_wait();
+      const bool bad = *failed != 0;
       const int t = prev_t0 + 32 * Q + lane;
-      if (t < a.L) {
-        uint4 lo, hi;
-        lo.x = pack2(acc[0], acc[1]); lo.y = pack2(acc[2], acc[3]); lo.z = pack2(acc[4], acc[5]); lo.w = pack2(acc[6], acc[7]);
-        hi.x = pack2(acc[8], acc[9]); hi.y = pack2(acc[10], acc[11]); hi.z = pack2(acc[12], acc[13]); hi.w = pack2(acc[14], acc[15]);
-        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
-        __stcs(dst, lo);
-        __stcs(dst + 1, hi);
+      uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float hi[8], lo[8];
+        umma::tmem_ld8(lane_addr + kColH + 16 * P + 8 * half, hi);
+        umma::tmem_ld8(lane_addr + kColH + 64 + 16 * P + 8 * half, lo);
+        umma::tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 8; ++x) hi[x] = bad ? kNaN : hi[x] + lo[x];
+        if (t < a.L) {
+          uint4 o;
+          o.x = pack2(hi[0], hi[1]); o.y = pack2(hi[2], hi[3]); o.z = pack2(hi[4], hi[5]); o.w = pack2(hi[6], hi[7]);
+          __stcs(dst + half, o);
+        }
       }
       umma::tc_fence_before();
-      FRACSSM_MARK(14)
     };
 
+    RawRegs<CKF32> raw0;
+    if (item < a.total) load_raw(raw0, a, item, w, lane, 0);
     uint32_t n_tiles_done = 0;
     for (uint32_t n = 0; item < a.total; ++n, ++n_tiles_done) {
       const int j = item / a.BH, bh = item - j * a.BH;
-      const int t0 = j * kTile;
+      const int jt = j + a.first_tile;
+      const int t0 = jt * kTile;
 
-      // ---- segment products and the base tiles, from the raw registers; one group of 4 tokens
-      // at a time to keep few values live
-      float2 cp[8][2], ks[8][2];
-      float g8[4];
+      // ---- segment products, the base tiles and the per-token factors cp / ks:
+      //   cp[i] = c[i] * (decay from the segment's start to token i, inclusive)
+      //   ks[i] = kappa[i] * (decay after token i to the segment's end)
+      f2 cp[8][2], ks[8][2];
+      f2 g8[2];
       {
-        // the inputs were pulled into L2 a tile ahead; both groups are requested at once
-        RawRegs<CKF32> raw0, raw1;
-        load_raw(raw0, a, item, w, lane, 0);
-        load_raw(raw1, a, item, w, lane, 1);
-        if (n > 0) write_rows(n - 1);  // the previous tile's output, while the loads are in flight
-        float ga[4], gb[4];
+        RawRegs<CKF32> raw1;
+        load_raw(raw1, a, item, w, lane, 1);   // second half of the segment; the first half is in raw0
+        const uint32_t rowsA = sb + kOffA0 + w * 1024 + th_fix, rowsB = sb + kOffB0 + w * 1024 + th_fix;
+        f2 g4a[2], g4b[2];
+        uint32_t wa[4][2], wb[4][2];
+        // tokens 0..3: reference point just after token 3
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-          const RawRegs<CKF32> &raw = grp ? raw1 : raw0;
-          float a0[4][4], b0[4][4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float rr[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 v = raw.r[i];
-              rr[i] = fmaxf(q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w, kRhoFloor);
-            }
-            // p4: running product from the start of the group (inclusive)
-            // s4: product of the tokens after t up to the end of the group (exclusive)
-            float p4[4], s4[4];
-            p4[0] = rr[0]; p4[1] = p4[0] * rr[1]; p4[2] = p4[1] * rr[2]; p4[3] = p4[2] * rr[3];
-            s4[3] = 1.f; s4[2] = rr[3]; s4[1] = s4[2] * rr[2]; s4[0] = s4[1] * rr[1];
-            if (grp == 0) ga[q] = p4[3]; else gb[q] = p4[3];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float cf = ck_get(raw.c[i], q), kf = ck_get(raw.k[i], q);
-              float &cpv = (q & 1) ? cp[4 * grp + i][q >> 1].y : cp[4 * grp + i][q >> 1].x;
-              float &ksv = (q & 1) ? ks[4 * grp + i][q >> 1].y : ks[4 * grp + i][q >> 1].x;
-              if (grp == 0) {  // base reference point: between token 3 and token 4 of the segment
-                a0[i][q] = __fdividef(cf, s4[i]);
-                b0[i][q] = kf * s4[i];
-                cpv = cf * p4[i];
-                ksv = kf * s4[i];          // times gb, below
-              } else {
-                a0[i][q] = cf * p4[i];
-                b0[i][q] = __fdividef(kf, p4[i]);
-                cpv = cf * ga[q] * p4[i];
-                ksv = kf * s4[i];
-              }
-            }
-          }
+        for (int hf = 0; hf < 2; ++hf) {
+          f2 r[4], cc[4], kk[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            emit_row(sArea0, th_off, c16, 4 * grp + i, make_float2(a0[i][0], a0[i][1]), make_float2(a0[i][2], a0[i][3]));
-            emit_row(sArea0 + kTileBytes, th_off, c16, 4 * grp + i, make_float2(b0[i][0], b0[i][1]),
-                     make_float2(b0[i][2], b0[i][3]));
+            f2 rp[2], cq[2], kq[2];
+            rho_pairs(raw0.r[i], rp);
+            ck_pairs(raw0.c[i], cq);
+            ck_pairs(raw0.k[i], kq);
+            r[i] = rp[hf]; cc[i] = cq[hf]; kk[i] = kq[hf];
           }
+          const f2 q2 = r[3], q1 = mul2(r[3], r[2]), q0 = mul2(q1, r[1]);    // decay after token i up to token 3
+          const f2 p1 = mul2(r[0], r[1]), p2 = mul2(p1, r[2]), p3 = mul2(p2, r[3]);
+          const f2 iq0 = rcp2(q0), iq1 = mul2(iq0, r[1]), iq2 = mul2(iq1, r[2]);
+          g4a[hf] = p3;
+          const f2 b0 = mul2(kk[0], q0), b1 = mul2(kk[1], q1), b2 = mul2(kk[2], q2);
+          wa[0][hf] = cvt_bf2(mul2(cc[0], iq0));
+          wa[1][hf] = cvt_bf2(mul2(cc[1], iq1));
+          wa[2][hf] = cvt_bf2(mul2(cc[2], iq2));
+          wa[3][hf] = cvt_bf2(cc[3]);
+          wb[0][hf] = cvt_bf2(b0); wb[1][hf] = cvt_bf2(b1); wb[2][hf] = cvt_bf2(b2); wb[3][hf] = cvt_bf2(kk[3]);
+          cp[0][hf] = mul2(cc[0], r[0]); cp[1][hf] = mul2(cc[1], p1); cp[2][hf] = mul2(cc[2], p2);
+          cp[3][hf] = mul2(cc[3], p3);
+          ks[0][hf] = b0; ks[1][hf] = b1; ks[2][hf] = b2; ks[3][hf] = kk[3];   // times g4b, below
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) g8[q] = ga[q] * gb[q];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          ks[i][0] = __fmul2_rn(ks[i][0], make_float2(gb[0], gb[1]));
-          ks[i][1] = __fmul2_rn(ks[i][1], make_float2(gb[2], gb[3]));
+          emit_words(rowsA, i, wa[i][0], wa[i][1]);
+          emit_words(rowsB, i, wb[i][0], wb[i][1]);
         }
-        *reinterpret_cast<float4 *>(seg + w * kM + 4 * lane) = make_float4(g8[0], g8[1], g8[2], g8[3]);
-      }
-      warp_arrive(full + 0, lane);
-      umma::named_barrier(1, kWorkers);  // segment products visible to every worker
-      FRACSSM_MARK(0)
-
-      // One sibling level: every token row holds its A-role or B-role value.
-      auto produce_level = [&](uint32_t tile_s, int hseg) {
-        float2 sig[2];
-        const bool role_a = (w & hseg) != 0;
-        const int first = w - (w & (hseg - 1));
-        if (role_a) seg_prod(seg, first, w, lane, sig);
-        else seg_prod(seg, w + 1, first + hseg, lane, sig);
+        // tokens 4..7: reference point just before token 4
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          emit_row(tile_s, th_off, c16, i, __fmul2_rn(role_a ? cp[i][0] : ks[i][0], sig[0]),
-                   __fmul2_rn(role_a ? cp[i][1] : ks[i][1], sig[1]));
+        for (int hf = 0; hf < 2; ++hf) {
+          f2 r[4], cc[4], kk[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            f2 rp[2], cq[2], kq[2];
+            rho_pairs(raw1.r[i], rp);
+            ck_pairs(raw1.c[i], cq);
+            ck_pairs(raw1.k[i], kq);
+            r[i] = rp[hf]; cc[i] = cq[hf]; kk[i] = kq[hf];
+          }
+          const f2 q5 = mul2(r[0], r[1]), q6 = mul2(q5, r[2]), q7 = mul2(q6, r[3]);  // decay from token 4 to token i
+          const f2 s5 = mul2(r[3], r[2]), s4 = mul2(s5, r[1]);                        // decay after token i to token 7
+          const f2 iq7 = rcp2(q7), iq6 = mul2(iq7, r[3]), iq5 = mul2(iq6, r[2]), iq4 = mul2(iq5, r[1]);
+          g4b[hf] = q7;
+          const f2 a4 = mul2(cc[0], r[0]), a5 = mul2(cc[1], q5), a6 = mul2(cc[2], q6), a7 = mul2(cc[3], q7);
+          wa[0][hf] = cvt_bf2(a4); wa[1][hf] = cvt_bf2(a5); wa[2][hf] = cvt_bf2(a6); wa[3][hf] = cvt_bf2(a7);
+          wb[0][hf] = cvt_bf2(mul2(kk[0], iq4));
+          wb[1][hf] = cvt_bf2(mul2(kk[1], iq5));
+          wb[2][hf] = cvt_bf2(mul2(kk[2], iq6));
+          wb[3][hf] = cvt_bf2(mul2(kk[3], iq7));
+          cp[4][hf] = mul2(a4, g4a[hf]); cp[5][hf] = mul2(a5, g4a[hf]); cp[6][hf] = mul2(a6, g4a[hf]);
+          cp[7][hf] = mul2(a7, g4a[hf]);
+          ks[4][hf] = mul2(kk[0], s4); ks[5][hf] = mul2(kk[1], s5); ks[6][hf] = mul2(kk[2], r[3]); ks[7][hf] = kk[3];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          emit_words(rowsA, 4 + i, wa[i][0], wa[i][1]);
+          emit_words(rowsB, 4 + i, wb[i][0], wb[i][1]);
+        }
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ks[i][hf] = mul2(ks[i][hf], g4b[hf]);
+          g8[hf] = mul2(g4a[hf], g4b[hf]);
+        }
+        asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(seg_s + w * (kM * 4)), "l"(g8[0]), "l"(g8[1]) : "memory");
+      }
+      warp_arrive(fA, lane);
+      umma::named_barrier(1, kWorkers);  // segment products visible to every worker
+      if (n > 0) write_rows(n - 1);  // also: every MMA of the previous tile is done, slots 2..5 are free
+
+      // ---- products of whole segments: back from this segment to the start of its 16 / 32 / 64 /
+      // 128-token block (bk), forward from it to the end of that block (fw).  A level uses bk when
+      // this segment sits in the second half of the level's block (A role), else fw (B role).  The
+      // products grow level by level, interleaved with the levels' operand rows.
+      f2 bk[2] = {one2(), one2()}, fw[2] = {one2(), one2()};
+      auto mulseg = [&](f2 (&acc)[2], int s) {
+        f2 x, y;
+        lds_f2x2(seg_s + s * (kM * 4), x, y);
+        acc[0] = mul2(acc[0], x);
+        acc[1] = mul2(acc[1], y);
       };
-
-      // ---- levels 8 and 16 -> area1
-      produce_level(sArea1, 1);
-      produce_level(sArea1 + kTileBytes, 2);
-      warp_arrive(full + 1, lane);
-      FRACSSM_MARK(1)
-
-      // ---- levels 32 and 64 -> the Chat-low and state slots (their readers finished with the
-      // previous tile), so nothing has to be waited for here
-      produce_level(sChatLo, 4);
-      produce_level(sSt, 8);
-      warp_arrive(full + 2, lane);
-      FRACSSM_MARK(3)
-
-      // ---- Chat (high) and Khat (high) -> area0 (after the base MMAs), Chat (low) -> area1 tile 0
-      // (after the level-8/16 MMAs)
-      FRACSSM_WAIT(cb + 0, n);
-      FRACSSM_MARK(2)
-      FRACSSM_WAIT(cb + 1, n);
-      FRACSSM_MARK(4)
-      {
-        float2 e[2], f[2];
-        seg_prod(seg, 0, w, lane, e);
-        seg_prod(seg, w + 1, 16, lane, f);
-        if (w == 0)
-          *reinterpret_cast<float4 *>(gt_s + 4 * lane) =
-              make_float4(g8[0] * f[0].x, g8[1] * f[0].y, g8[2] * f[1].x, g8[3] * f[1].y);
+      // One sibling level: this segment's 8 rows go to the A-role or the B-role tile of its stack.
+      auto emit_level = [&](uint32_t rows_s, const f2 (&src)[8][2], const f2 (&sig)[2], bool scale) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float2 cl[2], kl[2];
-          uint32_t pch[2], pkh[2];  // the high parts, already packed
+          const f2 v0 = scale ? mul2(src[i][0], sig[0]) : src[i][0];
+          const f2 v1 = scale ? mul2(src[i][1], sig[1]) : src[i][1];
+          emit_words(rows_s, i, cvt_bf2(v0), cvt_bf2(v1));
+        }
+      };
+      // ---- levels 8 (rows 0..63 of the stack) and 16 (rows 64..127) -> slots 2 / 3
+      {
+        const uint32_t rg8 = w >> 1, rg16 = 8 + (((w >> 2) << 1) | (w & 1));
+        if (w & 1) emit_level(sb + kOffY1 + rg8 * 1024 + th_fix, cp, bk, false);
+        else emit_level(sb + kOffZ1 + rg8 * 1024 + th_fix, ks, bk, false);
+        if (w & 1) mulseg(bk, w - 1); else mulseg(fw, w + 1);
+        if (w & 2) emit_level(sb + kOffY1 + rg16 * 1024 + th_fix, cp, bk, true);
+        else emit_level(sb + kOffZ1 + rg16 * 1024 + th_fix, ks, fw, true);
+      }
+      warp_arrive(fL1, lane);
+      // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
+      {
+        const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
+        const int b4 = w & ~3, b8 = w & ~7;
+        if (w & 2) { mulseg(bk, b4); mulseg(bk, b4 + 1); } else { mulseg(fw, b4 + 2); mulseg(fw, b4 + 3); }
+        if (w & 4) emit_level(sb + kOffY2 + rg32 * 1024 + th_fix, cp, bk, true);
+        else emit_level(sb + kOffZ2 + rg32 * 1024 + th_fix, ks, fw, true);
+        if (w & 4) {
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const float2 chat = __fmul2_rn(cp[i][hf], e[hf]);
-            const float2 ch = bf16_round2(chat, pch[hf]);
-            cl[hf] = __fadd2_rn(chat, make_float2(-ch.x, -ch.y));
-            const float2 full_k = __fmul2_rn(ks[i][hf], f[hf]);
-            const float2 kh = bf16_round2(full_k, pkh[hf]);
-            kl[hf] = __fadd2_rn(full_k, make_float2(-kh.x, -kh.y));
-          }
-          emit_row_packed(sArea0, th_off, c16, i, pch[0], pch[1]);
-          emit_row(sArea1, th_off, c16, i, cl[0], cl[1]);
-          emit_row_packed(sArea0 + kTileBytes, th_off, c16, i, pkh[0], pkh[1]);
-          emit_row(sArea1 + kTileBytes, th_off, c16, i, kl[0], kl[1]);
+          for (int s = 0; s < 4; ++s) mulseg(bk, b8 + s);
+        } else {
+#pragma unroll
+          for (int s = 4; s < 8; ++s) mulseg(fw, b8 + s);
+        }
+        if (w & 8) emit_level(sb + kOffY2 + rg64 * 1024 + th_fix, cp, bk, true);
+        else emit_level(sb + kOffZ2 + rg64 * 1024 + th_fix, ks, fw, true);
+      }
+      warp_arrive(fL2, lane);
+      // to the tile's start (E) and end (F)
+      if (w & 8) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) mulseg(bk, s);
+      } else {
+#pragma unroll
+        for (int s = 8; s < 16; ++s) mulseg(fw, s);
+      }
+      const f2 (&E)[2] = bk, (&F)[2] = fw;
+      // decay of the whole tile for the mode this thread owns in the state update (m = 32 Q + lane):
+      // every warp holds the full vector, four modes per lane
+      float gt_row;
+      {
+        float g[4];
+        un2(mul2(mul2(E[0], g8[0]), F[0]), g[0], g[1]);
+        un2(mul2(mul2(E[1], g8[1]), F[1]), g[2], g[3]);
+        const int src = 8 * Q + (lane >> 2);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) g[x] = __shfl_sync(0xffffffffu, g[x], src);
+        const int cmp = lane & 3;
+        gt_row = cmp == 0 ? g[0] : cmp == 1 ? g[1] : cmp == 2 ? g[2] : g[3];
+      }
+
+      // ---- Khat = ks * (decay to the tile's end), high and low parts -> slots 0 / 1 (base product done)
+      FRACSSM_WAIT(cb0, n);
+      {
+        const uint32_t rowsH = sb + kOffKhi + w * 1024 + th_fix, rowsL = sb + kOffKlo + w * 1024 + th_fix;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const f2 k0 = mul2(ks[i][0], F[0]), k1 = mul2(ks[i][1], F[1]);
+          const uint32_t h0 = cvt_bf2(k0), h1 = cvt_bf2(k1);
+          emit_words(rowsH, i, h0, h1);
+          emit_words(rowsL, i, cvt_bf2(sub2(k0, widen_bf2(h0))), cvt_bf2(sub2(k1, widen_bf2(h1))));
         }
       }
-      warp_arrive(full + 3, lane);
-      FRACSSM_MARK(5)
+      // ---- Chat = cp * (decay from the tile's start) -> slots 2 / 3 (level-8/16 product done)
+      FRACSSM_WAIT(cb1, n);
+      {
+        const uint32_t rowsH = sb + kOffChi + w * 1024 + th_fix, rowsL = sb + kOffClo + w * 1024 + th_fix;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const f2 c0 = mul2(cp[i][0], E[0]), c1 = mul2(cp[i][1], E[1]);
+          const uint32_t h0 = cvt_bf2(c0), h1 = cvt_bf2(c1);
+          emit_words(rowsH, i, h0, h1);
+          emit_words(rowsL, i, cvt_bf2(sub2(c0, widen_bf2(h0))), cvt_bf2(sub2(c1, widen_bf2(h1))));
+        }
+      }
+      warp_arrive(fK, lane);
 
       // the next item (published by the control warp at the start of this tile); it must be read
-      // here, before this warp's arrival on out_bar lets the control warp move on and publish again
+      // here, before this warp's arrival on fW lets the control warp move on and publish again.
+      // Its first four token rows are requested now and arrive while the tile finishes.
       FRACSSM_WAIT(item_bar, n + 1);
       const int next = items[(n + 1) & 1];
-      FRACSSM_MARK(7)
+      if (next < a.total) load_raw(raw0, a, next, w, lane, 0);
 
-      // ---- the chain first: incoming state -> outgoing state, published for the next tile of the row
+      // ---- W -> slot 4: each block of accumulators goes to its place (levels 64+32 product done)
+      FRACSSM_WAIT(cb2, n);
+      umma::tc_fence_after();
+      {
+        const uint32_t sW = sb + kOffW;
+        // 8 accumulators of row t, columns 8 kc .. 8 kc + 7 of W, as one 16-byte store
+        auto put8 = [&](int t, int kc, const auto &v, int o) {
+          uint4 pk;
+          pk.x = pack2(v[o], v[o + 1]); pk.y = pack2(v[o + 2], v[o + 3]); pk.z = pack2(v[o + 4], v[o + 5]);
+          pk.w = pack2(v[o + 6], v[o + 7]);
+          const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                       : "memory");
+        };
+        const int grp = lane >> 3;  // row group of this lane inside the warp's 32 accumulator rows
+        float v[32];
+        if (P == 0) {
+          // base: row t = 32 Q + lane, its own segment's 8 columns, masked above the diagonal
+          umma::tmem_ld32(lane_addr + kColBase + 32 * Q, v);
+          umma::tmem_ld_wait();
+          float o[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const float s = grp == 0 ? v[x] : grp == 1 ? v[8 + x] : grp == 2 ? v[16 + x] : v[24 + x];
+            o[x] = x <= (lane & 7) ? s : 0.f;
+          }
+          put8(32 * Q + lane, 4 * Q + grp, o, 0);
+        } else if (Q < 2) {
+          if (P == 1) {
+            // level 8: accumulator row 32 Q + lane is token 64 Q + 16 grp + 8 + (lane & 7); its partner
+            // segment is the one before it
+            umma::tmem_ld32(lane_addr + kColL1 + 32 * Q, v);
+            umma::tmem_ld_wait();
+            float o[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) o[x] = grp == 0 ? v[x] : grp == 1 ? v[8 + x] : grp == 2 ? v[16 + x] : v[24 + x];
+            put8(64 * Q + 16 * grp + 8 + (lane & 7), 8 * Q + 2 * grp, o, 0);
+          } else {
+            // level 64: accumulator row 32 Q + lane is token 64 + 32 Q + lane; columns = tokens 0..63
+            const int c0 = 32 * (P - 2);
+            umma::tmem_ld32(lane_addr + kColL2 + c0, v);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 4; ++e) put8(64 + 32 * Q + lane, (c0 >> 3) + e, v, 8 * e);
+          }
+        } else {
+          const int q2 = Q - 2;
+          if (P == 1) {
+            // level 16: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 (lane >> 4) + 16 + (lane & 15);
+            // its partners are the 16 tokens before its 16-token half
+            umma::tmem_ld32(lane_addr + kColL1 + 64 + 32 * q2, v);
+            umma::tmem_ld_wait();
+            float o[16];
+#pragma unroll
+            for (int x = 0; x < 16; ++x) o[x] = (lane >> 4) ? v[16 + x] : v[x];
+            const int t = 64 * q2 + 32 * (lane >> 4) + 16 + (lane & 15);
+            const int kc = 8 * q2 + 4 * (lane >> 4);
+            put8(t, kc, o, 0);
+            put8(t, kc + 1, o, 8);
+          } else {
+            // level 32: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 + lane; partners: the 32
+            // tokens before its half
+            float u16[16];
+            umma::tmem_ld16(lane_addr + kColL2 + 64 + 32 * q2 + 16 * (P - 2), u16);
+            umma::tmem_ld_wait();
+            const int t = 64 * q2 + 32 + lane, kc = 8 * q2 + 2 * (P - 2);
+            put8(t, kc, u16, 0);
+            put8(t, kc + 1, u16, 8);
+          }
+        }
+        // zeros above the diagonal: row t = tid / 4 owns the blocks kc > t / 8, four threads share a row
+        {
+          const int t = tid >> 2;
+          for (int kc = (t >> 3) + 1 + (tid & 3); kc < 16; kc += 4) {
+            const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+          }
+        }
+      }
+      warp_arrive(fW, lane);
+
+      // ---- the chain: incoming state -> MMA operand (high | low) -> outgoing state
       FRACSSM_WAIT(state_bar, n);
-      umma::named_barrier(2, kWorkers);  // also orders warp 0's write of gt_s before its readers
-      FRACSSM_MARK(9)
       const int m_row = 32 * Q + lane;
       float sj[16];
       {
         // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
         const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
                            (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (j > 0) {
+        if (jt > 0) {
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
-            const float4 v = __ldcg(sp + x * kM);
-            sj[4 * x] = v.x; sj[4 * x + 1] = v.y; sj[4 * x + 2] = v.z; sj[4 * x + 3] = v.w;
+            const float4 s4 = __ldcg(sp + x * kM);
+            sj[4 * x] = s4.x; sj[4 * x + 1] = s4.y; sj[4 * x + 2] = s4.z; sj[4 * x + 3] = s4.w;
           }
         } else if (a.init) {
 #pragma unroll
@@ -514,19 +663,33 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           for (int x = 0; x < 16; ++x) sj[x] = 0.f;
         }
       }
-      FRACSSM_WAIT(cb + 3, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t ph[4], pl[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float2 sv = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
+          const float2 hi = bf16_round2(sv, ph[x]);
+          pl[x] = pack2(sv.x - hi.x, sv.y - hi.y);
+        }
+        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+        *reinterpret_cast<uint4 *>(smem + kOffS + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+        *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+      }
+      warp_arrive(fS, lane);
+
+      FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
       umma::tc_fence_after();
-      FRACSSM_MARK(11)
       {
         // S_next = Gt * S + Sacc
         float acc[16];
         umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
         umma::tmem_ld_wait();
-        const float gt = gt_s[m_row];
+        const bool bad = *failed != 0;
 #pragma unroll
-        for (int x = 0; x < 16; ++x) acc[x] = fmaf(gt, sj[x], acc[x]);
+        for (int x = 0; x < 16; ++x) acc[x] = bad ? kNaN : fmaf(gt_row, sj[x], acc[x]);
         float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (j + 1 < a.ntiles) {
+        if (jt + 1 < a.ntiles) {
 #pragma unroll
           for (int x = 0; x < 4; ++x)
             __stcg(sp + x * kM, make_float4(acc[4 * x], acc[4 * x + 1], acc[4 * x + 2], acc[4 * x + 3]));
@@ -539,78 +702,12 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       umma::tc_fence_before();
       __syncwarp();
       if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
-      FRACSSM_MARK(12)
-
-      // ---- every level MMA has completed: the state slot and the W slot are free
-      FRACSSM_WAIT(cb + 2, n);
-      umma::tc_fence_after();
-      FRACSSM_MARK(6)
-      // incoming state as MMA operands, bf16 high / low parts
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t ph[4], pl[4];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const float2 v = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
-          const float2 hi = bf16_round2(v, ph[x]);
-          pl[x] = pack2(v.x - hi.x, v.y - hi.y);
-        }
-        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-        *reinterpret_cast<uint4 *>(s_tile + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-        *reinterpret_cast<uint4 *>(slo_tile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-      }
-      warp_arrive(full + 5, lane);
-      FRACSSM_MARK(10)
-
-      // ---- W -> the Chat-low slot
-      {
-        uint8_t *wt = chat_lo;
-        const int t = 32 * Q + lane;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float v[8];
-          if (P > Q) {
-#pragma unroll
-            for (int x = 0; x < 8; ++x) v[x] = 0.f;
-          } else if (P < Q) {
-            const uint32_t col = ((Q >> 1) != (P >> 1)) ? (kColL64 + 32 * P + 8 * g)
-                                                        : (kColL32 + (P >> 1) * 32 + 8 * g);
-            umma::tmem_ld8(lane_addr + col, v);
-            umma::tmem_ld_wait();
-          } else {
-            float b[8], l8[8], l16[8];
-#pragma unroll
-            for (int x = 0; x < 8; ++x) l8[x] = l16[x] = 0.f;
-            umma::tmem_ld8(lane_addr + kColBase + 32 * Q + 8 * g, b);
-            if ((g & 1) == 0) umma::tmem_ld8(lane_addr + kColL8 + (2 * Q + (g >> 1)) * 8, l8);
-            if (g < 2) umma::tmem_ld8(lane_addr + kColL16 + (g & 1) * 32 + Q * 8, l16);
-            umma::tmem_ld_wait();
-            const int tb = lane >> 3;  // 8-token block of this row inside its 32-token block
-#pragma unroll
-            for (int x = 0; x < 8; ++x) {
-              float r = 0.f;
-              if (g == tb) r = (x <= (lane & 7)) ? b[x] : 0.f;
-              else if (g < tb) r = ((tb ^ g) >= 2) ? l16[x] : l8[x];
-              v[x] = r;
-            }
-          }
-          uint4 pk;
-          pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
-          const uint32_t chunk = (4 * P + g) & 7;
-          *reinterpret_cast<uint4 *>(wt + (P >> 1) * kAtom + t * 128 + ((chunk ^ (t & 7)) << 4)) = pk;
-        }
-      }
-      warp_arrive(full + 4, lane);
-      FRACSSM_MARK(8)
 
       prev_bh = bh;
       prev_t0 = t0;
       item = next;
     }
     if (n_tiles_done > 0) write_rows(n_tiles_done - 1);
-    if (PROF && tid == 0 && a.prof && blockIdx.x < kProfCtas) {
-      for (int i = 0; i < kProfPhases; ++i) a.prof[blockIdx.x * kProfPhases + i] = prof[i];
-    }
   }
 
   if (!ok) atomicExch(&a.ctrl[1], 1);
@@ -624,17 +721,23 @@ size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 }  // namespace
 
 size_t scan_fused_workspace_bytes(int64_t B, int64_t, int64_t R, int64_t M, int64_t) {
-  return kCtrlBytes + kProfBytes + align256((size_t)B * 4) + (size_t)B * R * M * 4;
+  return kCtrlBytes + align256((size_t)B * 4) + (size_t)B * R * M * 4;
 }
 
-int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
-                      const float *initial_state, void *h, void *final_state, int final_dtype,
-                      void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
-                      int64_t M, int64_t T, void *stream) {
+// first_tile / wait_ns: 0 and the default limit, except in the wait-limit self-test, which starts
+// at a tile whose predecessor is not part of the launch.
+int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
+                         const float *initial_state, void *h, void *final_state, int final_dtype,
+                         void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                         int64_t M, int64_t T, void *stream, int first_tile, unsigned long long wait_ns) {
   (void)T;
   const bool ckf32 = ck_dtype == FRACSSM_F32;
   if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
     return fail(FRACSSM_ERR_ARG, "frac_scan: workspace too small");
+  // the kernel reads c / kappa / rho and writes h with 8- and 16-byte accesses
+  if (((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(kappa) |
+        reinterpret_cast<uintptr_t>(rho) | reinterpret_cast<uintptr_t>(h)) & 15) != 0)
+    return fail(FRACSSM_ERR_ARG, "frac_scan: u, c, kappa, rho and h must be 16-byte aligned");
   // per device, once: opt in to the large dynamic shared memory and remember the SM count
   static std::mutex mu;
   static int sm_count[64] = {};
@@ -656,10 +759,8 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   {
     std::lock_guard<std::mutex> lock(mu);
     if (sm_count[dev] == 0) {
-      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, true>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, true>));
+      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true>));
       if (prc) return prc;
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -679,28 +780,32 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
   a.fin = final_state;
   a.fin_dt = final_dtype;
   a.ctrl = reinterpret_cast<int *>(ws);
-  a.prof = reinterpret_cast<long long *>(ws + kCtrlBytes);
-  a.flags = reinterpret_cast<int *>(ws + kCtrlBytes + kProfBytes);
-  a.state = reinterpret_cast<float *>(ws + kCtrlBytes + kProfBytes + align256((size_t)B * 4));
+  a.flags = reinterpret_cast<int *>(ws + kCtrlBytes);
+  a.state = reinterpret_cast<float *>(ws + kCtrlBytes + align256((size_t)B * 4));
   a.BH = (int)B;
   a.L = (int)L;
   a.ntiles = (int)ceil_div(L, kTile);
-  a.total = a.ntiles * a.BH;
+  a.first_tile = first_tile;
+  a.total = (a.ntiles - first_tile) * a.BH;
+  a.wait_ns = wait_ns;
   CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
   if (rc) return rc;
-  cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + kProfBytes + align256((size_t)B * 4), (cudaStream_t)stream);
+  cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + align256((size_t)B * 4), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
-  // FRACSSM_SCAN_PROFILE=1 in the environment selects the build that records per-phase cycles
-  const char *pe = getenv("FRACSSM_SCAN_PROFILE");
-  const bool prof = pe && pe[0] != '\0' && pe[0] != '0';
   const cudaStream_t st = (cudaStream_t)stream;
-  if (ckf32 && prof) scan_fused_kernel<true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-  else if (ckf32) scan_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-  else if (prof) scan_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-  else scan_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  if (ckf32) scan_fused_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  else scan_fused_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
   return check_launch("frac_scan (single-pass kernel)");
+}
+
+int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
+                      const float *initial_state, void *h, void *final_state, int final_dtype,
+                      void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                      int64_t M, int64_t T, void *stream) {
+  return scan_fused_launch_ex(u, c, kappa, ck_dtype, rho, initial_state, h, final_state, final_dtype, workspace,
+                              workspace_bytes, B, L, R, M, T, stream, 0, kWaitNs);
 }
 
 }  // namespace fracssm
@@ -727,23 +832,6 @@ extern "C" int fracssm_scan_fused_status(const void *workspace, void *stream) {
   return FRACSSM_OK;
 }
 
-// Diagnostic: cycles thread 0 of each CTA spent in each of the 16 phases of the tile loop during
-// the last single-pass launch that used `workspace`, summed over CTAs (synchronises the stream).
-extern "C" int fracssm_scan_fused_phase_cycles(const void *workspace, long long *out16, void *stream) {
-  using namespace fracssm;
-  if (!workspace || !out16) return fail(FRACSSM_ERR_ARG, "scan_fused_phase_cycles: null pointer");
-  static long long host[kProfCtas * kProfPhases];
-  cudaError_t e = cudaMemcpyAsync(host, reinterpret_cast<const char *>(workspace) + kCtrlBytes, kProfBytes,
-                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
-  if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "scan_fused_phase_cycles: %s", cudaGetErrorString(e));
-  for (int p = 0; p < kProfPhases; ++p) {
-    out16[p] = 0;
-    for (int cta = 0; cta < kProfCtas; ++cta) out16[p] += host[cta * kProfPhases + p];
-  }
-  return FRACSSM_OK;
-}
-
 // ---------------------------------------------------------------------------------------------
 // Single-pass scan without any allocation by caller or library.
 //
@@ -758,7 +846,7 @@ namespace fracssm {
 namespace {
 constexpr int64_t kNoAllocMaxRows = 64;
 constexpr size_t kNoAllocBytes =
-    kCtrlBytes + kProfBytes + ((kNoAllocMaxRows * 4 + 255) / 256) * 256 + kNoAllocMaxRows * kR * kM * 4;
+    kCtrlBytes + ((kNoAllocMaxRows * 4 + 255) / 256) * 256 + kNoAllocMaxRows * kR * kM * 4;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
@@ -802,6 +890,9 @@ extern "C" int fracssm_frac_scan_fwd_noalloc(const void *u, const void *c, const
   if (!fracssm_scan_fused_supported(B, L, R, M, 128, FRACSSM_BF16, FRACSSM_BF16))
     return fail(FRACSSM_ERR_UNSUPPORTED, "frac_scan (no-alloc): needs R = 64, M = 128 and bfloat16 u, c, kappa");
   if (!u || !c || !kappa || !rho || !h) return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): null pointer");
+  if (((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(kappa) |
+        reinterpret_cast<uintptr_t>(rho) | reinterpret_cast<uintptr_t>(h)) & 15) != 0)
+    return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): u, c, kappa, rho and h must be 16-byte aligned");
   if (final_state && final_dtype != FRACSSM_F32 && final_dtype != FRACSSM_BF16)
     return fail(FRACSSM_ERR_ARG, "frac_scan (no-alloc): final_state dtype must be float32 or bfloat16");
   void *scratch = nullptr;
@@ -811,4 +902,13 @@ extern "C" int fracssm_frac_scan_fwd_noalloc(const void *u, const void *c, const
   // the kernel; the state rows are written before they are read.
   return scan_fused_launch(u, c, kappa, FRACSSM_BF16, rho, initial_state, h, final_state, final_dtype,
                            scratch, kNoAllocBytes, B, L, R, M, 128, stream);
+}
+
+// Error word of the last no-alloc launch on the current device (synchronises the stream).
+extern "C" int fracssm_frac_scan_noalloc_status(void *stream) {
+  using namespace fracssm;
+  void *scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  return fracssm_scan_fused_status(scratch, stream);
 }

@@ -38,6 +38,8 @@ struct SummaryArgs {
   float *state;  // running state per row (worker access order)
   float *dec;    // running decay product per row [BH, 128]
   int BH, L, ntiles, total;
+  int first_tile;              // tile index of the first ticket (0 except in the wait-limit self-test)
+  unsigned long long wait_ns;  // limit of every device-side wait
 };
 
 template <bool KF32>
@@ -55,6 +57,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
   uint64_t *barU = cb + 1, *full = cb + 2, *item_bar = cb + 3, *state_bar = cb + 4, *out_bar = cb + 5;
   uint32_t *tmem_s = reinterpret_cast<uint32_t *>(cb + 6);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);
+  volatile int *failed = reinterpret_cast<volatile int *>(tmem_s + 3);  // a wait of this CTA ran out
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -66,15 +69,20 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
     umma::mbar_init(out_bar, 16);
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
+    *failed = 0;
   }
   if (w == 0) umma::tmem_alloc(tmem_s, kTmemCols);
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
   const uint32_t tmem = *tmem_s;
+  const uint64_t wait_ns = a.wait_ns;
   bool ok = true;  // cleared when a bounded wait runs out; later waits are then skipped
-#define FRACSSM_WAIT(bar, parity) \
-  if (ok) ok = umma::mbar_wait_parked(bar, (parity) & 1u, kWaitNs)
+#define FRACSSM_WAIT(bar, parity)                                \
+  if (ok) {                                                      \
+    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);    \
+    if (!ok) *failed = 1;                                        \
+  }
 
   if (w > 16) {
     // spare warps: nothing to do
@@ -91,7 +99,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
     item = __shfl_sync(0xffffffffu, item, 0);
 #pragma unroll 1
     for (uint32_t n = 0; item < a.total; ++n) {
-      const int j = item / a.BH, bh = item - j * a.BH;
+      const int j = item / a.BH + a.first_tile, bh = item % a.BH;
       // The next ticket is taken a tile ahead and published through item_bar.  For the first tile it
       // has to wait until the workers have read the first item (their arrival on `full`): two
       // completions of item_bar in a row would flip its parity twice, and a worker that had not
@@ -106,7 +114,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
         }
         next = __shfl_sync(0xffffffffu, next, 0);
         if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
-          const int nj = next / a.BH, nb = next - nj * a.BH;
+          const int nj = next / a.BH + a.first_tile, nb = next % a.BH;
           const int ntok = min(kTile, a.L - nj * kTile);
           const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
           constexpr int kKb = KF32 ? 4 : 2;
@@ -140,7 +148,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
             const uint64_t t_start = umma::global_ns();
             while (ld_acquire(a.flags + bh) < j) {
               __nanosleep(100);
-              if (umma::global_ns() - t_start > kWaitNs) { ok = false; break; }
+              if (umma::global_ns() - t_start > wait_ns) { ok = false; *failed = 1; break; }
             }
           }
           umma::mbar_arrive(state_bar);
@@ -164,7 +172,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
     for (uint32_t n = 0; item < a.total; ++n) {
-      const int j = item / a.BH, bh = item - j * a.BH;
+      const int j = item / a.BH + a.first_tile, bh = item % a.BH;
       const int t0 = j * kTile + 8 * w;
       const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
       float4 rr[8];
@@ -252,19 +260,21 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
         umma::tmem_ld16(lane_addr + 16 * P, acc);
         umma::tmem_ld_wait();
         const float gt = gt_s[m_row];
+        // a wait that ran out leaves no valid state: NaN marks everything computed from it
+        const float mark = *failed == 0 ? 0.f : __int_as_float(0x7fc00000);
 #pragma unroll
-        for (int x = 0; x < 16; ++x) acc[x] = fmaf(gt, sj[x], acc[x]);
+        for (int x = 0; x < 16; ++x) acc[x] = fmaf(gt, sj[x], acc[x]) + mark;
         if (j + 1 < a.ntiles) {
           float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
 #pragma unroll
           for (int x = 0; x < 4; ++x)
             __stcg(sp + x * kM, make_float4(acc[4 * x], acc[4 * x + 1], acc[4 * x + 2], acc[4 * x + 3]));
-          if (P == 0) __stcg(a.dec + static_cast<int64_t>(bh) * kM + m_row, dec_in * gt);
+          if (P == 0) __stcg(a.dec + static_cast<int64_t>(bh) * kM + m_row, dec_in * gt + mark);
         } else {
 #pragma unroll
           for (int x = 0; x < 16; ++x)
             a.fin[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row] = acc[x];
-          if (P == 0) a.decay[static_cast<int64_t>(bh) * kM + m_row] = dec_in * gt;
+          if (P == 0) a.decay[static_cast<int64_t>(bh) * kM + m_row] = dec_in * gt + mark;
         }
       }
       umma::tc_fence_before();
@@ -292,11 +302,13 @@ extern "C" size_t fracssm_segment_summary_workspace_bytes(int64_t B, int64_t R, 
   return kCtrlBytes + align256((size_t)B * 4) + (size_t)B * R * M * 4 + align256((size_t)B * M * 4);
 }
 
-extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_dtype, const float *rho,
-                                       const float *initial_state, float *final_state, float *decay,
-                                       void *workspace, size_t workspace_bytes, int64_t B, int64_t L,
-                                       int64_t R, int64_t M, void *stream) {
-  using namespace fracssm;
+namespace fracssm {
+// first_tile / wait_ns: 0 and the default limit, except in the wait-limit self-test, which starts at a
+// tile whose predecessor is not part of the launch.
+int segment_summary_launch_ex(const void *u, const void *kappa, int k_dtype, const float *rho,
+                              const float *initial_state, float *final_state, float *decay, void *workspace,
+                              size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M, void *stream,
+                              int first_tile, unsigned long long wait_ns) {
   if (B < 0 || L < 0) return fail(FRACSSM_ERR_ARG, "segment_summary: bad sizes");
   if (R != kR || M != kM || (k_dtype != FRACSSM_BF16 && k_dtype != FRACSSM_F32))
     return fail(FRACSSM_ERR_UNSUPPORTED, "segment_summary: needs R = 64, M = 128, bfloat16 u and bfloat16 or float32 kappa");
@@ -308,6 +320,9 @@ extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_d
     return fail(FRACSSM_ERR_ARG, "segment_summary: null pointer");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
     return fail(FRACSSM_ERR_ARG, "segment_summary: workspace must be 256-byte aligned");
+  // the kernel reads kappa and rho with 8- and 16-byte accesses, u by TMA
+  if (((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(kappa) | reinterpret_cast<uintptr_t>(rho)) & 15) != 0)
+    return fail(FRACSSM_ERR_ARG, "segment_summary: u, kappa and rho must be 16-byte aligned");
   if (workspace_bytes < fracssm_segment_summary_workspace_bytes(B, R, M))
     return fail(FRACSSM_ERR_ARG, "segment_summary: workspace too small");
 
@@ -344,7 +359,9 @@ extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_d
   a.BH = (int)B;
   a.L = (int)L;
   a.ntiles = (int)ceil_div(L, kTile);
-  a.total = a.ntiles * a.BH;
+  a.first_tile = first_tile;
+  a.total = (a.ntiles - first_tile) * a.BH;
+  a.wait_ns = wait_ns;
   CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
   if (rc) return rc;
@@ -354,4 +371,13 @@ extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_d
   if (k_dtype == FRACSSM_F32) scan_summary_kernel<true><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
   else scan_summary_kernel<false><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(a, map);
   return check_launch("segment_summary");
+}
+}  // namespace fracssm
+
+extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_dtype, const float *rho,
+                                       const float *initial_state, float *final_state, float *decay,
+                                       void *workspace, size_t workspace_bytes, int64_t B, int64_t L,
+                                       int64_t R, int64_t M, void *stream) {
+  return fracssm::segment_summary_launch_ex(u, kappa, k_dtype, rho, initial_state, final_state, decay, workspace,
+                                            workspace_bytes, B, L, R, M, stream, 0, fracssm::tile::kWaitNs);
 }

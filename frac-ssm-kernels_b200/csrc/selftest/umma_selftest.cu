@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "tmap.cuh"
 #include "umma.cuh"
+#include "fracssm_selftest.h"
 
 namespace fracssm {
 
@@ -33,7 +34,7 @@ umma_selftest_kernel(const SelfTestArgs a, const __grid_constant__ CUtensorMap b
   for (int i = tid; i < 128 * 128; i += 128) {
     const int row = i / 128, col = i % 128;
     *reinterpret_cast<__nv_bfloat16 *>(tileA + umma::tile_off(row, col, 16384)) = __float2bfloat16_rn(a.A[i]);
-    if (!a.b_tma && (!a.b_mn || col < 64))
+    if (!a.b_tma && (!a.b_mn || col < a.N))
       *reinterpret_cast<__nv_bfloat16 *>(tileB + umma::tile_off(row, col, 16384)) = __float2bfloat16_rn(a.B[i]);
   }
   umma::fence_async_smem();
@@ -87,7 +88,9 @@ extern "C" int fracssm_selftest_umma(const float *A, const float *B, const void 
   using namespace fracssm;
   if (!A || !B || !D || !status) return fail(FRACSSM_ERR_ARG, "selftest_umma: null pointer");
   if (N < 16 || N > 128 || N % 16) return fail(FRACSSM_ERR_ARG, "selftest_umma: N must be a multiple of 16 in 16..128");
-  if (b_mn_major && N != 64) return fail(FRACSSM_ERR_ARG, "selftest_umma: MN-major B is a single 64-wide atom");
+  if (b_mn_major && N != 64 && N != 128)
+    return fail(FRACSSM_ERR_ARG, "selftest_umma: MN-major B is one or two 64-wide atoms");
+  if (b_via_tma && N != 64) return fail(FRACSSM_ERR_ARG, "selftest_umma: the TMA path loads one 64-wide atom");
   if (!b_mn_major && (b_sbo_bytes % 1024 || b_sbo_bytes <= 0 ||
                       (int64_t)b_row_group0 * 1024 + (int64_t)(N / 8 - 1) * b_sbo_bytes + 1024 > 16384))
     return fail(FRACSSM_ERR_ARG, "selftest_umma: B row groups leave the tile");

@@ -44,14 +44,12 @@ _SIGNATURES = {
     "fracssm_segment_summary_workspace_bytes": (sz, [i64, i64, i64]),
     "fracssm_segment_summary": (ci, [vp, vp, ci, vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, vp]),
     "fracssm_scan_fused_status": (ci, [vp, vp]),
-    "fracssm_scan_fused_phase_cycles": (ci, [vp, vp, vp]),
+    "fracssm_frac_scan_noalloc_status": (ci, [vp]),
     "fracssm_compute_params": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, ci, i64, i64,
                                     vp, i64, i64, vp, vp, cf, cf, cf, cf, cf, cf, cf, cf, cf,
                                     vp, vp, vp, ci, vp, i64, i64, i64, i64, i64, vp]),
     "fracssm_skip_mix": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, vp, ci, i64, i64, i64, i64, vp]),
     "fracssm_rmsnorm_gated": (ci, [vp, i64, vp, i64, ci, vp, ci, cf, vp, vp, i64, i64, vp]),
-    "fracssm_selftest_umma_m64": (ci, [vp, vp, vp, vp, ci, vp]),
-    "fracssm_selftest_umma": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "fracssm_scan_epilogue": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, vp, ci,
                                    cf, cf, vp, i64, i64, i64, i64, vp]),
     "fracssm_causal_conv_silu": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, vp, ci, vp, ci, i64, i64, i64,

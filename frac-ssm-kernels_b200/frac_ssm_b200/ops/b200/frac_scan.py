@@ -15,24 +15,8 @@ from ... import _cabi as C
 # "auto": the single-pass tcgen05 kernel when it covers the shape, else the staged kernels.
 _PATHS = {"auto": C.PATH_AUTO, "staged": C.PATH_STAGED, "fused": C.PATH_FUSED}
 
-_last_ws = None     # scratch of the last call made with keep_workspace=True (diagnostics)
-
-
-def last_phase_cycles():
-    """Cycles per phase of the single-pass kernel's tile loop in the last call made with
-    keep_workspace=True (16 numbers summed over CTAs; synchronises).  Diagnostic."""
-    import ctypes
-    if _last_ws is None:
-        raise RuntimeError("no call with keep_workspace=True yet")
-    out = (ctypes.c_longlong * 16)()
-    with torch.cuda.device(_last_ws.device):
-        C.check(C.lib().fracssm_scan_fused_phase_cycles(C.ptr(_last_ws), out, C.stream_of(_last_ws)),
-                "scan_fused_phase_cycles")
-    return list(out)
-
-
 def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False, *,
-              final_state_dtype=None, path="auto", check=False, keep_workspace=False):
+              final_state_dtype=None, path="auto", check=False):
     """Fractional chunked scan, forward.
 
     Args:
@@ -77,9 +61,9 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
     assert final_state_dtype in (torch.float32, torch.bfloat16)
 
     path_code = _PATHS[path]
-    if check or keep_workspace:      # diagnostics bypass the registered op (they need the scratch)
+    if check:      # the status read-back bypasses the registered op (it needs the scratch)
         h, fin = _launch(u, c, kappa, rho, chunk_size, initial_state, return_final_state,
-                         final_state_dtype == torch.float32, path_code, check, keep_workspace)
+                         final_state_dtype == torch.float32, path_code, check)
     else:
         h, fin = _frac_scan_fwd_op(u, c, kappa, rho, chunk_size, initial_state, return_final_state,
                                    final_state_dtype == torch.float32, path_code)
@@ -88,8 +72,7 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
     return h
 
 
-def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code, check=False,
-            keep_workspace=False):
+def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code, check=False):
     B, L, R = u.shape
     M = c.shape[-1]
     final_state_dtype = torch.float32 if final_fp32 else torch.bfloat16
@@ -102,9 +85,6 @@ def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32,
         with C.trace("frac_scan"), torch.cuda.device(u.device):
             nbytes = lib.fracssm_frac_scan_workspace_bytes(B, max(L, 1), R, M, chunk_size, path_code)
             ws = torch.empty(max(nbytes, 256), device=u.device, dtype=torch.uint8)
-            if keep_workspace:
-                global _last_ws
-                _last_ws = ws
             C.check(lib.fracssm_frac_scan_fwd(
                 C.ptr(u), C.dt(u), u.stride(0), u.stride(1), C.ptr(c), C.ptr(kappa), C.dt(c),
                 c.stride(0), c.stride(1), kappa.stride(0), kappa.stride(1), C.ptr(rho), rho.stride(0),

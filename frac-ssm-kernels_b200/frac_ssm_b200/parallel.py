@@ -95,16 +95,26 @@ def incoming_state(decay_all, final_all, rank, initial_state=None):
     return state
 
 
-def _auto_local_splits(B, L_local, chunk_size, world):
-    """How many sub-segments to cut this rank's segment into.  The scan kernels hand the state from
-    tile to tile of a row, so few rows mean few independent chains; sub-segments are extra rows.
-    Splitting costs one more read of u, kappa and rho, so a single rank does not split."""
+def _auto_local_splits(B, L_local, chunk_size, world, device, group=None):
+    """How many sub-segments every rank cuts its segment into (the same number on all ranks).
+
+    The scan kernels hand the state from tile to tile of a row, so few rows mean few independent
+    chains; sub-segments are extra rows.  Splitting costs one more read of u, kappa and rho, so a
+    single rank does not split.  Each rank can only judge its own segment (segments differ by a chunk
+    when the chunk count does not divide by the world size, and the last one may be ragged), so the
+    ranks agree on the smallest of their candidates with one MIN all-reduce of a single integer;
+    candidates are powers of two and a segment that can be cut into S whole-chunk pieces can also be
+    cut into any smaller power of two.  Reading the agreed value synchronises the host with the
+    device; callers that must not synchronise pass `local_splits` themselves.
+    """
     if world == 1:
         return 1
     s = 1
     while B * s < 148 and L_local % (2 * s * chunk_size) == 0 and L_local // (2 * s) >= 1024:
         s *= 2
-    return s
+    agreed = torch.tensor([s], dtype=torch.int64, device=device)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+    return int(agreed.item())
 
 
 def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False,
@@ -116,9 +126,10 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     the whole sequence, or None).  Returns this rank's `h` and, if requested, the final state of
     the WHOLE sequence (broadcast from the last rank).
 
-    `local_splits` (a divisor of L_local / chunk_size, the same on every rank; default chosen from
-    the row count) cuts each rank's segment into that many sub-segments which are scanned as extra
-    rows: with few (batch x head) rows this is what keeps all SMs busy.
+    `local_splits` (a divisor of L_local / chunk_size, the SAME on every rank) cuts each rank's
+    segment into that many sub-segments which are scanned as extra rows: with few (batch x head)
+    rows this is what keeps all SMs busy.  By default the ranks agree on a value among themselves
+    (one small all-reduce and a host synchronisation, see `_auto_local_splits`).
     """
     ops = CudaStageOps if ops is None else ops
     world = dist.get_world_size(group)
@@ -128,7 +139,8 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     if rank < world - 1 and L_local % chunk_size != 0:
         raise ValueError(
             f"segment of rank {rank} has {L_local} tokens, not a multiple of chunk_size {chunk_size}")
-    S = _auto_local_splits(B, L_local, chunk_size, world) if local_splits is None else int(local_splits)
+    S = (_auto_local_splits(B, L_local, chunk_size, world, u.device, group) if local_splits is None
+         else int(local_splits))
     if S < 1 or L_local % S != 0 or (S > 1 and (L_local // S) % chunk_size != 0):
         raise ValueError(f"local_splits={S} does not cut {L_local} tokens into whole chunks")
     if world == 1 and S == 1:

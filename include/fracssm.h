@@ -136,7 +136,8 @@ int fracssm_frac_scan_fwd(const void *u, int u_dtype, int64_t u_sb, int64_t u_sl
  * fracssm_frac_scan_fwd with path = 2, but the kernel's scratch is a fixed array inside the
  * library's device image (about 2.1 MB per GPU that loads the library, held until exit), so
  * there is no workspace argument.  Limits: dense tensors, R = 64, M = 128, bf16 u/c/kappa,
- * fp32 rho, and batch*heads B <= 64; larger B is rejected with FRACSSM_ERR_UNSUPPORTED.
+ * fp32 rho, 16-byte aligned pointers, and batch*heads B <= 64; larger B is rejected with
+ * FRACSSM_ERR_UNSUPPORTED.
  * Calls no cudaMalloc / cudaFree.  The first call on a device looks up the array's device
  * address (once, with that device current): make that first call outside any stream capture.
  * All calls on a device share the array: the ticket and progress counters are cleared on the
@@ -166,19 +167,18 @@ int fracssm_segment_summary(const void *u, const void *kappa, int k_dtype, const
 /*
  * Reads back the error word of the last single-pass launch that used `workspace` (this call
  * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
- * (for a predecessor tile's state, a TMA load or an MMA) ran out and the results are invalid.
+ * (for a predecessor tile's state, a TMA load or an MMA) ran out; the outputs of the affected rows
+ * are then NaN from that point on.
  * No counterpart in the reference (its kernels have no cross-CTA waits).
  */
 int fracssm_scan_fused_status(const void *workspace, void *stream);
 
 /*
- * Diagnostic: cycles spent per phase of the single-pass kernel's tile loop (16 phases, summed
- * over CTAs, as seen by thread 0 of each CTA) during the last launch that used `workspace`.
- * Synchronises the stream.  The counters are only written by the profiling build of the kernel,
- * which a launch uses when the environment variable FRACSSM_SCAN_PROFILE is set to a non-zero
- * value (it is about 7 % slower); otherwise all 16 numbers are zero.  No counterpart in the reference.
+ * The same read-back for fracssm_frac_scan_fwd_noalloc, whose scratch the caller never sees: error
+ * word of the last such launch on the current device (synchronises the stream).  No counterpart in
+ * the reference.
  */
-int fracssm_scan_fused_phase_cycles(const void *workspace, long long *out16, void *stream);
+int fracssm_frac_scan_noalloc_status(void *stream);
 
 /*
  * Elementwise scan-parameter prep after the two projections.
@@ -230,17 +230,6 @@ int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl
                           int64_t Bt, int64_t L, int64_t H, int64_t R, void *stream);
 
 /*
- * Diagnostic: one 128-row tcgen05 MMA tile, D[128,N] = A[128,128] * B[N,128]^T, with the
- * shared-memory operand layouts the scan kernel uses (K-major / MN-major, strided row groups,
- * TMA-loaded B).  A and B are float32 [128][128] tiles rounded to bf16 on staging; B_bf16
- * (bf16 [128][64], dense) is only read when b_via_tma != 0.  status: device int, 0 = ok.
- * No counterpart in the reference; used by the GPU tests.
- */
-int fracssm_selftest_umma(const float *A, const float *B, const void *B_bf16, float *D, int *status,
-                          int a_mn_major, int b_mn_major, int N, int b_row_group0, int b_sbo_bytes,
-                          int b_via_tma, void *stream);
-
-/*
  * The same epilogue for a layer whose heads are spread over several GPUs (the norm then spans columns
  * held by other GPUs).  Pass 1 writes, per (b, l) row, the sum of squares of the gated values of the H
  * local heads; the caller adds these [Bt*L] float32 vectors across GPUs (one all-reduce); pass 2
@@ -282,13 +271,6 @@ int fracssm_causal_conv_silu(const void *x, int x_dtype, int64_t x_sb, int64_t x
 int fracssm_decode_step(const void *u, int u_dtype, const float *c, const float *kappa, const float *rho,
                         const float *D, float *state, float *out, int64_t Bt, int64_t H, int64_t R,
                         int64_t M, void *stream);
-
-/*
- * Diagnostic: as fracssm_selftest_umma with K-major operands but a 64-row MMA; D [128][N] receives
- * all 128 tensor-memory lanes, which shows where the 64 result rows land.  No counterpart in the
- * reference.
- */
-int fracssm_selftest_umma_m64(const float *A, const float *B, float *D, int *status, int N, void *stream);
 
 #ifdef __cplusplus
 }

@@ -9,8 +9,8 @@ from frac_ssm_b200 import _cabi
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared():
-    text = open(os.path.join(ROOT, "include", "fracssm.h")).read()
+def _declared(header="fracssm.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(fracssm_[a-z0-9_]+)\s*\(", text)))
 
@@ -21,6 +21,15 @@ def test_library_exports_every_declared_symbol():
     handle = ctypes.CDLL(_cabi.lib_path())
     missing = [n for n in names if not hasattr(handle, n)]
     assert not missing, f"not exported: {missing}"
+
+
+def test_selftest_library_exports_its_header_and_stays_out_of_the_product():
+    names = _declared("fracssm_selftest.h")
+    assert len(names) == 4
+    product = ctypes.CDLL(_cabi.lib_path())
+    selftest = ctypes.CDLL(os.path.join(os.path.dirname(_cabi.lib_path()), "libfracssm_selftest.so"))
+    assert not [n for n in names if not hasattr(selftest, n)]
+    assert not [n for n in names if hasattr(product, n)], "test-only entry points leaked into libfracssm.so"
 
 
 def test_binding_covers_every_declared_symbol():

@@ -255,14 +255,14 @@ def test_no_device_wait_runs_out_in_back_to_back_launches(B, L, ckdt):
     k = (0.1 * torch.softmax(torch.randn(B, L, 128, device="cuda", generator=g), -1)).to(ckdt)
     rho = torch.rand(B, L, 128, device="cuda", generator=g).clamp(1e-6, 1 - 1e-6)
     filler = torch.randn(2048, 2048, device="cuda", dtype=torch.bfloat16)
-    spaces, first = [], None
+    bad = torch.zeros((), device="cuda", dtype=torch.int64)    # a launch whose wait ran out writes NaN
+    first = None
     for it in range(120):
-        h = FS.frac_scan(u, c, k, rho, 256, None, False, path="fused", keep_workspace=True)
-        spaces.append(FS._last_ws)
+        h = FS.frac_scan(u, c, k, rho, 256, None, False, path="fused")
+        bad += torch.isnan(h).any()
         first = h if first is None else first
         if it % 3 == 0:
             filler = (filler @ filler) * 1e-3
     torch.cuda.synchronize()
-    failed = sum(int(ws[:8].view(torch.int32)[1].item() != 0) for ws in spaces)
-    assert failed == 0, f"{failed} of {len(spaces)} launches had a device-side wait run out"
+    assert bad.item() == 0, f"{bad.item()} of 120 launches had a device-side wait run out"
     assert torch.equal(h, first)

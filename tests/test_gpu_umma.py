@@ -3,6 +3,8 @@
 import pytest
 import torch
 
+from tests.helpers import selftest_lib
+
 pytestmark = pytest.mark.gpu
 
 
@@ -15,14 +17,14 @@ def _run(a_mn, b_mn, N, group0=0, sbo=1024, tma=False, seed=0):
     B16 = B[:, :64].contiguous().bfloat16().cuda()
     D = torch.full((128, N), float("nan"), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    C.check(C.lib().fracssm_selftest_umma(C.ptr(Ad), C.ptr(Bd), C.ptr(B16), C.ptr(D), C.ptr(status),
+    C.check(selftest_lib().fracssm_selftest_umma(C.ptr(Ad), C.ptr(Bd), C.ptr(B16), C.ptr(D), C.ptr(status),
                                           int(a_mn), int(b_mn), N, group0, sbo, int(tma),
                                           C.stream_of(Ad)), "selftest_umma")
     torch.cuda.synchronize()
     assert status.item() == 0, "the MMA completion wait timed out"
     Am = A.t() if a_mn else A                     # [M, K]
     if b_mn:
-        Bm = B[:, :64].t()                        # rows are k, columns n -> [N, K]
+        Bm = B[:, :N].t()                         # rows are k, columns n -> [N, K]
     else:
         rows = torch.cat([torch.arange(8) + 8 * (group0 + i * (sbo // 1024)) for i in range(N // 8)])
         Bm = B[rows]                              # [N, K]
@@ -45,6 +47,10 @@ def test_mn_major_b():
     _run(False, True, 64)
 
 
+def test_mn_major_b_two_atoms():
+    _run(False, True, 128)                         # 128 columns = two 64-wide atoms side by side
+
+
 def test_mn_major_a_and_b():
     _run(True, True, 64)
 
@@ -64,7 +70,7 @@ def test_64_row_mma_lane_layout():
     for N in (64, 16):
         D = torch.full((128, N), -777.0, device="cuda")
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        C.check(C.lib().fracssm_selftest_umma_m64(C.ptr(Ad), C.ptr(Bd), C.ptr(D), C.ptr(status), N,
+        C.check(selftest_lib().fracssm_selftest_umma_m64(C.ptr(Ad), C.ptr(Bd), C.ptr(D), C.ptr(status), N,
                                                   C.stream_of(Ad)), "selftest_umma_m64")
         torch.cuda.synchronize()
         assert status.item() == 0, "the MMA completion wait timed out"

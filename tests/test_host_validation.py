@@ -71,3 +71,24 @@ def test_shard_heads_covers_every_head_once():
             sl = parallel.shard_heads(heads, r, world)
             seen.extend(range(sl.start, sl.stop))
         assert seen == list(range(heads))
+
+
+def test_misaligned_pointers_are_refused_before_any_launch():
+    """The single-pass kernels use 8- and 16-byte accesses: a pointer off a 16-byte boundary is an
+    argument error, not a device fault.  Checked on the host with made-up addresses (nothing runs)."""
+    import ctypes
+    from frac_ssm_b200 import _cabi as C
+    lib = C.lib()
+    ok, bad = ctypes.c_void_p(0x10000), ctypes.c_void_p(0x10008)
+    for which in range(5):
+        ptrs = [bad if i == which else ok for i in range(5)]      # u, c, kappa, rho, h
+        rc = lib.fracssm_frac_scan_fwd_noalloc(ptrs[0], ptrs[1], ptrs[2], ptrs[3], None, ptrs[4], None, C.F32,
+                                               2, 256, 64, 128, None)
+        assert rc == 1 and b"16-byte aligned" in lib.fracssm_last_error()
+    ws = ctypes.c_void_p(0x20000)
+    need = lib.fracssm_segment_summary_workspace_bytes(2, 64, 128)
+    for which in range(3):
+        ptrs = [bad if i == which else ok for i in range(3)]      # u, kappa, rho
+        rc = lib.fracssm_segment_summary(ptrs[0], ptrs[1], C.BF16, ptrs[2], None, ok, ok, ws, need,
+                                         2, 256, 64, 128, None)
+        assert rc == 1 and b"16-byte aligned" in lib.fracssm_last_error()

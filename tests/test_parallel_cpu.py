@@ -71,6 +71,18 @@ def _worker(rank, world, port, mode, out):
                                                 local_splits=4 if mode == "seq_split" else 1)
             ok = torch.allclose(h, h_ref[:, tok], rtol=1e-4, atol=1e-4) and \
                 torch.allclose(fin, f_ref, rtol=1e-4, atol=1e-4)
+        elif mode.startswith("ragged"):
+            # unequal segments (17 chunks over 2 ranks; or a ragged tail): each rank's own candidate for
+            # the sub-segment count differs, the ranks must agree on one before they exchange
+            L = int(mode[6:])
+            B, T = 2, 256
+            u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, dtype=torch.float32, gen="model_like", seed=9)
+            h_ref, f_ref = O.frac_scan(u, c, kappa, rho, T, init, True, exact=True)
+            tok = parallel.shard_tokens(L, T, rank, world)
+            h, fin = parallel.seq_parallel_scan(u[:, tok], c[:, tok], kappa[:, tok], rho[:, tok], T, init,
+                                                True, ops=OracleStageOps)          # default local_splits
+            ok = torch.allclose(h, h_ref[:, tok], rtol=1e-4, atol=1e-4) and \
+                torch.allclose(fin, f_ref, rtol=1e-4, atol=1e-4)
         elif mode == "heads":       # a layer's heads spread over the ranks; the norm spans all heads
             batch, H, Rh, Lh = 2, 6, 8, 40
             g = torch.Generator().manual_seed(11)
@@ -124,6 +136,11 @@ def test_sequence_sharding_matches_single_scan(world):
 
 def test_sequence_sharding_with_local_sub_segments():
     _run(2, "seq_split")
+
+
+@pytest.mark.parametrize("L", [3996, 4352])
+def test_sequence_sharding_with_unequal_segments_and_default_splits(L):
+    _run(2, f"ragged{L}")
 
 
 def test_row_sharding_matches_single_scan():

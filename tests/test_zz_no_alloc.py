@@ -3,7 +3,8 @@
 `fracssm_frac_scan_fwd_noalloc` serves callers that cannot hand the library scratch memory and
 must not trigger an allocation (allocator callbacks, no-cudaMalloc serving loops, bindings with
 no device allocator).  Its scratch is a fixed array inside the library, shared by every call, so
-the test runs it twice in a row and checks both results against the workspace-based entry point.
+the test runs it twice in a row and checks both results against the workspace-based entry point
+and against the CPU oracle.
 """
 
 import pytest
@@ -28,6 +29,7 @@ def _noalloc(u, c, kappa, rho, init):
 
 
 def test_noalloc_matches_workspace_entry_twice_in_a_row():
+    from frac_ssm_b200 import _cabi as C
     from frac_ssm_b200.ops.b200 import frac_scan
     cases = [O.scan_inputs(7, 700, 64, 128, gen="model_like", seed=31),
              O.scan_inputs(64, 300, 64, 128, gen="random", seed=32)]
@@ -36,11 +38,16 @@ def test_noalloc_matches_workspace_entry_twice_in_a_row():
         init = init if use_init else None
         h_ref, f_ref = frac_scan(u, c, kappa, rho, 256, init, True, final_state_dtype=torch.float32,
                                  path="fused", check=True)
+        uc, cc, kc, rc, _ = case
+        h_orc, f_orc = O.frac_scan_slabs(uc.float(), cc.float(), kc.float(), rc, 256,
+                                         case[4] if use_init else None, True, exact=True, slab=8)
         for _ in range(2):
             h, fin = _noalloc(u, c, kappa, rho, init)
-            torch.cuda.synchronize()
+            assert C.lib().fracssm_frac_scan_noalloc_status(C.stream_of(u)) == 0     # synchronises
             torch.testing.assert_close(h.float(), h_ref.float(), **TOL_BF16)
             torch.testing.assert_close(fin, f_ref, **TOL_F32)
+            torch.testing.assert_close(h.float().cpu(), h_orc.float(), **TOL_BF16)
+            torch.testing.assert_close(fin.cpu(), f_orc.float(), **TOL_F32)
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
