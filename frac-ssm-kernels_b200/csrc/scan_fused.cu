@@ -9,12 +9,19 @@
 // by a running CTA (one item ahead of the one it is working on) and dependencies point to
 // lower tickets, so the lowest unfinished item is always being worked on and never waits.
 //
-// One CTA per SM, 20 warps (three of them only pad the control warp's register group).  Warps
-// 0-15 ("workers") turn the raw inputs into bf16 operand tiles in shared memory and run the
-// epilogues; warp 16 ("control") takes tickets, issues the TMA load of u and every tcgen05.mma,
-// and polls the state counter.  Workers hand a batch of tiles over by arriving on a "full"
-// mbarrier (one arrival per warp, after a proxy fence); the control warp hands buffers and
-// accumulators back through tcgen05.commit mbarriers.
+// One CTA per SM, 20 warps.  Warps 0-15 ("workers") turn the raw inputs into bf16 operand tiles in
+// shared memory and run the epilogues; warp 16 ("MMA warp") issues the TMA load of u and every
+// tcgen05.mma; warp 17 ("chain warp") takes the tickets, pulls the next item into L2 and hands the
+// state from tile to tile of a row (polls and releases the per-row counter); warps 18-19 only pad
+// the register group of those two.  Workers hand a batch of tiles over by arriving on a "full"
+// mbarrier (one arrival per warp, after a proxy fence); the MMA warp hands buffers and accumulators
+// back through tcgen05.commit mbarriers.
+//
+// A tile is processed in two passes over the modes (64 + 64): a worker thread owns 8 token rows x 2
+// modes per pass, so its per-token factors (32 registers) and the raw inputs of the other pass
+// (32 registers, requested one pass ahead) fit in registers without spilling; each operand tile's two
+// 64-column halves are filled by the two passes and the level / base products are issued per pass
+// (4 of their 8 contraction steps), accumulating in tensor memory.
 //
 // Math per tile (tokens t, k in 0..127; modes m; rho floored at 1e-6, 1 beyond L):
 //   h[t]   = sum_m Chat[t,m] S[m,:]  +  sum_{k<=t} W[t,k] u[k,:]
@@ -39,8 +46,7 @@
 //   slot 2 / 3: levels 8+16, A / B rows   -> Chat high / low   (after the level-8/16 product)
 //   slot 4 / 5: levels 64+32, A / B rows  -> W / incoming state high|low (after that product)
 // Tensor memory (fp32 columns): base 0..127, tile's own state contribution 128..191, levels 8+16
-// 192..319, levels 64+32 320..447; the output accumulator H re-uses 320..447 (columns 384..447
-// take the product with the state's low part and are added when the rows are written).
+// 192..319, levels 64+32 320..447, output accumulator H 448..511.
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -56,8 +62,8 @@ namespace {
 using namespace tile;
 constexpr int kWorkers = 512, kThreads = 640;
 // Registers are re-divided after launch (setmaxnreg): the 16 worker warps grow to kWorkerRegs,
-// the control warp's group of four shrinks to kControlRegs.  Each SM sub-partition holds four
-// worker warps and one warp of the control group: 4 * 112 + 32 = 5 * 96, the launch allocation
+// the group of the MMA and chain warps shrinks to kControlRegs.  Each SM sub-partition holds four
+// worker warps and one warp of that group: 4 * 112 + 32 = 5 * 96, the launch allocation
 // (checked on the host: it must cover both, or the growing warps would wait forever).
 constexpr int kWorkerRegs = 112, kControlRegs = 32;
 constexpr int kLaunchRegsNeeded = (kWorkers * kWorkerRegs + (kThreads - kWorkers) * kControlRegs + kThreads - 1) / kThreads;
@@ -72,12 +78,13 @@ constexpr uint32_t kOffSeg = kOffU + 16384;     // float [16][128]: decay produc
 constexpr uint32_t kOffMisc = kOffSeg + 8192;   // mbarriers, TMEM base, tickets, failure flag
 constexpr uint32_t kSmemBytes = kOffMisc + 256 + 1024;
 // tensor-memory columns (fp32, 128 lanes each)
-constexpr uint32_t kColBase = 0, kColS = 128, kColL1 = 192, kColL2 = 320, kColH = 320;
+constexpr uint32_t kColBase = 0, kColS = 128, kColL1 = 192, kColL2 = 320, kColH = 448;
 constexpr size_t kCtrlBytes = 256;
 
 struct FusedArgs {
   const void *c, *kappa;  // bf16 or f32 [BH, L, 128], see the kernel's CKF32 parameter
   const float *rho, *init;
+  const __nv_bfloat16 *u;   // [BH, L, 64] (read by TMA; the pointer is only used for the L2 prefetch)
   __nv_bfloat16 *h;
   void *fin;
   int fin_dt;
@@ -89,40 +96,65 @@ struct FusedArgs {
   unsigned long long wait_ns;  // limit of every device-side wait
 };
 
-// Raw inputs of one item for one worker thread, one group of 4 tokens x 4 modes.
-// c and kappa arrive as bf16 (4 values in a uint2) or as f32 (a float4).
+// Diagnostic build (-DFRACSSM_PHASE_PROF, never the product library): clock stamps of a few warps of
+// CTA 0 at the phase boundaries of four consecutive tiles, read back with fracssm_prof_stamps.
+#ifdef FRACSSM_PHASE_PROF
+constexpr int kProfTile0 = 8, kProfTiles = 4, kProfWarps = 4, kProfMarks = 40;
+__device__ long long g_prof[kProfTiles][kProfWarps][kProfMarks];
+#define FRACSSM_MARK(slot, id)                                                                   \
+  if (blockIdx.x == 0 && lane == 0 && n >= kProfTile0 && n < kProfTile0 + kProfTiles && (slot) >= 0) \
+    g_prof[n - kProfTile0][slot][id] = clock64();
+#else
+#define FRACSSM_MARK(slot, id)
+#endif
+
+// Raw inputs of one item for one worker thread and one half of the modes: its 8 token rows x 2 modes.
+// rho arrives as two floats; c and kappa as two bf16 (one word) or two floats.
 template <bool CKF32>
-struct RawRegs {
-  using CK = typename std::conditional<CKF32, float4, uint2>::type;
-  float4 r[4];
-  CK c[4], k[4];
+struct RawHalf {
+  using CK = typename std::conditional<CKF32, f2, uint32_t>::type;
+  f2 r[8];
+  CK c[8], k[8];
 };
 
+// The loads do not allocate in L1 (with 222 KB of shared memory per CTA the L1 keeps about 28 KB, a
+// tile reads 164 KB) and are volatile so that they stay where they are written.
+__device__ __forceinline__ void ldg_stream(f2 &d, const void *p) {
+  asm volatile("ld.global.L1::no_allocate.b64 %0, [%1];" : "=l"(d) : "l"(p));
+}
+__device__ __forceinline__ void ldg_stream(uint32_t &d, const void *p) {
+  asm volatile("ld.global.L1::no_allocate.b32 %0, [%1];" : "=r"(d) : "l"(p));
+}
+__device__ __forceinline__ f2 ck_wide(uint32_t v) { return widen_bf2(v); }
+__device__ __forceinline__ f2 ck_wide(f2 v) { return v; }
+
+// Requests token row i (0..7) of this thread's segment of `item`, modes 64 h + 2 lane, + 1.
 template <bool CKF32>
-__device__ __forceinline__ void load_raw(RawRegs<CKF32> &raw, const FusedArgs &a, int item, int w, int lane,
-                                         int grp) {
-  using CK = typename RawRegs<CKF32>::CK;
-  const int j = item / a.BH, bh = item - j * a.BH;
-  const int t0 = (j + a.first_tile) * kTile + 8 * w + 4 * grp;
-  const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
-  const CK *cp = reinterpret_cast<const CK *>(a.c), *kp = reinterpret_cast<const CK *>(a.kappa);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    raw.r[i] = make_float4(1.f, 1.f, 1.f, 1.f);
-    raw.c[i] = CK{};
-    raw.k[i] = CK{};
-    if (t0 + i < a.L) {
-      raw.r[i] = __ldcs(reinterpret_cast<const float4 *>(a.rho + (tok0 + i) * kM) + lane);
-      raw.c[i] = __ldcs(cp + (tok0 + i) * 32 + lane);   // 32 pieces of 4 modes per token row
-      raw.k[i] = __ldcs(kp + (tok0 + i) * 32 + lane);
-    }
+__device__ __forceinline__ void load_tok(RawHalf<CKF32> &raw, const FusedArgs &a, int bh, int t0, int w, int lane,
+                                         int h, int i) {
+  using CK = typename RawHalf<CKF32>::CK;
+  const int t = t0 + 8 * w + i;
+  raw.r[i] = mk2(1.f, 1.f);
+  raw.c[i] = CK{};
+  raw.k[i] = CK{};
+  if (t < a.L) {
+    const int64_t e = (static_cast<int64_t>(bh) * a.L + t) * kM + 64 * h + 2 * lane;   // element index
+    ldg_stream(raw.r[i], a.rho + e);
+    ldg_stream(raw.c[i], reinterpret_cast<const char *>(a.c) + e * (CKF32 ? 4 : 2));
+    ldg_stream(raw.k[i], reinterpret_cast<const char *>(a.kappa) + e * (CKF32 ? 4 : 2));
   }
 }
 
-// The two floored decay pairs of one token.
-__device__ __forceinline__ void rho_pairs(const float4 &v, f2 (&out)[2]) {
-  out[0] = mk2(fmaxf(v.x, kRhoFloor), fmaxf(v.y, kRhoFloor));
-  out[1] = mk2(fmaxf(v.z, kRhoFloor), fmaxf(v.w, kRhoFloor));
+__device__ __forceinline__ f2 floor2(f2 v) {
+  float lo, hi;
+  un2(v, lo, hi);
+  return mk2(fmaxf(lo, kRhoFloor), fmaxf(hi, kRhoFloor));
+}
+// One 4-byte store of an operand row: rows_s = tile + 16384 * half + 1024 * row group + the thread's
+// fixed offset (bits 4..6 hold its 16-byte chunk index), i = row inside the group.
+__device__ __forceinline__ void emit_pair(uint32_t rows_s, int i, uint32_t w0) {
+  const uint32_t addr = (rows_s ^ (static_cast<uint32_t>(i) << 4)) + i * 128;
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(w0) : "memory");
 }
 
 template <bool CKF32>
@@ -130,13 +162,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // mbarriers, each completed exactly once per tile:
-  //   cb0 / cb1 / cb2 / cbK / barH by tcgen05.commit, barU by the TMA load,
-  //   fA / fL1 / fL2 / fK / fW / fS / out_bar by the 16 worker warps, item_bar / state_bar by the control warp
+  // mbarriers.  Completed once per tile: cb2 / cbK / barH (tcgen05.commit), barU (TMA), fS / fW / out_bar
+  // (16 worker warps), item_bar / state_bar (chain warp), read_bar (workers + MMA warp).  Completed once per HALF of the modes,
+  // i.e. twice per tile, so the phase parity of half h is simply h: cb0 / cbL (tcgen05.commit) and
+  // fA / fL / fK (16 worker warps).
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffMisc);
-  uint64_t *cb0 = bars + 0, *cb1 = bars + 1, *cb2 = bars + 2, *cbK = bars + 3, *barH = bars + 4, *barU = bars + 5;
-  uint64_t *fA = bars + 6, *fL1 = bars + 7, *fL2 = bars + 8, *fK = bars + 9, *fW = bars + 10, *fS = bars + 11;
-  uint64_t *item_bar = bars + 12, *state_bar = bars + 13, *out_bar = bars + 14;
+  uint64_t *cb0 = bars + 0, *cbL = bars + 1, *cb2 = bars + 2, *cbK = bars + 3, *barH = bars + 4, *barU = bars + 5;
+  uint64_t *fA = bars + 6, *fL = bars + 7, *fK = bars + 8, *fW = bars + 9, *fS = bars + 10;
+  uint64_t *item_bar = bars + 11, *state_bar = bars + 12, *out_bar = bars + 13, *read_bar = bars + 14;
   uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 15);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_s + 3);  // a wait of this CTA ran out
@@ -145,10 +178,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 
   if (tid == 0) {
     for (int i = 0; i < 6; ++i) umma::mbar_init(bars + i, 1);
-    for (int i = 6; i < 12; ++i) umma::mbar_init(bars + i, 16);
+    for (int i = 6; i < 11; ++i) umma::mbar_init(bars + i, 16);
     umma::mbar_init(item_bar, 1);
     umma::mbar_init(state_bar, 1);
     umma::mbar_init(out_bar, 16);
+    umma::mbar_init(read_bar, 17);   // the 16 worker warps and the MMA warp, once each has read the tile's item
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
     *failed = 0;
@@ -160,45 +194,24 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   const uint32_t tmem = *tmem_s;
   const uint64_t wait_ns = a.wait_ns;
   bool ok = true;  // cleared when a bounded wait runs out; later waits are then skipped
-  // Bounded waits.  The control warp polls (it is one warp and every hand-over of the tile passes
-  // through it: a parked wait wakes up several hundred cycles after the barrier completes); the 16
-  // worker warps park, which leaves the issue slots to the warps that have work.  A wait that runs
+  // Bounded waits.  The MMA and chain warps poll (every hand-over of the tile passes through them:
+  // a parked wait wakes up several hundred cycles after the barrier completes); the 16 worker
+  // warps park, which leaves the issue slots to the warps that have work.  A wait that runs
   // out marks the CTA as failed: its remaining outputs are written as NaN and the error word is set.
   // (each setmaxnreg sits inside its role's branch: the register limit must not merge across roles)
-  if (w > 16) {
-    // spare warps of the control warp's register group: give the registers back, nothing else
+  if (w > 17) {
+    // spare warps of the two service warps' register group: give the registers back, nothing else
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-  } else if (w == 16) {
+  } else if (w == 17) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
 #define FRACSSM_WAIT(bar, parity)                                  \
   if (ok) {                                                        \
     ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
     if (!ok) *failed = 1;                                          \
   }
-    // =========================== control warp ===========================
-    const uint32_t sb = umma::smem_u32(smem);
-    const uint32_t sA0 = sb + kOffA0, sB0 = sb + kOffB0, sY1 = sb + kOffY1, sZ1 = sb + kOffZ1, sY2 = sb + kOffY2,
-                   sZ2 = sb + kOffZ2, sU = sb + kOffU;
-    const uint32_t sKhi = sb + kOffKhi, sKlo = sb + kOffKlo, sChi = sb + kOffChi, sClo = sb + kOffClo,
-                   sW = sb + kOffW, sS = sb + kOffS;
-    constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
-    constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
-    constexpr uint32_t kIdKMn128 = umma::make_idesc(128, 128, false, true);
-    constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
-    // One GEMM piece = 8 contraction steps of 16.  A K-major 128-column tile advances by 32 bytes
-    // inside a 64-column atom and by one atom after 4 steps; an MN-major tile by 16 rows (2048 B).
-    auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t idesc,
-                     uint32_t acc_first) {
-      const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
-      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, 1024);
-#pragma unroll
-      for (uint32_t s = 0; s < 8; ++s) {
-        const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
-        umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
-                     s > 0 ? 1u : acc_first);
-      }
-    };
-
+    // =========================== chain warp ===========================
+    // Tickets, the L2 prefetch of the next item, and the hand-over of the state between the tiles of
+    // a (batch, head) row: nothing here waits for an MMA, so a row's chain is never held up by them.
     int item = 0;
     if (lane == 0) {
       item = atomicAdd(&a.ctrl[0], 1);
@@ -210,111 +223,152 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     for (uint32_t n = 0; item < a.total; ++n) {
       const int j = item / a.BH, bh = item - j * a.BH;
       const int jt = j + a.first_tile;  // tile index inside the row
-      // The next ticket is taken a tile ahead (the workers read it in the second half of this tile,
-      // and its inputs are pulled into L2 now) and published through item_bar.  In the first tile of
-      // a CTA this has to wait until the workers have read the first item, i.e. until their arrival
-      // on fA: two completions of item_bar in a row would flip its parity twice, and a worker
-      // that had not looked yet would wait for a phase that never comes.  From the second tile on
-      // every worker has read item n before the control warp can get here (the read precedes the
-      // worker's arrival on fW of the previous tile).
+      // The next ticket is published through item_bar only after every reader holds the current one
+      // (read_bar): two completions of item_bar in a row would flip its parity twice, and a reader
+      // that had not looked yet would wait for a phase that never comes.
+      FRACSSM_WAIT(read_bar, n);
       int next = 0;
-      auto take_next = [&]() {
-        if (lane == 0) {
-          next = atomicAdd(&a.ctrl[0], 1);
-          items[(n + 1) & 1] = next;
-          umma::mbar_arrive(item_bar);
-        }
-        next = __shfl_sync(0xffffffffu, next, 0);
-        if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
-          const int nj = next / a.BH, nb = next - nj * a.BH;
-          const int tk0 = (nj + a.first_tile) * kTile;
-          const int ntok = min(kTile, a.L - tk0);
-          const int64_t tok = static_cast<int64_t>(nb) * a.L + tk0;
-          umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
-          constexpr int kCkBytes = CKF32 ? 4 : 2;
-          umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
-          umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
-        }
-      };
-      if (n > 0) take_next();
-      // base: D[t,k] = A0[t,:] . B0[k,:]
-      FRACSSM_WAIT(fA, n);
-      umma::tc_fence_after();
       if (lane == 0) {
-        piece(kColBase, sA0, false, sB0, false, kIdKK128, 0u);
-        umma::mma_commit(cb0);
+        next = atomicAdd(&a.ctrl[0], 1);
+        items[(n + 1) & 1] = next;
+        umma::mbar_arrive(item_bar);
       }
-      if (n == 0) take_next();
-      // the u tile is free once every MMA of the previous tile has finished
-      if (n > 0) { FRACSSM_WAIT(barH, n - 1); }
-      if (lane == 0) {
-        umma::mbar_expect_tx(barU, kTile * kR * 2);
-        umma::tma_load_3d(smem + kOffU, &u_map, barU, 0, jt * kTile, bh);
+      next = __shfl_sync(0xffffffffu, next, 0);
+      if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
+        const int nj = next / a.BH, nb = next - nj * a.BH;
+        const int tk0 = (nj + a.first_tile) * kTile;
+        const int ntok = min(kTile, a.L - tk0);
+        const int64_t tok = static_cast<int64_t>(nb) * a.L + tk0;
+        umma::prefetch_l2(a.rho + tok * kM, ntok * kM * 4);
+        constexpr int kCkBytes = CKF32 ? 4 : 2;
+        umma::prefetch_l2(reinterpret_cast<const char *>(a.c) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
+        umma::prefetch_l2(reinterpret_cast<const char *>(a.kappa) + tok * kM * kCkBytes, ntok * kM * kCkBytes);
+        umma::prefetch_l2(a.u + tok * kR, ntok * kR * 2);
       }
-      // levels 8 + 16, then 64 + 32: A rows x B rows of the stacked tiles
-      FRACSSM_WAIT(fL1, n);
-      umma::tc_fence_after();
+      // the state left by the previous tile of this row
       if (lane == 0) {
-        piece(kColL1, sY1, false, sZ1, false, kIdKK128, 0u);
-        umma::mma_commit(cb1);
-      }
-      FRACSSM_WAIT(fL2, n);
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColL2, sY2, false, sZ2, false, kIdKK128, 0u);
-        umma::mma_commit(cb2);
-      }
-      // the state left by the previous tile of this (batch, head) row is usually there already:
-      // look before the wait for the workers, when this warp has nothing else to do
-      bool early = false;
-      if (lane == 0) {
-        early = jt == 0 || ld_acquire(a.flags + bh) >= jt;
-        if (early) umma::mbar_arrive(state_bar);
-      }
-      // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
-      FRACSSM_WAIT(fK, n);
-      FRACSSM_WAIT(barU, n);
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColS, sKhi, true, sU, true, kIdMnMn64, 0u);
-        piece(kColS, sKlo, true, sU, true, kIdMnMn64, 1u);
-        umma::mma_commit(cbK);
-        if (!early) {
-          if (ok) {
-            const uint64_t t_start = umma::global_ns();
-            while (ld_acquire(a.flags + bh) < jt) {
-              __nanosleep(100);
-              if (umma::global_ns() - t_start > wait_ns) { ok = false; *failed = 1; break; }
-            }
+        if (jt > 0 && ok) {
+          const uint64_t t_start = umma::global_ns();
+          while (ld_acquire(a.flags + bh) < jt) {
+            __nanosleep(100);
+            if (umma::global_ns() - t_start > wait_ns) { ok = false; *failed = 1; break; }
           }
-          umma::mbar_arrive(state_bar);
         }
+        umma::mbar_arrive(state_bar);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      FRACSSM_WAIT(fW, n);
-      FRACSSM_WAIT(fS, n);
-      // Publish the outgoing state as soon as the workers have stored it: their stores are ordered
-      // before their arrivals on out_bar, this release makes them visible to the next tile's CTA.
-      // If they are not done yet, the output MMAs go first.
-      bool released = false;
-      if (umma::mbar_test(out_bar, n & 1u)) {
-        if (lane == 0 && jt + 1 < a.ntiles) st_release(a.flags + bh, jt + 1);
-        released = true;
-      }
-      // H = Chat S (both split into bf16 high and low parts, low x low dropped) + W u
-      umma::tc_fence_after();
-      if (lane == 0) {
-        piece(kColH, sChi, false, sS, true, kIdKMn128, 0u);   // Chat(high) [S(high) | S(low)], 128 columns
-        piece(kColH, sClo, false, sS, true, kIdKMn64, 1u);    // Chat(low) S(high)
-        piece(kColH, sW, false, sU, true, kIdKMn64, 1u);      // W u
-        umma::mma_commit(barH);
-      }
-      if (!released) {
-        FRACSSM_WAIT(out_bar, n);
-        if (lane == 0 && jt + 1 < a.ntiles) st_release(a.flags + bh, jt + 1);
-      }
+      // publish the outgoing state once the workers have stored it: their stores are ordered before
+      // their arrivals on out_bar, this release makes them visible to the next tile's CTA
+      FRACSSM_WAIT(out_bar, n);
+      if (lane == 0 && jt + 1 < a.ntiles) st_release(a.flags + bh, jt + 1);
       __syncwarp();
       item = next;
+    }
+#undef FRACSSM_WAIT
+  } else if (w == 16) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+#define FRACSSM_WAIT(bar, parity)                                  \
+  if (ok) {                                                        \
+    ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
+    if (!ok) *failed = 1;                                          \
+  }
+    // =========================== MMA warp ===========================
+    const uint32_t sb = umma::smem_u32(smem);
+    const uint32_t sA0 = sb + kOffA0, sB0 = sb + kOffB0, sY1 = sb + kOffY1, sZ1 = sb + kOffZ1, sY2 = sb + kOffY2,
+                   sZ2 = sb + kOffZ2, sU = sb + kOffU;
+    const uint32_t sKhi = sb + kOffKhi, sKlo = sb + kOffKlo, sChi = sb + kOffChi, sClo = sb + kOffClo,
+                   sW = sb + kOffW, sS = sb + kOffS;
+    constexpr uint32_t kIdKK128 = umma::make_idesc(128, 128, false, false);
+    constexpr uint32_t kIdKMn64 = umma::make_idesc(128, 64, false, true);
+    constexpr uint32_t kIdMnMn64 = umma::make_idesc(128, 64, true, true);
+    // Contraction steps s0 .. s1-1 (16 modes or tokens each) of one GEMM piece.  A K-major 128-column
+    // tile advances by 32 bytes inside a 64-column atom and by one atom after 4 steps (steps 0..3 are
+    // the first half of the modes, 4..7 the second); an MN-major tile by 16 rows (2048 B).
+    auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t idesc,
+                     uint32_t acc_first, uint32_t s0, uint32_t s1) {
+      const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
+      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, 1024);
+#pragma unroll
+      for (uint32_t s = s0; s < s1; ++s) {   // s0, s1 are constants at every call: fully unrolled
+        const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
+        umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
+                     s > s0 ? 1u : acc_first);
+      }
+    };
+
+#pragma unroll 1
+    for (uint32_t n = 0;; ++n) {
+      FRACSSM_WAIT(item_bar, n);
+      const int item = items[n & 1];
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(read_bar);
+      if (item >= a.total) break;
+      const int j = item / a.BH, bh = item - j * a.BH;
+      const int jt = j + a.first_tile;  // tile index inside the row
+      FRACSSM_MARK(3, 0)
+#pragma unroll
+      for (uint32_t h = 0; h < 2; ++h) {
+        // base: D[t,k] += A0[t, modes of half h] . B0[k, the same modes]
+        FRACSSM_WAIT(fA, h);
+        FRACSSM_MARK(3, 1 + 4 * h)
+        umma::tc_fence_after();
+        if (lane == 0) {
+          piece(kColBase, sA0, false, sB0, false, kIdKK128, h, 4 * h, 4 * h + 4);
+          umma::mma_commit(cb0);
+        }
+        if (h == 0) {
+          // the u tile is free once every MMA of the previous tile has finished
+          if (n > 0) { FRACSSM_WAIT(barH, n - 1); }
+          FRACSSM_MARK(3, 2)
+          if (lane == 0) {
+            umma::mbar_expect_tx(barU, kTile * kR * 2);
+            umma::tma_load_3d(smem + kOffU, &u_map, barU, 0, jt * kTile, bh);
+          }
+        }
+        // levels 8 + 16, then 64 + 32: A rows x B rows of the stacked tiles, this half of the modes
+        FRACSSM_WAIT(fL, h);
+        FRACSSM_MARK(3, 3 + 4 * h)
+        umma::tc_fence_after();
+        if (lane == 0) {
+          piece(kColL1, sY1, false, sZ1, false, kIdKK128, h, 4 * h, 4 * h + 4);
+          umma::mma_commit(cbL);
+          piece(kColL2, sY2, false, sZ2, false, kIdKK128, h, 4 * h, 4 * h + 4);
+          if (h == 1) umma::mma_commit(cb2);
+        }
+        FRACSSM_MARK(3, 4 + 4 * h)
+      }
+      // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
+      // (fK completes once per half.  Its first completion of this tile is known to have happened:
+      // the workers arrive on it before they arrive on fA for the second half, which was waited for
+      // above.  Waiting for it here again could miss it: once BOTH completions are in, the barrier's
+      // parity is back where it started.)
+      FRACSSM_WAIT(fK, 1);
+      FRACSSM_WAIT(barU, n);
+      FRACSSM_MARK(3, 9)
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColS, sKhi, true, sU, true, kIdMnMn64, 0u, 0, 8);
+        piece(kColS, sKlo, true, sU, true, kIdMnMn64, 1u, 0, 8);
+        umma::mma_commit(cbK);
+      }
+      FRACSSM_MARK(3, 10)
+      // H = Chat S (both split into bf16 high and low parts, low x low dropped) ...
+      FRACSSM_WAIT(fS, n);
+      FRACSSM_MARK(3, 11)
+      umma::tc_fence_after();
+      if (lane == 0) piece(kColH, sChi, false, sS, true, kIdKMn64, 0u, 0, 8);           // Chat(high) S(high)
+      if (lane == 0) piece(kColH, sClo, false, sS, true, kIdKMn64, 1u, 0, 8);           // Chat(low)  S(high)
+      if (lane == 0) piece(kColH, sChi, false, sS + kAtom, true, kIdKMn64, 1u, 0, 8);   // Chat(high) S(low)
+      // ... + W u
+      FRACSSM_WAIT(fW, n);
+      FRACSSM_MARK(3, 12)
+      umma::tc_fence_after();
+      if (lane == 0) {
+        piece(kColH, sW, false, sU, true, kIdKMn64, 1u, 0, 8);
+        umma::mma_commit(barH);
+      }
+      FRACSSM_MARK(3, 13)
+      __syncwarp();
     }
   } else {
     // =========================== worker warps ===========================
@@ -327,321 +381,258 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
     const int Q = w & 3, P = w >> 2;  // TMEM lane quarter of this warp, and its share of the columns
     const uint32_t sb = umma::smem_u32(smem);
-    // operand-tile addressing of this thread: modes 4*lane..4*lane+3 of a row; the row group and the
-    // row inside it are added per store (emit_words)
-    const uint32_t th_fix = (lane >> 4) * kAtom + ((lane & 1) << 3) + (((lane & 15) >> 1) << 4);
+    // operand-tile addressing of this thread inside one half (64 modes = one 64-column atom) of a row:
+    // modes 2*lane, 2*lane+1 -> 16-byte chunk lane / 4, bytes 4 * (lane % 4); the half, the row group
+    // and the row inside it are added per store (emit_pair)
+    const uint32_t th_fix = ((lane >> 2) << 4) + ((lane & 3) << 2);
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(32 * Q) << 16);
-    const uint32_t seg_s = sb + kOffSeg + 16 * lane;  // this lane's four modes of segment 0
+    const uint32_t seg_s = sb + kOffSeg + 8 * lane;  // this lane's two modes of segment 0, half 0
     const float kNaN = __int_as_float(0x7fc00000);
+#ifdef FRACSSM_PHASE_PROF
+    const int pslot = w == 0 ? 0 : w == 5 ? 1 : w == 15 ? 2 : -1;
+#endif
 
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
+    __syncwarp();
+    if (lane == 0) umma::mbar_arrive(read_bar);
     int prev_bh = 0, prev_t0 = 0;
     // Output rows of the previous tile (its H accumulator is complete when barH fires).  It runs in
-    // the middle of the next tile, so that tile's first phase overlaps the output MMAs.
+    // the middle of the next tile's first phase, which so overlaps the output MMAs.
     auto write_rows = [&](uint32_t n_done) {
       FRACSSM_WAIT(barH, n_done);
       umma::tc_fence_after();
       const bool bad = *failed != 0;
       const int t = prev_t0 + 32 * Q + lane;
       uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
+      float acc[16];
+      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
+      umma::tmem_ld_wait();
+      if (t < a.L) {
+        uint4 o0, o1;
+        if (bad) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float hi[8], lo[8];
-        umma::tmem_ld8(lane_addr + kColH + 16 * P + 8 * half, hi);
-        umma::tmem_ld8(lane_addr + kColH + 64 + 16 * P + 8 * half, lo);
-        umma::tmem_ld_wait();
-#pragma unroll
-        for (int x = 0; x < 8; ++x) hi[x] = bad ? kNaN : hi[x] + lo[x];
-        if (t < a.L) {
-          uint4 o;
-          o.x = pack2(hi[0], hi[1]); o.y = pack2(hi[2], hi[3]); o.z = pack2(hi[4], hi[5]); o.w = pack2(hi[6], hi[7]);
-          __stcs(dst + half, o);
+          for (int x = 0; x < 16; ++x) acc[x] = kNaN;
         }
+        o0.x = pack2(acc[0], acc[1]); o0.y = pack2(acc[2], acc[3]); o0.z = pack2(acc[4], acc[5]); o0.w = pack2(acc[6], acc[7]);
+        o1.x = pack2(acc[8], acc[9]); o1.y = pack2(acc[10], acc[11]); o1.z = pack2(acc[12], acc[13]); o1.w = pack2(acc[14], acc[15]);
+        __stcs(dst, o0);
+        __stcs(dst + 1, o1);
       }
       umma::tc_fence_before();
     };
 
-    RawRegs<CKF32> raw0;
-    if (item < a.total) load_raw(raw0, a, item, w, lane, 0);
+    // The raw inputs of one half of the modes live in registers from their request to their use:
+    // half 0 of an item is requested during the second part of the previous tile, half 1 during
+    // half 0's own pass, right after half 0's registers have been used.
+    RawHalf<CKF32> raw;
+    if (item < a.total) {
+      const int j0 = item / a.BH;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) load_tok(raw, a, item - j0 * a.BH, (j0 + a.first_tile) * kTile, w, lane, 0, i);
+    }
     uint32_t n_tiles_done = 0;
     for (uint32_t n = 0; item < a.total; ++n, ++n_tiles_done) {
       const int j = item / a.BH, bh = item - j * a.BH;
       const int jt = j + a.first_tile;
       const int t0 = jt * kTile;
+      FRACSSM_MARK(pslot, 0)
+      float gt_row = 0.f;   // decay of the whole tile for the mode this thread owns in the state update
 
-      // ---- segment products, the base tiles and the per-token factors cp / ks:
-      //   cp[i] = c[i] * (decay from the segment's start to token i, inclusive)
-      //   ks[i] = kappa[i] * (decay after token i to the segment's end)
-      f2 cp[8][2], ks[8][2];
-      f2 g8[2];
-      {
-        RawRegs<CKF32> raw1;
-        load_raw(raw1, a, item, w, lane, 1);   // second half of the segment; the first half is in raw0
-        const uint32_t rowsA = sb + kOffA0 + w * 1024 + th_fix, rowsB = sb + kOffB0 + w * 1024 + th_fix;
-        f2 g4a[2], g4b[2];
-        uint32_t wa[4][2], wb[4][2];
-        // tokens 0..3: reference point just after token 3
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          f2 r[4], cc[4], kk[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            f2 rp[2], cq[2], kq[2];
-            rho_pairs(raw0.r[i], rp);
-            ck_pairs(raw0.c[i], cq);
-            ck_pairs(raw0.k[i], kq);
-            r[i] = rp[hf]; cc[i] = cq[hf]; kk[i] = kq[hf];
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t half_off = h * kAtom + th_fix;
+        // ---- segment products, the base tiles and the per-token factors cp / ks of this half:
+        //   cp[i] = c[i] * (decay from the segment's start to token i, inclusive)
+        //   ks[i] = kappa[i] * (decay after token i to the segment's end)
+        f2 cp[8], ks[8], g8;
+        {
+          const uint32_t rowsA = sb + kOffA0 + half_off + w * 1024, rowsB = sb + kOffB0 + half_off + w * 1024;
+          f2 g4a, g4b;
+          {
+            // tokens 0..3: reference point just after token 3
+            const f2 r0 = floor2(raw.r[0]), r1 = floor2(raw.r[1]), r2 = floor2(raw.r[2]), r3 = floor2(raw.r[3]);
+            const f2 c0 = ck_wide(raw.c[0]), c1 = ck_wide(raw.c[1]), c2 = ck_wide(raw.c[2]), c3 = ck_wide(raw.c[3]);
+            const f2 k0 = ck_wide(raw.k[0]), k1 = ck_wide(raw.k[1]), k2 = ck_wide(raw.k[2]), k3 = ck_wide(raw.k[3]);
+            const f2 q1 = mul2(r3, r2), q0 = mul2(q1, r1);                   // decay after token i up to token 3
+            const f2 p1 = mul2(r0, r1), p2 = mul2(p1, r2), p3 = mul2(p2, r3);
+            const f2 iq0 = rcp2(q0), iq1 = mul2(iq0, r1), iq2 = mul2(iq1, r2);
+            g4a = p3;
+            const f2 b0 = mul2(k0, q0), b1 = mul2(k1, q1), b2 = mul2(k2, r3);
+            emit_pair(rowsA, 0, cvt_bf2(mul2(c0, iq0)));
+            emit_pair(rowsA, 1, cvt_bf2(mul2(c1, iq1)));
+            emit_pair(rowsA, 2, cvt_bf2(mul2(c2, iq2)));
+            emit_pair(rowsA, 3, cvt_bf2(c3));
+            emit_pair(rowsB, 0, cvt_bf2(b0));
+            emit_pair(rowsB, 1, cvt_bf2(b1));
+            emit_pair(rowsB, 2, cvt_bf2(b2));
+            emit_pair(rowsB, 3, cvt_bf2(k3));
+            cp[0] = mul2(c0, r0); cp[1] = mul2(c1, p1); cp[2] = mul2(c2, p2); cp[3] = mul2(c3, p3);
+            ks[0] = b0; ks[1] = b1; ks[2] = b2; ks[3] = k3;   // times g4b, below
           }
-          const f2 q2 = r[3], q1 = mul2(r[3], r[2]), q0 = mul2(q1, r[1]);    // decay after token i up to token 3
-          const f2 p1 = mul2(r[0], r[1]), p2 = mul2(p1, r[2]), p3 = mul2(p2, r[3]);
-          const f2 iq0 = rcp2(q0), iq1 = mul2(iq0, r[1]), iq2 = mul2(iq1, r[2]);
-          g4a[hf] = p3;
-          const f2 b0 = mul2(kk[0], q0), b1 = mul2(kk[1], q1), b2 = mul2(kk[2], q2);
-          wa[0][hf] = cvt_bf2(mul2(cc[0], iq0));
-          wa[1][hf] = cvt_bf2(mul2(cc[1], iq1));
-          wa[2][hf] = cvt_bf2(mul2(cc[2], iq2));
-          wa[3][hf] = cvt_bf2(cc[3]);
-          wb[0][hf] = cvt_bf2(b0); wb[1][hf] = cvt_bf2(b1); wb[2][hf] = cvt_bf2(b2); wb[3][hf] = cvt_bf2(kk[3]);
-          cp[0][hf] = mul2(cc[0], r[0]); cp[1][hf] = mul2(cc[1], p1); cp[2][hf] = mul2(cc[2], p2);
-          cp[3][hf] = mul2(cc[3], p3);
-          ks[0][hf] = b0; ks[1][hf] = b1; ks[2][hf] = b2; ks[3][hf] = kk[3];   // times g4b, below
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          emit_words(rowsA, i, wa[i][0], wa[i][1]);
-          emit_words(rowsB, i, wb[i][0], wb[i][1]);
-        }
-        // tokens 4..7: reference point just before token 4
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          f2 r[4], cc[4], kk[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            f2 rp[2], cq[2], kq[2];
-            rho_pairs(raw1.r[i], rp);
-            ck_pairs(raw1.c[i], cq);
-            ck_pairs(raw1.k[i], kq);
-            r[i] = rp[hf]; cc[i] = cq[hf]; kk[i] = kq[hf];
+          {
+            // tokens 4..7: reference point just before token 4
+            const f2 r4 = floor2(raw.r[4]), r5 = floor2(raw.r[5]), r6 = floor2(raw.r[6]), r7 = floor2(raw.r[7]);
+            const f2 c4 = ck_wide(raw.c[4]), c5 = ck_wide(raw.c[5]), c6 = ck_wide(raw.c[6]), c7 = ck_wide(raw.c[7]);
+            const f2 k4 = ck_wide(raw.k[4]), k5 = ck_wide(raw.k[5]), k6 = ck_wide(raw.k[6]), k7 = ck_wide(raw.k[7]);
+            const f2 q5 = mul2(r4, r5), q6 = mul2(q5, r6), q7 = mul2(q6, r7);  // decay from token 4 to token i
+            const f2 s5 = mul2(r7, r6), s4 = mul2(s5, r5);                      // decay after token i to token 7
+            const f2 iq7 = rcp2(q7), iq6 = mul2(iq7, r7), iq5 = mul2(iq6, r6), iq4 = mul2(iq5, r5);
+            g4b = q7;
+            const f2 a4 = mul2(c4, r4), a5 = mul2(c5, q5), a6 = mul2(c6, q6), a7 = mul2(c7, q7);
+            emit_pair(rowsA, 4, cvt_bf2(a4));
+            emit_pair(rowsA, 5, cvt_bf2(a5));
+            emit_pair(rowsA, 6, cvt_bf2(a6));
+            emit_pair(rowsA, 7, cvt_bf2(a7));
+            emit_pair(rowsB, 4, cvt_bf2(mul2(k4, iq4)));
+            emit_pair(rowsB, 5, cvt_bf2(mul2(k5, iq5)));
+            emit_pair(rowsB, 6, cvt_bf2(mul2(k6, iq6)));
+            emit_pair(rowsB, 7, cvt_bf2(mul2(k7, iq7)));
+            cp[4] = mul2(a4, g4a); cp[5] = mul2(a5, g4a); cp[6] = mul2(a6, g4a); cp[7] = mul2(a7, g4a);
+            ks[4] = mul2(k4, s4); ks[5] = mul2(k5, s5); ks[6] = mul2(k6, r7); ks[7] = k7;
           }
-          const f2 q5 = mul2(r[0], r[1]), q6 = mul2(q5, r[2]), q7 = mul2(q6, r[3]);  // decay from token 4 to token i
-          const f2 s5 = mul2(r[3], r[2]), s4 = mul2(s5, r[1]);                        // decay after token i to token 7
-          const f2 iq7 = rcp2(q7), iq6 = mul2(iq7, r[3]), iq5 = mul2(iq6, r[2]), iq4 = mul2(iq5, r[1]);
-          g4b[hf] = q7;
-          const f2 a4 = mul2(cc[0], r[0]), a5 = mul2(cc[1], q5), a6 = mul2(cc[2], q6), a7 = mul2(cc[3], q7);
-          wa[0][hf] = cvt_bf2(a4); wa[1][hf] = cvt_bf2(a5); wa[2][hf] = cvt_bf2(a6); wa[3][hf] = cvt_bf2(a7);
-          wb[0][hf] = cvt_bf2(mul2(kk[0], iq4));
-          wb[1][hf] = cvt_bf2(mul2(kk[1], iq5));
-          wb[2][hf] = cvt_bf2(mul2(kk[2], iq6));
-          wb[3][hf] = cvt_bf2(mul2(kk[3], iq7));
-          cp[4][hf] = mul2(a4, g4a[hf]); cp[5][hf] = mul2(a5, g4a[hf]); cp[6][hf] = mul2(a6, g4a[hf]);
-          cp[7][hf] = mul2(a7, g4a[hf]);
-          ks[4][hf] = mul2(kk[0], s4); ks[5][hf] = mul2(kk[1], s5); ks[6][hf] = mul2(kk[2], r[3]); ks[7][hf] = kk[3];
-        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          emit_words(rowsA, 4 + i, wa[i][0], wa[i][1]);
-          emit_words(rowsB, 4 + i, wb[i][0], wb[i][1]);
+          for (int i = 0; i < 4; ++i) ks[i] = mul2(ks[i], g4b);
+          g8 = mul2(g4a, g4b);
+          asm volatile("st.shared.b64 [%0], %1;" ::"r"(seg_s + h * 4096 + w * 256), "l"(g8) : "memory");
         }
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) ks[i][hf] = mul2(ks[i][hf], g4b[hf]);
-          g8[hf] = mul2(g4a[hf], g4b[hf]);
-        }
-        asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(seg_s + w * (kM * 4)), "l"(g8[0]), "l"(g8[1]) : "memory");
-      }
-      warp_arrive(fA, lane);
-      umma::named_barrier(1, kWorkers);  // segment products visible to every worker
-      if (n > 0) write_rows(n - 1);  // also: every MMA of the previous tile is done, slots 2..5 are free
+        FRACSSM_MARK(pslot, 1 + 10 * h)
+        warp_arrive(fA, lane);
+        // The other half's inputs (or, in the second pass, nothing: the next item's first half is
+        // requested in the tile's last part) are requested now that this half's registers are free.
+        // (two token rows at a time, between phases: measured faster than one batch)
+        auto request_other_half = [&](int i) {
+          if (h == 0) {
+            load_tok(raw, a, bh, t0, w, lane, 1, i);
+            load_tok(raw, a, bh, t0, w, lane, 1, i + 1);
+          }
+        };
+        request_other_half(0);
+        umma::named_barrier(1, kWorkers);  // segment products visible to every worker
+        FRACSSM_MARK(pslot, 2 + 10 * h)
+        if (h == 0 && n > 0) write_rows(n - 1);  // also: every MMA of the previous tile is done, slots 2..5 are free
+        request_other_half(2);
+        FRACSSM_MARK(pslot, 3 + 10 * h)
 
-      // ---- products of whole segments: back from this segment to the start of its 16 / 32 / 64 /
-      // 128-token block (bk), forward from it to the end of that block (fw).  A level uses bk when
-      // this segment sits in the second half of the level's block (A role), else fw (B role).  The
-      // products grow level by level, interleaved with the levels' operand rows.
-      f2 bk[2] = {one2(), one2()}, fw[2] = {one2(), one2()};
-      auto mulseg = [&](f2 (&acc)[2], int s) {
-        f2 x, y;
-        lds_f2x2(seg_s + s * (kM * 4), x, y);
-        acc[0] = mul2(acc[0], x);
-        acc[1] = mul2(acc[1], y);
-      };
-      // One sibling level: this segment's 8 rows go to the A-role or the B-role tile of its stack.
-      auto emit_level = [&](uint32_t rows_s, const f2 (&src)[8][2], const f2 (&sig)[2], bool scale) {
+        // ---- products of whole segments: back from this segment to the start of its 16 / 32 / 64 /
+        // 128-token block (bk), forward from it to the end of that block (fw).  A level uses bk when
+        // this segment sits in the second half of the level's block (A role), else fw (B role).  The
+        // products grow level by level, interleaved with the levels' operand rows.
+        f2 bk = one2(), fw = one2();
+        const uint32_t seg_h = seg_s + h * 4096;
+        auto mulseg = [&](f2 &acc, int s) {
+          f2 x;
+          asm volatile("ld.shared.b64 %0, [%1];" : "=l"(x) : "r"(seg_h + s * 256));
+          acc = mul2(acc, x);
+        };
+        // One sibling level: this segment's 8 rows go to the A-role or the B-role tile of its stack.
+        auto emit_level = [&](uint32_t rows_s, const f2 (&src)[8], f2 sig, bool scale) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const f2 v0 = scale ? mul2(src[i][0], sig[0]) : src[i][0];
-          const f2 v1 = scale ? mul2(src[i][1], sig[1]) : src[i][1];
-          emit_words(rows_s, i, cvt_bf2(v0), cvt_bf2(v1));
+          for (int i = 0; i < 8; ++i) emit_pair(rows_s, i, cvt_bf2(scale ? mul2(src[i], sig) : src[i]));
+        };
+        // ---- levels 8 (rows 0..63 of the stack) and 16 (rows 64..127) -> slots 2 / 3
+        {
+          const uint32_t rg8 = w >> 1, rg16 = 8 + (((w >> 2) << 1) | (w & 1));
+          if (w & 1) emit_level(sb + kOffY1 + half_off + rg8 * 1024, cp, bk, false);
+          else emit_level(sb + kOffZ1 + half_off + rg8 * 1024, ks, bk, false);
+          if (w & 1) mulseg(bk, w - 1); else mulseg(fw, w + 1);
+          if (w & 2) emit_level(sb + kOffY1 + half_off + rg16 * 1024, cp, bk, true);
+          else emit_level(sb + kOffZ1 + half_off + rg16 * 1024, ks, fw, true);
         }
-      };
-      // ---- levels 8 (rows 0..63 of the stack) and 16 (rows 64..127) -> slots 2 / 3
-      {
-        const uint32_t rg8 = w >> 1, rg16 = 8 + (((w >> 2) << 1) | (w & 1));
-        if (w & 1) emit_level(sb + kOffY1 + rg8 * 1024 + th_fix, cp, bk, false);
-        else emit_level(sb + kOffZ1 + rg8 * 1024 + th_fix, ks, bk, false);
-        if (w & 1) mulseg(bk, w - 1); else mulseg(fw, w + 1);
-        if (w & 2) emit_level(sb + kOffY1 + rg16 * 1024 + th_fix, cp, bk, true);
-        else emit_level(sb + kOffZ1 + rg16 * 1024 + th_fix, ks, fw, true);
-      }
-      warp_arrive(fL1, lane);
-      // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
-      {
-        const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
-        const int b4 = w & ~3, b8 = w & ~7;
-        if (w & 2) { mulseg(bk, b4); mulseg(bk, b4 + 1); } else { mulseg(fw, b4 + 2); mulseg(fw, b4 + 3); }
-        if (w & 4) emit_level(sb + kOffY2 + rg32 * 1024 + th_fix, cp, bk, true);
-        else emit_level(sb + kOffZ2 + rg32 * 1024 + th_fix, ks, fw, true);
-        if (w & 4) {
+        request_other_half(4);
+        // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
+        {
+          const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
+          const int b4 = w & ~3, b8 = w & ~7;
+          if (w & 2) { mulseg(bk, b4); mulseg(bk, b4 + 1); } else { mulseg(fw, b4 + 2); mulseg(fw, b4 + 3); }
+          if (w & 4) emit_level(sb + kOffY2 + half_off + rg32 * 1024, cp, bk, true);
+          else emit_level(sb + kOffZ2 + half_off + rg32 * 1024, ks, fw, true);
+          if (w & 4) {
 #pragma unroll
-          for (int s = 0; s < 4; ++s) mulseg(bk, b8 + s);
+            for (int s = 0; s < 4; ++s) mulseg(bk, b8 + s);
+          } else {
+#pragma unroll
+            for (int s = 4; s < 8; ++s) mulseg(fw, b8 + s);
+          }
+          if (w & 8) emit_level(sb + kOffY2 + half_off + rg64 * 1024, cp, bk, true);
+          else emit_level(sb + kOffZ2 + half_off + rg64 * 1024, ks, fw, true);
+        }
+        warp_arrive(fL, lane);
+        request_other_half(6);
+        FRACSSM_MARK(pslot, 4 + 10 * h)
+        // to the tile's start (bk becomes E) and end (fw becomes F)
+        if (w & 8) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s) mulseg(bk, s);
         } else {
 #pragma unroll
-          for (int s = 4; s < 8; ++s) mulseg(fw, b8 + s);
+          for (int s = 8; s < 16; ++s) mulseg(fw, s);
         }
-        if (w & 8) emit_level(sb + kOffY2 + rg64 * 1024 + th_fix, cp, bk, true);
-        else emit_level(sb + kOffZ2 + rg64 * 1024 + th_fix, ks, fw, true);
-      }
-      warp_arrive(fL2, lane);
-      // to the tile's start (E) and end (F)
-      if (w & 8) {
-#pragma unroll
-        for (int s = 0; s < 8; ++s) mulseg(bk, s);
-      } else {
-#pragma unroll
-        for (int s = 8; s < 16; ++s) mulseg(fw, s);
-      }
-      const f2 (&E)[2] = bk, (&F)[2] = fw;
-      // decay of the whole tile for the mode this thread owns in the state update (m = 32 Q + lane):
-      // every warp holds the full vector, four modes per lane
-      float gt_row;
-      {
-        float g[4];
-        un2(mul2(mul2(E[0], g8[0]), F[0]), g[0], g[1]);
-        un2(mul2(mul2(E[1], g8[1]), F[1]), g[2], g[3]);
-        const int src = 8 * Q + (lane >> 2);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) g[x] = __shfl_sync(0xffffffffu, g[x], src);
-        const int cmp = lane & 3;
-        gt_row = cmp == 0 ? g[0] : cmp == 1 ? g[1] : cmp == 2 ? g[2] : g[3];
-      }
+        // Every warp holds the tile's decay for all 64 modes of this half, two per lane; this thread
+        // needs the one of mode m = 32 Q + lane, which lies in half Q / 2.
+        {
+          float g0, g1;
+          un2(mul2(mul2(bk, g8), fw), g0, g1);
+          const int src = (32 * (Q & 1) + lane) >> 1;
+          g0 = __shfl_sync(0xffffffffu, g0, src);
+          g1 = __shfl_sync(0xffffffffu, g1, src);
+          if (h == (Q >> 1)) gt_row = (lane & 1) ? g1 : g0;
+        }
+        FRACSSM_MARK(pslot, 5 + 10 * h)
 
-      // ---- Khat = ks * (decay to the tile's end), high and low parts -> slots 0 / 1 (base product done)
-      FRACSSM_WAIT(cb0, n);
-      {
-        const uint32_t rowsH = sb + kOffKhi + w * 1024 + th_fix, rowsL = sb + kOffKlo + w * 1024 + th_fix;
+        // ---- Khat = ks * (decay to the tile's end), high and low parts -> slots 0 / 1 (this half's
+        // base product done)
+        FRACSSM_WAIT(cb0, h);
+        FRACSSM_MARK(pslot, 6 + 10 * h)
+        {
+          const uint32_t rowsH = sb + kOffKhi + half_off + w * 1024, rowsL = sb + kOffKlo + half_off + w * 1024;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const f2 k0 = mul2(ks[i][0], F[0]), k1 = mul2(ks[i][1], F[1]);
-          const uint32_t h0 = cvt_bf2(k0), h1 = cvt_bf2(k1);
-          emit_words(rowsH, i, h0, h1);
-          emit_words(rowsL, i, cvt_bf2(sub2(k0, widen_bf2(h0))), cvt_bf2(sub2(k1, widen_bf2(h1))));
+          for (int i = 0; i < 8; ++i) {
+            const f2 kf = mul2(ks[i], fw);
+            const uint32_t hi = cvt_bf2(kf);
+            emit_pair(rowsH, i, hi);
+            emit_pair(rowsL, i, cvt_bf2(sub2(kf, widen_bf2(hi))));
+          }
         }
-      }
-      // ---- Chat = cp * (decay from the tile's start) -> slots 2 / 3 (level-8/16 product done)
-      FRACSSM_WAIT(cb1, n);
-      {
-        const uint32_t rowsH = sb + kOffChi + w * 1024 + th_fix, rowsL = sb + kOffClo + w * 1024 + th_fix;
+        // ---- Chat = cp * (decay from the tile's start) -> slots 2 / 3 (this half's level-8/16 product done)
+        FRACSSM_WAIT(cbL, h);
+        FRACSSM_MARK(pslot, 7 + 10 * h)
+        {
+          const uint32_t rowsH = sb + kOffChi + half_off + w * 1024, rowsL = sb + kOffClo + half_off + w * 1024;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const f2 c0 = mul2(cp[i][0], E[0]), c1 = mul2(cp[i][1], E[1]);
-          const uint32_t h0 = cvt_bf2(c0), h1 = cvt_bf2(c1);
-          emit_words(rowsH, i, h0, h1);
-          emit_words(rowsL, i, cvt_bf2(sub2(c0, widen_bf2(h0))), cvt_bf2(sub2(c1, widen_bf2(h1))));
+          for (int i = 0; i < 8; ++i) {
+            const f2 cf = mul2(cp[i], bk);
+            const uint32_t hi = cvt_bf2(cf);
+            emit_pair(rowsH, i, hi);
+            emit_pair(rowsL, i, cvt_bf2(sub2(cf, widen_bf2(hi))));
+          }
         }
+        warp_arrive(fK, lane);
+        FRACSSM_MARK(pslot, 8 + 10 * h)
       }
-      warp_arrive(fK, lane);
 
       // the next item (published by the control warp at the start of this tile); it must be read
-      // here, before this warp's arrival on fW lets the control warp move on and publish again.
-      // Its first four token rows are requested now and arrive while the tile finishes.
+      // here, before this warp's arrivals on fS / fW let the control warp move on and publish again.
+      // The first half of its inputs is requested now and arrives while the tile finishes.
       FRACSSM_WAIT(item_bar, n + 1);
       const int next = items[(n + 1) & 1];
-      if (next < a.total) load_raw(raw0, a, next, w, lane, 0);
-
-      // ---- W -> slot 4: each block of accumulators goes to its place (levels 64+32 product done)
-      FRACSSM_WAIT(cb2, n);
-      umma::tc_fence_after();
-      {
-        const uint32_t sW = sb + kOffW;
-        // 8 accumulators of row t, columns 8 kc .. 8 kc + 7 of W, as one 16-byte store
-        auto put8 = [&](int t, int kc, const auto &v, int o) {
-          uint4 pk;
-          pk.x = pack2(v[o], v[o + 1]); pk.y = pack2(v[o + 2], v[o + 3]); pk.z = pack2(v[o + 4], v[o + 5]);
-          pk.w = pack2(v[o + 6], v[o + 7]);
-          const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
-                       : "memory");
-        };
-        const int grp = lane >> 3;  // row group of this lane inside the warp's 32 accumulator rows
-        float v[32];
-        if (P == 0) {
-          // base: row t = 32 Q + lane, its own segment's 8 columns, masked above the diagonal
-          umma::tmem_ld32(lane_addr + kColBase + 32 * Q, v);
-          umma::tmem_ld_wait();
-          float o[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const float s = grp == 0 ? v[x] : grp == 1 ? v[8 + x] : grp == 2 ? v[16 + x] : v[24 + x];
-            o[x] = x <= (lane & 7) ? s : 0.f;
-          }
-          put8(32 * Q + lane, 4 * Q + grp, o, 0);
-        } else if (Q < 2) {
-          if (P == 1) {
-            // level 8: accumulator row 32 Q + lane is token 64 Q + 16 grp + 8 + (lane & 7); its partner
-            // segment is the one before it
-            umma::tmem_ld32(lane_addr + kColL1 + 32 * Q, v);
-            umma::tmem_ld_wait();
-            float o[8];
-#pragma unroll
-            for (int x = 0; x < 8; ++x) o[x] = grp == 0 ? v[x] : grp == 1 ? v[8 + x] : grp == 2 ? v[16 + x] : v[24 + x];
-            put8(64 * Q + 16 * grp + 8 + (lane & 7), 8 * Q + 2 * grp, o, 0);
-          } else {
-            // level 64: accumulator row 32 Q + lane is token 64 + 32 Q + lane; columns = tokens 0..63
-            const int c0 = 32 * (P - 2);
-            umma::tmem_ld32(lane_addr + kColL2 + c0, v);
-            umma::tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 4; ++e) put8(64 + 32 * Q + lane, (c0 >> 3) + e, v, 8 * e);
-          }
-        } else {
-          const int q2 = Q - 2;
-          if (P == 1) {
-            // level 16: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 (lane >> 4) + 16 + (lane & 15);
-            // its partners are the 16 tokens before its 16-token half
-            umma::tmem_ld32(lane_addr + kColL1 + 64 + 32 * q2, v);
-            umma::tmem_ld_wait();
-            float o[16];
-#pragma unroll
-            for (int x = 0; x < 16; ++x) o[x] = (lane >> 4) ? v[16 + x] : v[x];
-            const int t = 64 * q2 + 32 * (lane >> 4) + 16 + (lane & 15);
-            const int kc = 8 * q2 + 4 * (lane >> 4);
-            put8(t, kc, o, 0);
-            put8(t, kc + 1, o, 8);
-          } else {
-            // level 32: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 + lane; partners: the 32
-            // tokens before its half
-            float u16[16];
-            umma::tmem_ld16(lane_addr + kColL2 + 64 + 32 * q2 + 16 * (P - 2), u16);
-            umma::tmem_ld_wait();
-            const int t = 64 * q2 + 32 + lane, kc = 8 * q2 + 2 * (P - 2);
-            put8(t, kc, u16, 0);
-            put8(t, kc + 1, u16, 8);
-          }
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(read_bar);
+      const bool more = next < a.total;
+      const int nj = more ? next / a.BH : 0;
+      const int nbh = next - nj * a.BH, nt0 = (nj + a.first_tile) * kTile;
+      auto request_next = [&](int i) {   // two token rows of the next item's first half
+        if (more) {
+          load_tok(raw, a, nbh, nt0, w, lane, 0, i);
+          load_tok(raw, a, nbh, nt0, w, lane, 0, i + 1);
         }
-        // zeros above the diagonal: row t = tid / 4 owns the blocks kc > t / 8, four threads share a row
-        {
-          const int t = tid >> 2;
-          for (int kc = (t >> 3) + 1 + (tid & 3); kc < 16; kc += 4) {
-            const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
-          }
-        }
-      }
-      warp_arrive(fW, lane);
+      };
+      request_next(0);
 
       // ---- the chain: incoming state -> MMA operand (high | low) -> outgoing state
       FRACSSM_WAIT(state_bar, n);
+      FRACSSM_WAIT(cb2, n);  // levels 64+32 product done: slots 4 / 5 are free, its accumulators complete
+      FRACSSM_MARK(pslot, 20)
       const int m_row = 32 * Q + lane;
       float sj[16];
       {
@@ -677,9 +668,12 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
       }
       warp_arrive(fS, lane);
+      request_next(2);
+      FRACSSM_MARK(pslot, 21)
 
       FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
       umma::tc_fence_after();
+      FRACSSM_MARK(pslot, 22)
       {
         // S_next = Gt * S + Sacc
         float acc[16];
@@ -701,7 +695,99 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
       umma::tc_fence_before();
       __syncwarp();
-      if (lane == 0) umma::mbar_arrive(out_bar);  // the control warp releases the row counter
+      if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
+      request_next(4);
+      FRACSSM_MARK(pslot, 23)
+
+      // ---- W -> slot 4: each block of accumulators goes to its place, 8 columns at a time
+      umma::tc_fence_after();
+      {
+        const uint32_t sW = sb + kOffW;
+        // 8 accumulators of row t, columns 8 kc .. 8 kc + 7 of W, as one 16-byte store
+        auto put8 = [&](int t, int kc, const float (&v)[8]) {
+          uint4 pk;
+          pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
+          const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                       : "memory");
+        };
+        // of the warp's 32 accumulator rows, row group g (8 rows) owns the g-th block of 8 columns:
+        // all four blocks are read, each lane keeps its own group's
+        auto own_block = [&](uint32_t col0, float (&o)[8]) {
+          const int grp = lane >> 3;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float b[8];
+            umma::tmem_ld8(lane_addr + col0 + 8 * g, b);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int x = 0; x < 8; ++x) o[x] = (g == 0 || grp == g) ? b[x] : o[x];
+          }
+        };
+        if (P == 0) {
+          // base: row t = 32 Q + lane, its own segment's 8 columns, masked above the diagonal
+          float o[8];
+          own_block(kColBase + 32 * Q, o);
+#pragma unroll
+          for (int x = 0; x < 8; ++x) o[x] = x <= (lane & 7) ? o[x] : 0.f;
+          put8(32 * Q + lane, 4 * Q + (lane >> 3), o);
+        } else if (Q < 2) {
+          if (P == 1) {
+            // level 8: accumulator row 32 Q + lane is token 64 Q + 16 (lane / 8) + 8 + lane % 8; its
+            // partner segment is the one before it
+            float o[8];
+            own_block(kColL1 + 32 * Q, o);
+            put8(64 * Q + 16 * (lane >> 3) + 8 + (lane & 7), 8 * Q + 2 * (lane >> 3), o);
+          } else {
+            // level 64: accumulator row 32 Q + lane is token 64 + 32 Q + lane; columns = tokens 0..63
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float b[8];
+              umma::tmem_ld8(lane_addr + kColL2 + 32 * (P - 2) + 8 * e, b);
+              umma::tmem_ld_wait();
+              put8(64 + 32 * Q + lane, 4 * (P - 2) + e, b);
+            }
+          }
+        } else {
+          const int q2 = Q - 2;
+          if (P == 1) {
+            // level 16: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 (lane / 16) + 16 + lane % 16;
+            // its partners are the 16 tokens before its 16-token half
+            const int t = 64 * q2 + 32 * (lane >> 4) + 16 + (lane & 15);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float b0[8], b1[8];
+              umma::tmem_ld8(lane_addr + kColL1 + 64 + 32 * q2 + 8 * e, b0);
+              umma::tmem_ld8(lane_addr + kColL1 + 64 + 32 * q2 + 16 + 8 * e, b1);
+              umma::tmem_ld_wait();
+#pragma unroll
+              for (int x = 0; x < 8; ++x) b0[x] = (lane >> 4) ? b1[x] : b0[x];
+              put8(t, 8 * q2 + 4 * (lane >> 4) + e, b0);
+            }
+          } else {
+            // level 32: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 + lane; partners: the 32
+            // tokens before its half
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float b[8];
+              umma::tmem_ld8(lane_addr + kColL2 + 64 + 32 * q2 + 16 * (P - 2) + 8 * e, b);
+              umma::tmem_ld_wait();
+              put8(64 * q2 + 32 + lane, 8 * q2 + 2 * (P - 2) + e, b);
+            }
+          }
+        }
+        request_next(6);
+        // zeros above the diagonal: row t = tid / 4 owns the blocks kc > t / 8, four threads share a row
+        {
+          const int t = tid >> 2;
+          for (int kc = (t >> 3) + 1 + (tid & 3); kc < 16; kc += 4) {
+            const uint32_t addr = sW + (kc >> 3) * kAtom + t * 128 + (((kc & 7) ^ (t & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+          }
+        }
+      }
+      warp_arrive(fW, lane);
+      FRACSSM_MARK(pslot, 24)
 
       prev_bh = bh;
       prev_t0 = t0;
@@ -775,6 +861,7 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   a.c = c;
   a.kappa = kappa;
   a.rho = rho;
+  a.u = reinterpret_cast<const __nv_bfloat16 *>(u);
   a.init = initial_state;
   a.h = reinterpret_cast<__nv_bfloat16 *>(h);
   a.fin = final_state;
@@ -912,3 +999,12 @@ extern "C" int fracssm_frac_scan_noalloc_status(void *stream) {
   if (rc) return rc;
   return fracssm_scan_fused_status(scratch, stream);
 }
+
+#ifdef FRACSSM_PHASE_PROF
+// Diagnostic build only: copies the clock stamps of the last launch to the host.
+extern "C" int fracssm_prof_stamps(long long *out, int n) {
+  using namespace fracssm;
+  if (n != kProfTiles * kProfWarps * kProfMarks) return FRACSSM_ERR_ARG;
+  return cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * n) == cudaSuccess ? FRACSSM_OK : FRACSSM_ERR_CUDA;
+}
+#endif

@@ -94,6 +94,11 @@ __device__ __forceinline__ void emit_words(uint32_t rows_s, int i, uint32_t w0, 
   const uint32_t addr = (rows_s ^ (static_cast<uint32_t>(i) << 4)) + i * 128;
   asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(w0), "r"(w1) : "memory");
 }
+// Half of such a store: the packed pair of modes 2 hf, 2 hf + 1 of the thread's four.
+__device__ __forceinline__ void emit_word(uint32_t rows_s, int i, int hf, uint32_t w0) {
+  const uint32_t addr = (rows_s ^ (static_cast<uint32_t>(i) << 4)) + i * 128 + 4 * hf;
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(w0) : "memory");
+}
 // Both components rounded to bf16: the packed pair, and the same values as floats.
 __device__ __forceinline__ float2 bf16_round2(float2 v, uint32_t &packed) {
   const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
