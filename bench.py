@@ -174,6 +174,17 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
+def host_threads():
+    """Use every host core this process may run on, whatever OMP_NUM_THREADS says (torch.distributed.run
+    exports OMP_NUM_THREADS=1 to its workers, which would throttle the CPU arm tenfold); returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline_sample(slabs, threads=None):
     """Time the CPU restatement of the reference scan on `slabs` (batch, head) rows of the workload
     (working precision: bf16 inputs, as the reference's upcast=False).  Returns tokens/s and a note."""
@@ -199,7 +210,7 @@ def run_reference(args, rank):
 
     H, L, R, M, T = CFG["H"], CFG["L"], CFG["R"], CFG["M"], CFG["T"]
     slabs = 2
-    cores = torch.get_num_threads()
+    cores = host_threads()
     u, c, kappa, rho, _ = O.scan_inputs(slabs, L, R, M, dtype=torch.bfloat16, gen="model_like", seed=0)
     for _ in range(args.warmup):
         O.frac_scan_slabs(u[:1], c[:1], kappa[:1], rho[:1], T, None, True, exact=False, slab=1)
@@ -586,6 +597,8 @@ def main():
                     help="launch the timed steps one by one instead of replaying a captured CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="skip the config 3 (sequence-sharded) and config 4 (head-sharded) sections of the line")
     args = ap.parse_args()
     if args.watchdog > 0:      # a stalled run must end with a traceback, not run until someone kills it
         import faulthandler
@@ -683,6 +696,7 @@ def main():
             graph = None
             torch.cuda.synchronize()
     barrier()
+    timed_launch = "CUDA graph of one step, replayed once per step" if graph is not None else "plain launches"
     sampler.reset()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -773,6 +787,19 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": ems, "steps": k2}
         del host, y_host
 
+    # The two sharding modes that communicate, measured in the same process on the same ranks (at one
+    # rank: the same workloads unsharded), each with a parity flag from a small case.
+    config3 = config4 = None
+    if not args.no_sharded and not args.seq_len:
+        d.clear()                  # the config-1 tensors (2.4 GB) are no longer needed
+        y = h = graph = None
+        torch.cuda.empty_cache()
+        k3 = max(3, min(args.steps, 10))
+        config3 = measure_seq(args, rank, world, dev, dist, k3, 3)
+        torch.cuda.empty_cache()
+        config4 = measure_heads(args, rank, world, dev, dist, k3, 3) if 64 % world == 0 else None
+        torch.cuda.empty_cache()
+
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         alg = algorithmic_bytes(BH, L, R, M)
@@ -792,18 +819,20 @@ def main():
         cpu = None
         if not args.no_cpu_baseline:
             slabs = 32
+            cpu_threads = host_threads()
             v, secs = cpu_baseline_sample(slabs)
-            cpu = {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                   "sample": f"{slabs} of {BH} (batch, head) rows of the workload, {secs:.1f} s, "
-                             f"working precision, {os.cpu_count()} logical cpus"}
+            cpu = {"value": v, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
+                   "sample": f"{slabs} of {BH} (batch, head) rows of the workload, one row per call (slab = 1), "
+                             f"{secs:.1f} s, working precision, {cpu_threads} torch threads on "
+                             f"{os.cpu_count()} logical cpus"}
         line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
                 "tokens_per_s_per_gpu": value / world, "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+                "config3": config3, "config4": config4,
                 "scan_path": "fused" if use_fused else "staged",
-                "timed_launch": ("CUDA graph of one step, replayed once per step" if graph is not None
-                                 else "plain launches"),
+                "timed_launch": timed_launch,
                 "ms_per_step_plain_launches": ms_plain}
         print(json.dumps(line), flush=True)
     if dist is not None:

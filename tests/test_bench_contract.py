@@ -32,3 +32,15 @@ def test_reference_arm_on_other_ranks_prints_nothing():
                          env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     assert not [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_reference_arm_sets_its_own_thread_count():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm must not inherit that."""
+    ncpu = len(os.sched_getaffinity(0))
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][0])
+    assert rec["cpu_baseline"]["cores"] == ncpu
+    assert f"{ncpu} torch threads" in rec["cpu_baseline"]["sample"]
