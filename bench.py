@@ -399,6 +399,8 @@ def measure_heads(args, rank, world, dev, dist, steps, warmup):
     w = torch.ones(n * R, device=dev, dtype=torch.bfloat16)
 
     def step():
+        if args.fused_layer:
+            return parallel.head_parallel_layer(u, c, kappa, rho, z, D, w, n, H, 1e-6)
         h = frac_scan(u, c, kappa, rho, T, None, False)
         if world == 1:
             return scan_epilogue(h, x_conv, z, D, w, n, R, 1e-6)
@@ -418,45 +420,55 @@ def measure_heads(args, rank, world, dev, dist, steps, warmup):
             "collective": ("none" if world == 1 else
                            f"one all_reduce (sum) of a [batch, L] float32 vector per step, {batch * L * 4} bytes, NCCL"),
             "collective_bytes_per_rank": 0 if world == 1 else batch * L * 4, "parity_ok": parity_ok,
-            "parity_case": "batch 2, L 512, 64 heads: head-sharded two-pass epilogue vs the one-pass epilogue "
-                           "over all heads, within 1e-3 (relative and absolute, bf16 outputs compared as float)"}
+            "parity_case": "batch 2, L 512, 64 heads: the layer with its heads spread over the ranks vs the same "
+                           "layer unsharded; bf16 outputs within rtol 1e-2 (two bf16 steps: the sums of squares "
+                           "are added in another order) and atol 1e-3"}
 
 
 def heads_parity(rank, world, dev, dist):
-    """Small case at config 4's head count: the head-sharded epilogue (partial sums of squares,
-    all-reduce, second pass) against the one-pass epilogue over all 64 heads (same seed on every rank)."""
+    """Small case at config 4's head count (same seed on every rank): the layer with its 64 heads spread
+    over the ranks against the same layer unsharded, in both forms the library has: scan + two-pass
+    epilogue with one all-reduce of the rows' sums of squares, and the scan with the gate fused into its
+    output stage + norm pass.  One rank: two shards in turn, their sums added by hand."""
     from frac_ssm_b200 import parallel
-    from frac_ssm_b200.layers import scan_epilogue
-    batch, L, H, R = 2, 512, 64, CFG["R"]
-    g = torch.Generator(device=dev).manual_seed(77)
-    h = torch.randn(batch * H, L, R, device=dev, generator=g).bfloat16()
-    x = torch.randn(batch, L, H * R, device=dev, generator=g).bfloat16()
+    from frac_ssm_b200.layers import (scan_epilogue, scan_epilogue_apply, scan_epilogue_sumsq, scan_layer,
+                                      scan_layer_gated, scan_layer_norm, scan_layer_sumsq)
+    from frac_ssm_b200.ops.b200 import frac_scan
+    batch, L, H, R, M, T = 2, 512, 64, CFG["R"], CFG["M"], CFG["T"]
+    u, c, kappa, rho, _ = scan_inputs_device(batch * H, L, R, M, dev, seed=77)
+    g = torch.Generator(device=dev).manual_seed(78)
     z = torch.randn(batch, L, H * R, device=dev, generator=g).bfloat16()
     D = torch.randn(H, R, device=dev, generator=g)
     w = (torch.rand(H * R, device=dev, generator=g) + 0.5).bfloat16()
-    y_ref = scan_epilogue(h, x, z, D, w, H, R, 1e-6)
-    parts = max(world, 2)       # one rank: two shards in turn, the partial sums added by hand
+    x_conv = u.view(batch, H, L, R).permute(0, 2, 1, 3).reshape(batch, L, H * R).contiguous()
+    y_ref = scan_epilogue(frac_scan(u, c, kappa, rho, T, None, False), x_conv, z, D, w, H, R, 1e-6)
+    y_ref_fused = scan_layer(u, c, kappa, rho, z, D, w, H, 1e-6)
+    rows = lambda t, hs: t.view(batch, H, L, -1)[:, hs].reshape(-1, L, t.shape[-1]).contiguous()
+    near = lambda a, b: torch.allclose(a.float(), b.float(), rtol=1e-2, atol=1e-3)
     ok = True
-    if world == 1:
-        from frac_ssm_b200.layers import scan_epilogue_apply, scan_epilogue_sumsq
-        shards = [parallel.shard_heads(H, r, parts) for r in range(parts)]
-        loc = lambda hs: (h.view(batch, H, L, R)[:, hs].reshape(-1, L, R).contiguous(),
-                          x[..., hs.start * R:hs.stop * R].contiguous(), z[..., hs.start * R:hs.stop * R].contiguous(),
-                          D[hs].contiguous())
-        total = sum(scan_epilogue_sumsq(*loc(hs), hs.stop - hs.start, R, 0.0) for hs in shards)
-        for hs in shards:
-            hl, xl, zl, Dl = loc(hs)
-            y = scan_epilogue_apply(hl, xl, zl, Dl, w[hs.start * R:hs.stop * R].contiguous(), hs.stop - hs.start, R,
-                                    total, H * R, 1e-6, 0.0)
-            ok = ok and torch.allclose(y.float(), y_ref[..., hs.start * R:hs.stop * R].float(), rtol=1e-3, atol=1e-3)
-    else:
-        hs = parallel.shard_heads(H, rank, world)
+    shards = [parallel.shard_heads(H, r, 2) for r in range(2)] if world == 1 else [parallel.shard_heads(H, rank, world)]
+    loc = []
+    for hs in shards:
         cols = slice(hs.start * R, hs.stop * R)
+        loc.append((hs, cols, rows(u, hs), rows(c, hs), rows(kappa, hs), rows(rho, hs), z[..., cols].contiguous(),
+                    x_conv[..., cols].contiguous(), D[hs].contiguous(), w[cols].contiguous()))
+    if world == 1:
+        hl = [frac_scan(ul, cl, kl, rl, T, None, False) for _, _, ul, cl, kl, rl, _, _, _, _ in loc]
+        tot = sum(scan_epilogue_sumsq(h, xl, zl, Dl, hs.stop - hs.start, R, 0.0)
+                  for h, (hs, _, _, _, _, _, zl, xl, Dl, _) in zip(hl, loc))
+        fused = [scan_layer_gated(ul, cl, kl, rl, zl, Dl, hs.stop - hs.start)[:2]
+                 for hs, _, ul, cl, kl, rl, zl, _, Dl, _ in loc]
+        tot_f = sum(scan_layer_sumsq(ss) for _, ss in fused)
+        for h, (gated, ss), (hs, cols, _, _, _, _, zl, xl, Dl, wl) in zip(hl, fused, loc):
+            y = scan_epilogue_apply(h, xl, zl, Dl, wl, hs.stop - hs.start, R, tot, H * R, 1e-6, 0.0)
+            yf = scan_layer_norm(gated, ss, wl, R, 1e-6, sumsq=tot_f, norm_width=H * R)
+            ok = ok and near(y, y_ref[..., cols]) and near(yf, y_ref_fused[..., cols])
+    else:
+        hs, cols, ul, cl, kl, rl, zl, xl, Dl, wl = loc[0]
         nl = hs.stop - hs.start
-        y = parallel.head_parallel_epilogue(h.view(batch, H, L, R)[:, hs].reshape(-1, L, R).contiguous(),
-                                            x[..., cols].contiguous(), z[..., cols].contiguous(), D[hs].contiguous(),
-                                            w[cols].contiguous(), nl, R, H, 1e-6)
-        ok = torch.allclose(y.float(), y_ref[..., cols].float(), rtol=1e-3, atol=1e-3)
+        y = parallel.head_parallel_epilogue(frac_scan(ul, cl, kl, rl, T, None, False), xl, zl, Dl, wl, nl, R, H, 1e-6)
+        yf = parallel.head_parallel_layer(ul, cl, kl, rl, zl, Dl, wl, nl, H, 1e-6)
+        ok = near(y, y_ref[..., cols]) and near(yf, y_ref_fused[..., cols])
     return _all_ok(ok, dev, dist)
 
 
@@ -597,6 +609,10 @@ def main():
                     help="launch the timed steps one by one instead of replaying a captured CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--fused-layer", action="store_true",
+                    help="time the layer path with the skip-mix and the gate inside the scan kernel's output stage "
+                         "(two kernels, h never written) instead of scan + one-pass epilogue; measured slower: the "
+                         "scan kernel's worker warps are its bottleneck")
     ap.add_argument("--no-sharded", action="store_true",
                     help="skip the config 3 (sequence-sharded) and config 4 (head-sharded) sections of the line")
     args = ap.parse_args()
@@ -626,7 +642,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     from frac_ssm_b200 import _cabi
-    from frac_ssm_b200.layers import scan_epilogue
+    from frac_ssm_b200.layers import scan_epilogue, scan_layer
     from frac_ssm_b200.ops.b200 import frac_scan
 
     _cabi.lib()
@@ -645,8 +661,11 @@ def main():
     fused = bool(_cabi.lib().fracssm_scan_fused_supported(BH, L, R, M, T, _cabi.BF16, _cabi.BF16))
     use_fused = fused and args.path != "staged"
     launches_per_step = (1 if use_fused else 4) + 1
+    layer_fused = use_fused and args.fused_layer
 
     def step():
+        if layer_fused:    # skip-mix and gate inside the scan kernel's output stage, then the norm pass
+            return scan_layer(d["u"], d["c"], d["kappa"], d["rho"], d["z"], d["D"], d["w"], H, 1e-6)
         h = frac_scan(d["u"], d["c"], d["kappa"], d["rho"], T, None, False, path=args.path)
         return scan_epilogue(h, d["x_conv"], d["z"], d["D"], d["w"], H, R, 1e-6)
 
@@ -757,7 +776,7 @@ def main():
     # end to end: pinned host buffers in, result out, copies inside the timed region
     e2e = None
     if not args.no_e2e:
-        names = ("u", "c", "kappa", "rho", "x_conv", "z")
+        names = ("u", "c", "kappa", "rho", "z") if layer_fused else ("u", "c", "kappa", "rho", "x_conv", "z")
         host = {k: torch.empty(d[k].shape, dtype=d[k].dtype, pin_memory=True).copy_(d[k]) for k in names}
         y_host = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
         h2d = sum(host[k].numel() * host[k].element_size() for k in names)
@@ -765,8 +784,11 @@ def main():
 
         def e2e_step():
             t = {k: host[k].to(dev, non_blocking=True) for k in names}
-            hh = frac_scan(t["u"], t["c"], t["kappa"], t["rho"], T, None, False, path=args.path)
-            yy = scan_epilogue(hh, t["x_conv"], t["z"], d["D"], d["w"], H, R, 1e-6)
+            if layer_fused:
+                yy = scan_layer(t["u"], t["c"], t["kappa"], t["rho"], t["z"], d["D"], d["w"], H, 1e-6)
+            else:
+                hh = frac_scan(t["u"], t["c"], t["kappa"], t["rho"], T, None, False, path=args.path)
+                yy = scan_epilogue(hh, t["x_conv"], t["z"], d["D"], d["w"], H, R, 1e-6)
             y_host.copy_(yy, non_blocking=True)
 
         e2e_step()

@@ -39,4 +39,26 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Output stage of the single-pass scan in layer mode: skip connection and gate applied to the
+// accumulator rows, un-flattened to [batch, L, H * 64], with partial sums of squares for the norm.
+struct ScanLayerOut {
+  const void *gate;   // bf16 [batch, L, H * 64]
+  const float *D;     // [H, 64]
+  void *gated;        // bf16 [batch, L, H * 64]
+  float *ss;          // [batch, L, H, 4]
+  float gate_bias;
+  int64_t H;
+};
+
+// default limit of a device-side wait, in nanoseconds
+inline unsigned long long tile_default_wait_ns() { return 2000000000ull; }
+
+// defined in scan_fused.cu
+size_t scan_fused_workspace_bytes(int64_t B, int64_t L, int64_t R, int64_t M, int64_t T);
+int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
+                         const float *initial_state, void *h, void *final_state, int final_dtype,
+                         void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
+                         int64_t M, int64_t T, void *stream, int first_tile, unsigned long long wait_ns,
+                         const ScanLayerOut *layer);
+
 }  // namespace fracssm

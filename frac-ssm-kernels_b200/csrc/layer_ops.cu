@@ -393,6 +393,53 @@ scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int
   }
 }
 
+
+// Second pass of the fused layer path: the scan kernel has written the gated values g [batch, L, H*R]
+// (bf16) and, per (b, l, head), four partial sums of g^2; this normalises a row with the sum over all
+// its heads (taken from the partial sums, or from `sumsq` when the heads of the layer are spread over
+// several GPUs and the caller has added the per-rank sums).  One block per row, 8 elements per thread.
+__global__ void __launch_bounds__(1024)
+layer_norm_apply_kernel(const __nv_bfloat16 *__restrict__ g, const float *__restrict__ ss, int64_t n_partial,
+                        const float *__restrict__ sumsq, const void *__restrict__ w, int w_dt, float eps,
+                        int64_t norm_width, __nv_bfloat16 *__restrict__ y, int64_t HR) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int64_t j = (int64_t)threadIdx.x * 8;
+  float total;
+  if (sumsq) {
+    total = sumsq[row];
+  } else {
+    float part = 0.f;
+    for (int64_t i = threadIdx.x; i < n_partial; i += blockDim.x) part += ss[row * n_partial + i];
+    total = block_sum(part, red);
+  }
+  const float rs = rsqrtf(total / (float)norm_width + eps);
+  if (j < HR) {
+    float v[8];
+    unpack8(__ldcs(reinterpret_cast<const uint4 *>(g + row * HR + j)), v);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i] * rs * ld_f32(w, j + 2 * i, w_dt),
+                                                     v[2 * i + 1] * rs * ld_f32(w, j + 2 * i + 1, w_dt));
+      o[i] = *reinterpret_cast<const uint32_t *>(&t);
+    }
+    __stcs(reinterpret_cast<uint4 *>(y + row * HR + j), make_uint4(o[0], o[1], o[2], o[3]));
+  }
+}
+
+// sumsq[row] = sum of the row's partial sums (one warp per row)
+__global__ void layer_sumsq_kernel(const float *__restrict__ ss, int64_t n_partial, float *__restrict__ sumsq,
+                                   int64_t rows) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (row >= rows) return;
+  float part = 0.f;
+  for (int64_t i = threadIdx.x % 32; i < n_partial; i += 32) part += ss[row * n_partial + i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (threadIdx.x % 32 == 0) sumsq[row] = part;
+}
+
 }  // namespace fracssm
 
 extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64_t dyn_sl,
@@ -547,4 +594,70 @@ extern "C" int fracssm_scan_epilogue_apply(const void *h, int h_dtype, int64_t h
   return scan_epilogue_launch("scan_epilogue_apply", h, h_dtype, h_sb, h_sl, x_conv, x_sb, x_sl, gate, g_sb,
                               g_sl, xg_dtype, D, weight, w_dtype, gate_bias, eps, y, Bt, L, H, R, kEpilogueApply,
                               const_cast<float *>(sumsq), norm_width, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The layer path with the epilogue fused into the scan's output stage: h never reaches memory.
+//   pass 1 (fracssm_scan_layer_gated): the single-pass scan kernel writes
+//       g = (h + u * D) * silu(gate + gate_bias), un-flattened to [batch, L, H*64], and partial sums of g^2;
+//   pass 2 (fracssm_scan_layer_norm):  y = weight * g * rsqrt(mean(g^2) + eps) per (b, l) row.
+// u is the head-major copy of x_conv the parameter prep makes, so the skip connection reads it directly.
+extern "C" size_t fracssm_scan_layer_workspace_bytes(int64_t Bt, int64_t H, int64_t L, int64_t R, int64_t M) {
+  using namespace fracssm;
+  if (Bt <= 0 || H <= 0 || L <= 0) return 0;
+  return scan_fused_workspace_bytes(Bt * H, L, R, M, 128);
+}
+
+extern "C" int fracssm_scan_layer_gated(const void *u, const void *c, const void *kappa, int ck_dtype,
+                                        const float *rho, const float *initial_state, const void *gate,
+                                        const float *D, float gate_bias, void *gated, float *ss_partial,
+                                        void *final_state, int final_dtype, void *workspace,
+                                        size_t workspace_bytes, int64_t Bt, int64_t H, int64_t L, int64_t R,
+                                        int64_t M, void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || H < 1 || L < 0) return fail(FRACSSM_ERR_ARG, "scan_layer_gated: bad sizes");
+  if (Bt == 0 || L == 0) return fail(FRACSSM_ERR_UNSUPPORTED, "scan_layer_gated: empty input");
+  if (!fracssm_scan_fused_supported(Bt * H, L, R, M, 128, FRACSSM_BF16, ck_dtype))
+    return fail(FRACSSM_ERR_UNSUPPORTED, "scan_layer_gated: needs R = 64, M = 128, bfloat16 u and bfloat16 or float32 c / kappa");
+  if (!u || !c || !kappa || !rho || !gate || !D || !gated || !ss_partial || !workspace)
+    return fail(FRACSSM_ERR_ARG, "scan_layer_gated: null pointer");
+  if (final_state && final_dtype != FRACSSM_F32 && final_dtype != FRACSSM_BF16)
+    return fail(FRACSSM_ERR_ARG, "scan_layer_gated: final_state dtype must be float32 or bfloat16");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(FRACSSM_ERR_ARG, "scan_layer_gated: workspace must be 256-byte aligned");
+  ScanLayerOut lo{gate, D, gated, ss_partial, gate_bias, H};
+  // h is not written in this mode; the pointer only has to pass the alignment check
+  return scan_fused_launch_ex(u, c, kappa, ck_dtype, rho, initial_state, gated, final_state, final_dtype, workspace,
+                              workspace_bytes, Bt * H, L, R, M, 128, stream, 0, tile_default_wait_ns(), &lo);
+}
+
+extern "C" int fracssm_scan_layer_sumsq(const float *ss_partial, float *sumsq, int64_t Bt, int64_t L, int64_t H,
+                                        void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || L < 0 || H < 1) return fail(FRACSSM_ERR_ARG, "scan_layer_sumsq: bad sizes");
+  if (Bt == 0 || L == 0) return FRACSSM_OK;
+  if (!ss_partial || !sumsq) return fail(FRACSSM_ERR_ARG, "scan_layer_sumsq: null pointer");
+  const int64_t rows = Bt * L;
+  layer_sumsq_kernel<<<(unsigned)ceil_div(rows, 8), 256, 0, (cudaStream_t)stream>>>(ss_partial, 4 * H, sumsq, rows);
+  return check_launch("scan_layer_sumsq");
+}
+
+extern "C" int fracssm_scan_layer_norm(const void *gated, const float *ss_partial, const float *sumsq,
+                                       const void *weight, int w_dtype, float eps, int64_t norm_width, void *y,
+                                       int64_t Bt, int64_t L, int64_t H, int64_t R, void *stream) {
+  using namespace fracssm;
+  if (Bt < 0 || L < 0 || H < 1 || R < 1) return fail(FRACSSM_ERR_ARG, "scan_layer_norm: bad sizes");
+  if (Bt == 0 || L == 0) return FRACSSM_OK;
+  if (!gated || !weight || !y || (!ss_partial && !sumsq)) return fail(FRACSSM_ERR_ARG, "scan_layer_norm: null pointer");
+  if (!known_dtype(w_dtype)) return fail(FRACSSM_ERR_ARG, "scan_layer_norm: unsupported weight dtype");
+  const int64_t HR = H * R;
+  if (HR % 8 != 0 || HR > 8192 || norm_width < HR)
+    return fail(FRACSSM_ERR_UNSUPPORTED, "scan_layer_norm: row width must be a multiple of 8, at most 8192, and norm_width >= H * R");
+  if (((reinterpret_cast<uintptr_t>(gated) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+    return fail(FRACSSM_ERR_ARG, "scan_layer_norm: gated and y must be 16-byte aligned");
+  const unsigned threads = (unsigned)(((HR / 8) + 31) / 32 * 32);
+  layer_norm_apply_kernel<<<(unsigned)(Bt * L), threads, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16 *>(gated), ss_partial, 4 * H, sumsq, weight, w_dtype, eps, norm_width,
+      reinterpret_cast<__nv_bfloat16 *>(y), HR);
+  return check_launch("scan_layer_norm");
 }

@@ -94,6 +94,15 @@ struct FusedArgs {
   int BH, L, ntiles, total;
   int first_tile;              // tile index of the first ticket (0 except in the wait-limit self-test)
   unsigned long long wait_ns;  // limit of every device-side wait
+  // Layer mode (gate != null): instead of h, the output stage writes the gated value
+  //   g[b, l, head*64 + r] = (h[bh, l, r] + u[bh, l, r] * D[head, r]) * silu(gate[b, l, head*64 + r] + gate_bias)
+  // un-flattened to [batch, L, H*64], and per (b, l, head) four partial sums of g^2 (16 columns each).
+  const __nv_bfloat16 *gate;
+  const float *D;
+  __nv_bfloat16 *gated;
+  float *ss;
+  float gate_bias;
+  int H;
 };
 
 // Diagnostic build (-DFRACSSM_PHASE_PROF, never the product library): clock stamps of a few warps of
@@ -400,24 +409,70 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     // Output rows of the previous tile (its H accumulator is complete when barH fires).  It runs in
     // the middle of the next tile's first phase, which so overlaps the output MMAs.
     auto write_rows = [&](uint32_t n_done) {
-      FRACSSM_WAIT(barH, n_done);
-      umma::tc_fence_after();
-      const bool bad = *failed != 0;
       const int t = prev_t0 + 32 * Q + lane;
-      uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
-      float acc[16];
-      umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
-      umma::tmem_ld_wait();
-      if (t < a.L) {
-        uint4 o0, o1;
-        if (bad) {
+      if (a.gate == nullptr) {
+        FRACSSM_WAIT(barH, n_done);
+        umma::tc_fence_after();
+        const bool bad = *failed != 0;
+        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
+        float acc[16];
+        umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
+        umma::tmem_ld_wait();
+        if (t < a.L) {
+          uint4 o0, o1;
+          if (bad) {
 #pragma unroll
-          for (int x = 0; x < 16; ++x) acc[x] = kNaN;
+            for (int x = 0; x < 16; ++x) acc[x] = kNaN;
+          }
+          o0.x = pack2(acc[0], acc[1]); o0.y = pack2(acc[2], acc[3]); o0.z = pack2(acc[4], acc[5]); o0.w = pack2(acc[6], acc[7]);
+          o1.x = pack2(acc[8], acc[9]); o1.y = pack2(acc[10], acc[11]); o1.z = pack2(acc[12], acc[13]); o1.w = pack2(acc[14], acc[15]);
+          __stcs(dst, o0);
+          __stcs(dst + 1, o1);
         }
-        o0.x = pack2(acc[0], acc[1]); o0.y = pack2(acc[2], acc[3]); o0.z = pack2(acc[4], acc[5]); o0.w = pack2(acc[6], acc[7]);
-        o1.x = pack2(acc[8], acc[9]); o1.y = pack2(acc[10], acc[11]); o1.z = pack2(acc[12], acc[13]); o1.w = pack2(acc[14], acc[15]);
-        __stcs(dst, o0);
-        __stcs(dst + 1, o1);
+      } else {
+        // layer mode: skip connection, gate and the partial sum of squares, 8 columns at a time; the
+        // row's u and gate values are requested before the wait for the accumulator
+        const int b = prev_bh / a.H, head = prev_bh - b * a.H;
+        const bool live = t < a.L;
+        const int64_t urow = (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P;
+        const int64_t grow = ((static_cast<int64_t>(b) * a.L + t) * a.H + head) * kR + 16 * P;
+        uint4 uv[2] = {}, gv[2] = {};
+        if (live) {
+          const uint4 *up = reinterpret_cast<const uint4 *>(a.u + urow), *gp = reinterpret_cast<const uint4 *>(a.gate + grow);
+          uv[0] = __ldcs(up); uv[1] = __ldcs(up + 1);
+          gv[0] = __ldcs(gp); gv[1] = __ldcs(gp + 1);
+        }
+        FRACSSM_WAIT(barH, n_done);
+        umma::tc_fence_after();
+        const bool bad = *failed != 0;
+        float ss = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float acc[8];
+          umma::tmem_ld8(lane_addr + kColH + 16 * P + 8 * half, acc);
+          umma::tmem_ld_wait();
+          const float4 d0 = __ldg(reinterpret_cast<const float4 *>(a.D + head * kR + 16 * P + 8 * half));
+          const float4 d1 = __ldg(reinterpret_cast<const float4 *>(a.D + head * kR + 16 * P + 8 * half + 4));
+          const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+          const uint32_t uw[4] = {uv[half].x, uv[half].y, uv[half].z, uv[half].w};
+          const uint32_t gw[4] = {gv[half].x, gv[half].y, gv[half].z, gv[half].w};
+          uint32_t o[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float uf = __uint_as_float(e ? (uw[x] & 0xFFFF0000u) : (uw[x] << 16));
+              const float z = __uint_as_float(e ? (gw[x] & 0xFFFF0000u) : (gw[x] << 16)) + a.gate_bias;
+              const float mixed = fmaf(uf, dv[2 * x + e], acc[2 * x + e]);
+              v[e] = bad ? kNaN : mixed * __fdividef(z, 1.f + __expf(-z));
+              ss = fmaf(v[e], v[e], ss);
+            }
+            o[x] = pack2(v[0], v[1]);
+          }
+          if (live) __stcs(reinterpret_cast<uint4 *>(a.gated + grow) + half, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+        if (live) a.ss[((static_cast<int64_t>(b) * a.L + t) * a.H + head) * 4 + P] = ss;
       }
       umma::tc_fence_before();
     };
@@ -654,28 +709,30 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           for (int x = 0; x < 16; ++x) sj[x] = 0.f;
         }
       }
+      // the incoming state as the MMA operand [high | low] of H = Chat S
+      auto state_operand = [&]() {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t ph[4], pl[4];
+        for (int half = 0; half < 2; ++half) {
+          uint32_t ph[4], pl[4];
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const float2 sv = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
-          const float2 hi = bf16_round2(sv, ph[x]);
-          pl[x] = pack2(sv.x - hi.x, sv.y - hi.y);
+          for (int x = 0; x < 4; ++x) {
+            const float2 sv = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
+            const float2 hi = bf16_round2(sv, ph[x]);
+            pl[x] = pack2(sv.x - hi.x, sv.y - hi.y);
+          }
+          const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+          *reinterpret_cast<uint4 *>(smem + kOffS + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+          *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
         }
-        const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-        *reinterpret_cast<uint4 *>(smem + kOffS + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-        *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-      }
-      warp_arrive(fS, lane);
-      request_next(2);
-      FRACSSM_MARK(pslot, 21)
-
-      FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
-      umma::tc_fence_after();
-      FRACSSM_MARK(pslot, 22)
-      {
-        // S_next = Gt * S + Sacc
+        warp_arrive(fS, lane);
+        request_next(2);
+        FRACSSM_MARK(pslot, 21)
+      };
+      // S_next = Gt * S + Sacc, stored for the next tile of the row (or as the final state)
+      auto state_update = [&]() {
+        FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
+        umma::tc_fence_after();
+        FRACSSM_MARK(pslot, 22)
         float acc[16];
         umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
         umma::tmem_ld_wait();
@@ -692,12 +749,23 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           for (int x = 0; x < 16; ++x)
             st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, acc[x]);
         }
+        umma::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
+        request_next(4);
+        FRACSSM_MARK(pslot, 23)
+      };
+      // The outgoing state goes first when its own part (Sacc) is already complete: that is the case
+      // when the tile had to wait for the incoming state, i.e. when the row's chain of tiles is what
+      // limits the run; otherwise the operand goes first and the MMA warp gets to work earlier.
+      const bool chain_first = __shfl_sync(0xffffffffu, umma::mbar_test(cbK, n & 1u) ? 1 : 0, 0) != 0;
+      if (chain_first) {
+        state_update();
+        state_operand();
+      } else {
+        state_operand();
+        state_update();
       }
-      umma::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
-      request_next(4);
-      FRACSSM_MARK(pslot, 23)
 
       // ---- W -> slot 4: each block of accumulators goes to its place, 8 columns at a time
       umma::tc_fence_after();
@@ -815,7 +883,8 @@ size_t scan_fused_workspace_bytes(int64_t B, int64_t, int64_t R, int64_t M, int6
 int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
                          const float *initial_state, void *h, void *final_state, int final_dtype,
                          void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
-                         int64_t M, int64_t T, void *stream, int first_tile, unsigned long long wait_ns) {
+                         int64_t M, int64_t T, void *stream, int first_tile, unsigned long long wait_ns,
+                         const ScanLayerOut *layer) {
   (void)T;
   const bool ckf32 = ck_dtype == FRACSSM_F32;
   if (workspace_bytes < scan_fused_workspace_bytes(B, L, R, M, T))
@@ -824,6 +893,9 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   if (((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(kappa) |
         reinterpret_cast<uintptr_t>(rho) | reinterpret_cast<uintptr_t>(h)) & 15) != 0)
     return fail(FRACSSM_ERR_ARG, "frac_scan: u, c, kappa, rho and h must be 16-byte aligned");
+  if (layer && (((reinterpret_cast<uintptr_t>(layer->gate) | reinterpret_cast<uintptr_t>(layer->gated) |
+                  reinterpret_cast<uintptr_t>(layer->D)) & 15) != 0 || layer->H < 1 || B % layer->H != 0))
+    return fail(FRACSSM_ERR_ARG, "scan_layer: gate, gated and D must be 16-byte aligned and rows = batch * heads");
   // per device, once: opt in to the large dynamic shared memory and remember the SM count
   static std::mutex mu;
   static int sm_count[64] = {};
@@ -875,6 +947,14 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   a.first_tile = first_tile;
   a.total = (a.ntiles - first_tile) * a.BH;
   a.wait_ns = wait_ns;
+  if (layer) {
+    a.gate = reinterpret_cast<const __nv_bfloat16 *>(layer->gate);
+    a.D = layer->D;
+    a.gated = reinterpret_cast<__nv_bfloat16 *>(layer->gated);
+    a.ss = layer->ss;
+    a.gate_bias = layer->gate_bias;
+    a.H = (int)layer->H;
+  }
   CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
   if (rc) return rc;
@@ -892,7 +972,7 @@ int scan_fused_launch(const void *u, const void *c, const void *kappa, int ck_dt
                       void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
                       int64_t M, int64_t T, void *stream) {
   return scan_fused_launch_ex(u, c, kappa, ck_dtype, rho, initial_state, h, final_state, final_dtype, workspace,
-                              workspace_bytes, B, L, R, M, T, stream, 0, kWaitNs);
+                              workspace_bytes, B, L, R, M, T, stream, 0, kWaitNs, nullptr);
 }
 
 }  // namespace fracssm

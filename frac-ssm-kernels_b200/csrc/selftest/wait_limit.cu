@@ -6,10 +6,6 @@
 #include "fracssm_selftest.h"
 
 namespace fracssm {
-int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
-                         const float *initial_state, void *h, void *final_state, int final_dtype,
-                         void *workspace, size_t workspace_bytes, int64_t B, int64_t L, int64_t R,
-                         int64_t M, int64_t T, void *stream, int first_tile, unsigned long long wait_ns);
 int segment_summary_launch_ex(const void *u, const void *kappa, int k_dtype, const float *rho,
                               const float *initial_state, float *final_state, float *decay, void *workspace,
                               size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M, void *stream,
@@ -23,7 +19,7 @@ extern "C" int fracssm_selftest_scan_wait_limit(const void *u, const void *c, co
   using namespace fracssm;
   if (L <= 128 || B < 1) return fail(FRACSSM_ERR_ARG, "selftest_scan_wait_limit: needs at least two tiles");
   return scan_fused_launch_ex(u, c, kappa, FRACSSM_BF16, rho, nullptr, h, final_state, FRACSSM_F32, workspace,
-                              workspace_bytes, B, L, 64, 128, 128, stream, /*first_tile=*/1, wait_ns);
+                              workspace_bytes, B, L, 64, 128, 128, stream, /*first_tile=*/1, wait_ns, nullptr);
 }
 
 extern "C" int fracssm_selftest_summary_wait_limit(const void *u, const void *kappa, const float *rho,

@@ -52,6 +52,11 @@ _SIGNATURES = {
     "fracssm_rmsnorm_gated": (ci, [vp, i64, vp, i64, ci, vp, ci, cf, vp, vp, i64, i64, vp]),
     "fracssm_scan_epilogue": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, vp, ci,
                                    cf, cf, vp, i64, i64, i64, i64, vp]),
+    "fracssm_scan_layer_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),
+    "fracssm_scan_layer_gated": (ci, [vp, vp, vp, ci, vp, vp, vp, vp, cf, vp, vp, vp, ci, vp, sz,
+                                      i64, i64, i64, i64, i64, vp]),
+    "fracssm_scan_layer_sumsq": (ci, [vp, vp, i64, i64, i64, vp]),
+    "fracssm_scan_layer_norm": (ci, [vp, vp, vp, vp, ci, cf, i64, vp, i64, i64, i64, i64, vp]),
     "fracssm_causal_conv_silu": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, vp, ci, vp, ci, i64, i64, i64,
                                       i64, vp]),
     "fracssm_decode_step": (ci, [vp, ci, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]),

@@ -105,3 +105,74 @@ def scan_epilogue_apply(h, x_conv, gate, D, weight, num_heads, head_dim, sumsq, 
             C.ptr(w), C.dt(w), float(gate_bias), float(eps), C.ptr(sumsq), int(norm_width), C.ptr(y),
             B, L, H, R, C.stream_of(x_conv)), "scan_epilogue_apply")
     return y
+
+
+def scan_layer_supported(u, c, gate) -> bool:
+    """True when the fused layer path (scan + skip-mix + gate in one kernel) covers these tensors."""
+    return (u.is_cuda and u.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and u.dim() == 3
+            and u.shape[-1] == 64 and c.shape[-1] == 128 and c.dtype in (torch.bfloat16, torch.float32)
+            and u.shape[0] > 0 and u.shape[1] > 0)
+
+
+def scan_layer_gated(u, c, kappa, rho, gate, D, num_heads, gate_bias=0.0, initial_state=None,
+                     return_final_state=False, final_state_dtype=torch.float32):
+    """First pass of the fused layer path: the scan with the skip connection and the gate applied in
+    its output stage.  Returns (gated [batch, L, H*64] bf16, ss_partial [batch, L, H, 4] float32,
+    final_state or None); h itself is never written."""
+    assert scan_layer_supported(u, c, gate), "scan_layer needs CUDA bf16 u / gate with R = 64, M = 128"
+    assert rho.dtype == torch.float32, "rho must be float32 for numerical stability"
+    BH, L, R = u.shape
+    M = c.shape[-1]
+    H = num_heads
+    assert BH % H == 0 and gate.shape == (BH // H, L, H * R), "gate must be [batch, L, num_heads * head_dim]"
+    Bt = BH // H
+    u, c, kappa, rho, gate = (t.contiguous() for t in (u, c, kappa, rho, gate))
+    init = None if initial_state is None else initial_state.contiguous()
+    Df = D.detach().to(device=u.device, dtype=torch.float32).contiguous()
+    gated = torch.empty(Bt, L, H * R, device=u.device, dtype=torch.bfloat16)
+    ss = torch.empty(Bt, L, H, 4, device=u.device, dtype=torch.float32)
+    fin = torch.empty(BH, R, M, device=u.device, dtype=final_state_dtype) if return_final_state else None
+    lib = C.lib()
+    with C.trace("scan_layer_gated"), torch.cuda.device(u.device):
+        ws = torch.empty(max(lib.fracssm_scan_layer_workspace_bytes(Bt, H, L, R, M), 256), device=u.device,
+                         dtype=torch.uint8)
+        C.check(lib.fracssm_scan_layer_gated(
+            C.ptr(u), C.ptr(c), C.ptr(kappa), C.dt(c), C.ptr(rho), C.ptr(init), C.ptr(gate), C.ptr(Df),
+            float(gate_bias), C.ptr(gated), C.ptr(ss), C.ptr(fin), C.dt_of(final_state_dtype), C.ptr(ws),
+            ws.numel(), Bt, H, L, R, M, C.stream_of(u)), "scan_layer_gated")
+    return gated, ss, fin
+
+
+def scan_layer_sumsq(ss_partial):
+    """Per (b, l) row, the sum of the partial sums of squares of the local heads: float32 [batch, L]."""
+    Bt, L, H, _ = ss_partial.shape
+    out = torch.empty(Bt, L, device=ss_partial.device, dtype=torch.float32)
+    with torch.cuda.device(ss_partial.device):
+        C.check(C.lib().fracssm_scan_layer_sumsq(C.ptr(ss_partial), C.ptr(out), Bt, L, H,
+                                                 C.stream_of(ss_partial)), "scan_layer_sumsq")
+    return out
+
+
+def scan_layer_norm(gated, ss_partial, weight, head_dim, eps=1e-6, sumsq=None, norm_width=None):
+    """Second pass: y = weight * gated * rsqrt(mean(gated^2) + eps) per row; `sumsq` / `norm_width`
+    override the row total and the width when the layer's heads are spread over several GPUs."""
+    Bt, L, HR = gated.shape
+    H = HR // head_dim
+    w = weight.detach().contiguous()
+    y = torch.empty_like(gated)
+    with C.trace("scan_layer_norm"), torch.cuda.device(gated.device):
+        C.check(C.lib().fracssm_scan_layer_norm(
+            C.ptr(gated), C.ptr(ss_partial), C.ptr(sumsq), C.ptr(w), C.dt(w), float(eps),
+            int(HR if norm_width is None else norm_width), C.ptr(y), Bt, L, H, head_dim,
+            C.stream_of(gated)), "scan_layer_norm")
+    return y
+
+
+def scan_layer(u, c, kappa, rho, gate, D, weight, num_heads, eps=1e-6, gate_bias=0.0, initial_state=None,
+               return_final_state=False, final_state_dtype=torch.float32):
+    """frac_scan -> frac_skip_mix -> gated RMSNorm of one layer in two kernels, without writing h
+    (`frac_ssm/models/modeling_frac.py:203-214`).  u [batch*H, L, 64] is the head-major copy of x_conv."""
+    gated, ss, fin = scan_layer_gated(u, c, kappa, rho, gate, D, num_heads, gate_bias, initial_state,
+                                      return_final_state, final_state_dtype)
+    y = scan_layer_norm(gated, ss, weight, u.shape[-1], eps)
+    return (y, fin) if return_final_state else y

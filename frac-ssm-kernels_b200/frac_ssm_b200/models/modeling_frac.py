@@ -19,7 +19,7 @@ from torch import nn
 
 from .. import _cabi as C
 from ..layers.compute_params import compute_params_from_projections
-from ..layers.output_mix import scan_epilogue
+from ..layers.output_mix import scan_epilogue, scan_layer, scan_layer_supported
 from ..modules.rmsnorm_gated import MambaRMSNormGated as RMSNormGated
 from ..modules.rmsnorm_gated import rmsnorm_gated_fwd
 from ..ops.b200.frac_scan import frac_scan
@@ -107,6 +107,9 @@ class FracMixer(nn.Module):
         # dtype of the scan coefficients c / kappa: None = float32 as in the reference; torch.bfloat16
         # halves the scan's coefficient traffic (the benchmark's headline configuration)
         self.coeff_dtype = None
+        # True: skip-mix and gate inside the scan kernel's output stage (h never written; two kernels).
+        # Measured slower than scan + one-pass epilogue at the benchmark shapes, so off by default.
+        self.fuse_gate_into_scan = False
 
     def _gate_logits(self):
         key = (self.read_residual_logit._version, self.write_residual_scale._version,
@@ -144,17 +147,23 @@ class FracMixer(nn.Module):
         if layer_past is None and L > 1:
             x_conv = causal_conv_silu(x, self.conv1d.weight, self.conv1d.bias, attention_mask)
             u, c, kappa, rho = self._scan_params(x_conv, x, attention_mask)
-            # (the backend's own entry point: it can hand back the final state in float32, as carried)
-            out = frac_scan(u, c, kappa, rho, self.chunk_size, None, use_cache, final_state_dtype=torch.float32)
+            if self.fuse_gate_into_scan and scan_layer_supported(u, c, gate.contiguous()):
+                gate = gate.contiguous()
+                # scan, skip-mix and gated norm with the epilogue fused into the scan's output stage
+                # (u is the head-major copy of x_conv, so the skip term needs no second tensor)
+                out = scan_layer(u, c, kappa, rho, gate, self.D, self.out_norm.weight, H,
+                                 self.out_norm.variance_epsilon, gate_bias, None, use_cache)
+                y, final_state = out if use_cache else (out, None)
+            else:
+                # (the backend's own entry point: it can hand back the final state in float32, as carried)
+                out = frac_scan(u, c, kappa, rho, self.chunk_size, None, use_cache, final_state_dtype=torch.float32)
+                mixed, final_state = out if use_cache else (out, None)
+                y = scan_epilogue(mixed, x_conv, gate, self.D, self.out_norm.weight, H, R,
+                                  self.out_norm.variance_epsilon, gate_bias)
             next_cache = None
             if use_cache:
-                mixed, final_state = out
                 state = final_state.view(B, H, R, M).permute(0, 1, 3, 2).contiguous()
                 next_cache = (state, self._conv_state_after(x, attention_mask))
-            else:
-                mixed = out
-            y = scan_epilogue(mixed, x_conv, gate, self.D, self.out_norm.weight, H, R,
-                              self.out_norm.variance_epsilon, gate_bias)
             return self.out_proj(y), next_cache
 
         # token by token, with or without a cache (a one-token prompt starts from an empty one)

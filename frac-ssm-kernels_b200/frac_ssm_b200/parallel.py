@@ -132,8 +132,10 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     (one small all-reduce and a host synchronisation, see `_auto_local_splits`).
     """
     ops = CudaStageOps if ops is None else ops
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    if dist.is_available() and dist.is_initialized():
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+    else:                       # a single process: the same composition without any exchange
+        world, rank = 1, 0
     B, L_local, R = u.shape
     M = c.shape[-1]
     if rank < world - 1 and L_local % chunk_size != 0:
@@ -220,3 +222,19 @@ def head_parallel_epilogue(h, x_conv, gate, D, weight, local_heads, head_dim, to
         dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=group)
     return ops.apply(h, x_conv, gate, D, weight, local_heads, head_dim, sumsq, total_heads * head_dim,
                      eps, gate_bias)
+
+
+def head_parallel_layer(u, c, kappa, rho, gate, D, weight, local_heads, total_heads, eps=1e-6, gate_bias=0.0,
+                        group=None):
+    """Scan + skip-mix + gated RMSNorm of a layer whose heads are spread over the ranks of `group`, with
+    the epilogue fused into the scan's output stage.  Every rank passes the tensors of its own heads
+    (u, c, kappa, rho [batch*local_heads, L, .], gate [batch, L, local_heads*64], D [local_heads, 64],
+    weight [local_heads*64]); the only communication is one all-reduce of batch*L float32 sums."""
+    from .layers.output_mix import scan_layer_gated, scan_layer_norm, scan_layer_sumsq
+    gated, ss, _ = scan_layer_gated(u, c, kappa, rho, gate, D, local_heads, gate_bias)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        sumsq = scan_layer_sumsq(ss)
+        dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=group)
+        return scan_layer_norm(gated, ss, weight, u.shape[-1], eps, sumsq=sumsq,
+                               norm_width=total_heads * u.shape[-1])
+    return scan_layer_norm(gated, ss, weight, u.shape[-1], eps)

@@ -230,6 +230,34 @@ int fracssm_scan_epilogue(const void *h, int h_dtype, int64_t h_sb, int64_t h_sl
                           int64_t Bt, int64_t L, int64_t H, int64_t R, void *stream);
 
 /*
+ * Scan, skip-mix and gated RMSNorm of one layer with the epilogue fused into the scan's output stage:
+ * h never reaches memory.  Replaces the sequence frac_ssm/models/modeling_frac.py:203-214
+ * (frac_scan -> frac_skip_mix, frac_ssm/layers/output_mix.py:232 -> MambaRMSNormGated,
+ * frac_ssm/modules/rmsnorm_gated.py:292) for R = 64, M = 128, bf16 u / gate, dense tensors.
+ *   fracssm_scan_layer_gated: the single-pass scan kernel writes
+ *       gated[b, l, head*64 + r] = (h[b*H + head, l, r] + u[b*H + head, l, r] * D[head, r])
+ *                                  * silu(gate[b, l, head*64 + r] + gate_bias)          (bf16, [Bt, L, H*64])
+ *     and ss_partial [Bt, L, H, 4] float32, four partial sums of gated^2 per (b, l, head).  u [Bt*H, L, 64] is
+ *     the head-major copy of x_conv that the parameter prep makes, so the skip term reads it directly.
+ *     workspace: fracssm_scan_layer_workspace_bytes bytes, 256-byte aligned.
+ *   fracssm_scan_layer_norm: y[b, l, :] = weight * gated[b, l, :] * rsqrt(sum / norm_width + eps), where sum
+ *     is the row's total of ss_partial, or sumsq[b*L + l] when sumsq is not NULL (a layer whose heads are
+ *     spread over several GPUs: the caller adds the per-rank sums from fracssm_scan_layer_sumsq with one
+ *     all-reduce and passes the layer's full width as norm_width).
+ */
+size_t fracssm_scan_layer_workspace_bytes(int64_t Bt, int64_t H, int64_t L, int64_t R, int64_t M);
+int fracssm_scan_layer_gated(const void *u, const void *c, const void *kappa, int ck_dtype, const float *rho,
+                             const float *initial_state, const void *gate, const float *D, float gate_bias,
+                             void *gated, float *ss_partial, void *final_state, int final_dtype,
+                             void *workspace, size_t workspace_bytes, int64_t Bt, int64_t H, int64_t L,
+                             int64_t R, int64_t M, void *stream);
+int fracssm_scan_layer_sumsq(const float *ss_partial, float *sumsq, int64_t Bt, int64_t L, int64_t H,
+                             void *stream);
+int fracssm_scan_layer_norm(const void *gated, const float *ss_partial, const float *sumsq, const void *weight,
+                            int w_dtype, float eps, int64_t norm_width, void *y, int64_t Bt, int64_t L,
+                            int64_t H, int64_t R, void *stream);
+
+/*
  * The same epilogue for a layer whose heads are spread over several GPUs (the norm then spans columns
  * held by other GPUs).  Pass 1 writes, per (b, l) row, the sum of squares of the gated values of the H
  * local heads; the caller adds these [Bt*L] float32 vectors across GPUs (one all-reduce); pass 2

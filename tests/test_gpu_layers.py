@@ -244,3 +244,56 @@ def test_mixer_path_composition_matches_oracle():
     close(h, ho, **TOL_BF16)
     close(y, yo, rtol=3e-2, atol=3e-2)       # two bf16 roundings (h, mixed) before the norm
     close(y_fused, yo, **TOL_BF16)
+
+
+@pytest.mark.parametrize("B,H,L,with_init,ckdt", [(2, 3, 700, True, torch.bfloat16), (1, 4, 129, False, torch.float32),
+                                                   (3, 2, 1024, False, torch.bfloat16)])
+def test_fused_layer_path_matches_oracle(B, H, L, with_init, ckdt):
+    """Scan with the skip-mix and the gate fused into its output stage, then the norm pass: against
+    rmsnorm_gated(skip_mix(frac_scan(...))) of the oracle, on ragged L, with and without an initial
+    state; and the plain frac_scan still returns h as before."""
+    from frac_ssm_b200.layers import scan_layer
+    from frac_ssm_b200.ops.b200 import frac_scan
+    R, M, T = 64, 128, 256
+    u, c, kappa, rho, init = O.scan_inputs(B * H, L, R, M, dtype=torch.bfloat16, gen="model_like", seed=41)
+    init = init if with_init else None
+    g = torch.Generator().manual_seed(42)
+    gate = torch.randn(B, L, H * R, generator=g).bfloat16()
+    D = torch.randn(H, R, generator=g)
+    w = (torch.rand(H * R, generator=g) + 0.5).bfloat16()
+    x_conv = u.view(B, H, L, R).permute(0, 2, 1, 3).reshape(B, L, H * R)
+    h_ref, f_ref = O.frac_scan_slabs(u.float(), c.float(), kappa.float(), rho, T, init, True, exact=True, slab=2)
+    y_ref = O.rmsnorm_gated(O.skip_mix(h_ref, x_conv, D, H, R, exact=True), w, gate.float() + 0.25, 1e-6, exact=True)
+    cg, kg = c.to(ckdt).cuda(), kappa.to(ckdt).cuda()
+    y, fin = scan_layer(u.cuda(), cg, kg, rho.cuda(), gate.cuda(), D.cuda(), w.cuda(), H, 1e-6, 0.25,
+                        None if init is None else init.cuda(), True)
+    close(y, y_ref, rtol=3e-2, atol=3e-2)      # two bf16 roundings (the gated values, then y) around the norm
+    close(fin, f_ref, **TOL_F32)
+    h = frac_scan(u.cuda(), cg, kg, rho.cuda(), T, None if init is None else init.cuda(), False)
+    close(h, h_ref, **TOL_BF16)
+
+
+@pytest.mark.parametrize("shards", [2, 4])
+def test_fused_layer_path_head_sharded_emulation(shards):
+    """The head-sharded form on one GPU: every shard's scan + gate pass, the shards' row sums added by hand
+    (what the all-reduce does), every shard normalised with the total: equals the unsharded fused layer."""
+    from frac_ssm_b200.layers import scan_layer, scan_layer_gated, scan_layer_norm, scan_layer_sumsq
+    B, H, L, R, M = 2, 8, 300, 64, 128
+    u, c, kappa, rho, _ = (t.cuda() for t in O.scan_inputs(B * H, L, R, M, dtype=torch.bfloat16, gen="random", seed=43))
+    g = torch.Generator().manual_seed(44)
+    gate = torch.randn(B, L, H * R, generator=g).bfloat16().cuda()
+    D = torch.randn(H, R, generator=g).cuda()
+    w = (torch.rand(H * R, generator=g) + 0.5).bfloat16().cuda()
+    y_full = scan_layer(u, c, kappa, rho, gate, D, w, H, 1e-6, 0.0)
+    hl = H // shards
+    parts = []
+    for s in range(shards):
+        rows = lambda t: t.view(B, H, L, -1)[:, s * hl:(s + 1) * hl].reshape(B * hl, L, -1).contiguous()
+        cols = slice(s * hl * R, (s + 1) * hl * R)
+        gated, ss, _ = scan_layer_gated(rows(u), rows(c), rows(kappa), rows(rho), gate[..., cols].contiguous(),
+                                        D[s * hl:(s + 1) * hl], hl, 0.0)
+        parts.append((gated, ss, cols))
+    total = sum(scan_layer_sumsq(ss) for _, ss, _ in parts)
+    for gated, ss, cols in parts:
+        y = scan_layer_norm(gated, ss, w[cols], R, 1e-6, sumsq=total, norm_width=H * R)
+        torch.testing.assert_close(y.float(), y_full[..., cols].float(), rtol=1e-2, atol=1e-3)
