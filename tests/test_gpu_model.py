@@ -63,6 +63,13 @@ def test_bf16_model_takes_the_single_pass_scan(golden_dir):
     logits2, _ = model(g["input_ids"][:, :L].cuda(), use_cache=True)
     err2 = (logits2.float().cpu() - ref).abs().max().item()
     assert err2 <= 0.03 * ref.abs().max().item(), err2
+    # the gate fused into the scan kernel's output stage (off by default): same bound, same cached state
+    for layer in model.model.layers:
+        layer.mixer.fuse_gate_into_scan = True
+    logits3, past3 = model(g["input_ids"][:, :L].cuda(), use_cache=True)
+    err3 = (logits3.float().cpu() - ref).abs().max().item()
+    assert err3 <= 0.03 * ref.abs().max().item(), err3
+    close(past3[0][0], past[0][0].float().cpu(), rtol=1e-3, atol=1e-3)
 
 
 @pytest.mark.parametrize("dtype,C_,K", [(torch.bfloat16, 1536, 4), (torch.float32, 100, 4), (torch.bfloat16, 72, 3),
