@@ -23,7 +23,8 @@ struct ParamArgs {
   const void *x; int x_dt; int64_t x_sb, x_sl;
   const float *mask; int64_t m_sb, m_sl;
   const float *dt_bias, *log_tau;
-  float read_gate, write_gate, inv_read_temp, dt_min, dt_max, a_min, a_max, l_min, l_max;
+  const float *read_logit, *write_logit;   // the two gate parameters, one float each, on the device
+  float inv_read_temp, dt_min, dt_max, a_min, a_max, l_min, l_max;
   void *u, *c, *kappa; int ck_dt; float *rho;
   int64_t L, H, R, M;
 };
@@ -31,6 +32,7 @@ struct ParamArgs {
 // One warp per (bh, token): lanes stride over the M modes; two softmaxes by warp shuffles.
 __global__ void __launch_bounds__(128) compute_params_kernel(const ParamArgs a) {
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const float read_gate = sigmoidf_(__ldg(a.read_logit)), write_gate = sigmoidf_(__ldg(a.write_logit));
   const int64_t l = (int64_t)blockIdx.x * 4 + warp;
   const int64_t bh = blockIdx.y;
   if (l >= a.L) return;
@@ -50,24 +52,24 @@ __global__ void __launch_bounds__(128) compute_params_kernel(const ParamArgs a) 
   float rmax = -INFINITY, wmax = -INFINITY;
   for (int64_t m = lane; m < M; m += 32) {
     const float prior = -alpha * a.log_tau[m];
-    rmax = fmaxf(rmax, (prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp);
-    wmax = fmaxf(wmax, prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt));
+    rmax = fmaxf(rmax, (prior + read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp);
+    wmax = fmaxf(wmax, prior + write_gate * ld_f32(a.rw, wbase + m, a.rw_dt));
   }
   rmax = warp_max(rmax);
   wmax = warp_max(wmax);
   float rsum = 0.f, wsum = 0.f;
   for (int64_t m = lane; m < M; m += 32) {
     const float prior = -alpha * a.log_tau[m];
-    rsum += __expf((prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax);
-    wsum += __expf(prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax);
+    rsum += __expf((prior + read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax);
+    wsum += __expf(prior + write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax);
   }
   const float rinv = 1.f / warp_sum(rsum), winv = 1.f / warp_sum(wsum);
   const int64_t obase = (bh * a.L + l) * M;
   for (int64_t m = lane; m < M; m += 32) {
     const float lt = a.log_tau[m];
     const float prior = -alpha * lt;
-    const float cw = __expf((prior + a.read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax) * rinv;
-    const float ww = __expf(prior + a.write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax) * winv;
+    const float cw = __expf((prior + read_gate * ld_f32(a.rw, rbase + m, a.rw_dt)) * a.inv_read_temp - rmax) * rinv;
+    const float ww = __expf(prior + write_gate * ld_f32(a.rw, wbase + m, a.rw_dt) - wmax) * winv;
     float rho = expf(-dt * (rate / fmaxf(expf(lt), 1e-6f)));
     rho = fminf(fmaxf(rho, 1e-6f), 1.f - 1e-6f);
     float kap = (1.f - rho) * ww;
@@ -96,6 +98,7 @@ __device__ __forceinline__ void unpack4(const uint2 &p, float (&f)[4]) {
 
 __global__ void __launch_bounds__(128) compute_params_m128_kernel(const ParamArgs a) {
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const float read_gate = sigmoidf_(__ldg(a.read_logit)), write_gate = sigmoidf_(__ldg(a.write_logit));
   const int64_t l0 = ((int64_t)blockIdx.x * 4 + warp) * kPrepTokens;
   const int64_t bh = blockIdx.y;
   if (l0 >= a.L) return;
@@ -136,8 +139,8 @@ __global__ void __launch_bounds__(128) compute_params_m128_kernel(const ParamArg
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float prior = -alpha * lt[i];
-      rl[i] = (prior + a.read_gate * rres[i]) * a.inv_read_temp;
-      wl[i] = prior + a.write_gate * wres[i];
+      rl[i] = (prior + read_gate * rres[i]) * a.inv_read_temp;
+      wl[i] = prior + write_gate * wres[i];
       rmax = fmaxf(rmax, rl[i]);
       wmax = fmaxf(wmax, wl[i]);
     }
@@ -447,7 +450,7 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
                                       const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl,
                                       const float *mask, int64_t m_sb, int64_t m_sl,
                                       const float *dt_bias, const float *base_log_tau,
-                                      float read_gate_logit, float write_gate_logit, float read_temp,
+                                      const float *read_gate_logit, const float *write_gate_logit, float read_temp,
                                       float dt_min, float dt_max, float alpha_min, float alpha_max,
                                       float lambda_min, float lambda_max, void *u, void *c,
                                       void *kappa, int ck_dtype, float *rho, int64_t Bt, int64_t L,
@@ -457,7 +460,8 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
   if (!known_dtype(dyn_dtype) || !known_dtype(rw_dtype) || !known_dtype(x_dtype) || !known_dtype(ck_dtype))
     return fail(FRACSSM_ERR_ARG, "compute_params: unsupported dtype");
   if (Bt == 0 || L == 0) return FRACSSM_OK;
-  if (!dyn || !rw || !x_conv || !dt_bias || !base_log_tau || !u || !c || !kappa || !rho)
+  if (!dyn || !rw || !x_conv || !dt_bias || !base_log_tau || !read_gate_logit || !write_gate_logit || !u || !c ||
+      !kappa || !rho)
     return fail(FRACSSM_ERR_ARG, "compute_params: null pointer");
   if (Bt * H > 65535) return fail(FRACSSM_ERR_UNSUPPORTED, "compute_params: batch*heads too large for one launch");
   ParamArgs a{};
@@ -466,8 +470,8 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
   a.x = x_conv; a.x_dt = x_dtype; a.x_sb = x_sb; a.x_sl = x_sl;
   a.mask = mask; a.m_sb = m_sb; a.m_sl = m_sl;
   a.dt_bias = dt_bias; a.log_tau = base_log_tau;
-  a.read_gate = 1.f / (1.f + expf(-read_gate_logit));
-  a.write_gate = 1.f / (1.f + expf(-write_gate_logit));
+  a.read_logit = read_gate_logit;
+  a.write_logit = write_gate_logit;
   a.inv_read_temp = 1.f / read_temp;
   a.dt_min = dt_min; a.dt_max = dt_max; a.a_min = alpha_min; a.a_max = alpha_max;
   a.l_min = lambda_min; a.l_max = lambda_max;

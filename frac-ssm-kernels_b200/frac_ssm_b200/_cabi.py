@@ -21,6 +21,7 @@ F32, BF16, F16 = 0, 1, 2
 _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 PATH_AUTO, PATH_STAGED, PATH_FUSED = 0, 1, 2
+ABI_VERSION = 2       # FRACSSM_ABI_VERSION of include/fracssm.h this binding was written against
 
 i64, ci, cf, vp, sz = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 
@@ -46,7 +47,7 @@ _SIGNATURES = {
     "fracssm_scan_fused_status": (ci, [vp, vp]),
     "fracssm_frac_scan_noalloc_status": (ci, [vp]),
     "fracssm_compute_params": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, ci, i64, i64,
-                                    vp, i64, i64, vp, vp, cf, cf, cf, cf, cf, cf, cf, cf, cf,
+                                    vp, i64, i64, vp, vp, vp, vp, cf, cf, cf, cf, cf, cf, cf,
                                     vp, vp, vp, ci, vp, i64, i64, i64, i64, i64, vp]),
     "fracssm_skip_mix": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, vp, ci, i64, i64, i64, i64, vp]),
     "fracssm_rmsnorm_gated": (ci, [vp, i64, vp, i64, ci, vp, ci, cf, vp, vp, i64, i64, vp]),
@@ -90,7 +91,7 @@ def lib():
                 for name, (res, args) in _SIGNATURES.items():
                     fn = getattr(handle, name)
                     fn.restype, fn.argtypes = res, args
-                if handle.fracssm_abi_version() != 1:
+                if handle.fracssm_abi_version() != ABI_VERSION:
                     raise ImportError("libfracssm.so has an unexpected ABI version")
                 _lib = handle
     return _lib

@@ -18,7 +18,9 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
                                     lambda_min, lambda_max, coeff_dtype=torch.float32):
     """Elementwise part: dyn [B,L,3H], rw [B,L,2HM], x_conv [B,L,HR] ->
     (u [BH,L,R] in x_conv.dtype, c, kappa [BH,L,M] in `coeff_dtype`, rho [BH,L,M] float32),
-    head-major.  The reference emits float32 coefficients; bfloat16 halves what the scan reads."""
+    head-major.  The reference emits float32 coefficients; bfloat16 halves what the scan reads.
+    `read_residual_logit` / `write_residual_scale` are the two scalar parameters as tensors (they
+    stay on the device: nothing here synchronises) or, for convenience, Python numbers."""
     assert dyn.dim() == 3 and rw.dim() == 3 and x_conv.dim() == 3, "dyn, rw and x_conv must be 3D"
     assert dyn.is_cuda and rw.is_cuda and x_conv.is_cuda, "inputs must be on CUDA"
     B, L, _ = x_conv.shape
@@ -38,6 +40,12 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
     rho = torch.empty(B * H, L, M, device=dev, dtype=torch.float32)
     if B == 0 or L == 0:
         return u, c, kappa, rho
+    def scalar(v):
+        if torch.is_tensor(v):
+            return v.detach().to(device=dev, dtype=torch.float32).reshape(-1)[:1].contiguous()
+        return torch.full((1,), float(v), device=dev, dtype=torch.float32)
+
+    rlog, wlog = scalar(read_residual_logit), scalar(write_residual_scale)
     dtb = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
     ltau = base_log_tau.detach().to(device=dev, dtype=torch.float32).contiguous()
     with C.trace("frac_compute_scan_params"), torch.cuda.device(dev):
@@ -45,7 +53,7 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
             C.ptr(dyn), C.dt(dyn), dyn.stride(0), dyn.stride(1), C.ptr(rw), C.dt(rw), rw.stride(0),
             rw.stride(1), C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1),
             C.ptr(mask), 0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1),
-            C.ptr(dtb), C.ptr(ltau), float(read_residual_logit), float(write_residual_scale),
+            C.ptr(dtb), C.ptr(ltau), C.ptr(rlog), C.ptr(wlog),
             float(read_temp), float(dt_min), float(dt_max), float(alpha_min), float(alpha_max),
             float(lambda_min), float(lambda_max), C.ptr(u), C.ptr(c), C.ptr(kappa), C.dt(c), C.ptr(rho),
             B, L, H, R, M, C.stream_of(x_conv)), "compute_params")
@@ -62,7 +70,7 @@ def frac_compute_scan_params(model, x_conv, x, attention_mask=None):
     rw = F.linear(x_conv, model.rw_proj.weight)
     cfg = model.config
     return compute_params_from_projections(
-        dyn, rw, x_conv, attention_mask, model.dt_bias, model.read_residual_logit.item(),
-        model.write_residual_scale.item(), model.base_log_tau, model.num_heads, model.head_dim,
+        dyn, rw, x_conv, attention_mask, model.dt_bias, model.read_residual_logit,
+        model.write_residual_scale, model.base_log_tau, model.num_heads, model.head_dim,
         model.num_modes, model.read_temp, cfg.frac_dt_min, cfg.frac_dt_max, cfg.frac_alpha_min,
         cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max)

@@ -103,7 +103,6 @@ class FracMixer(nn.Module):
         self.out_norm = RMSNormGated(self.inner_dim, eps=config.rms_norm_eps)
         self.out_proj = nn.Linear(self.inner_dim, self.hidden_size, bias=False)
         self.D = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
-        self._gates = None  # (version key, read logit, write logit) as Python floats: no sync per call
         # dtype of the scan coefficients c / kappa: None = float32 as in the reference; torch.bfloat16
         # halves the scan's coefficient traffic (the benchmark's headline configuration)
         self.coeff_dtype = None
@@ -111,20 +110,13 @@ class FracMixer(nn.Module):
         # Measured slower than scan + one-pass epilogue at the benchmark shapes, so off by default.
         self.fuse_gate_into_scan = False
 
-    def _gate_logits(self):
-        key = (self.read_residual_logit._version, self.write_residual_scale._version,
-               self.read_residual_logit.data_ptr(), self.write_residual_scale.data_ptr())
-        if self._gates is None or self._gates[0] != key:
-            self._gates = (key, float(self.read_residual_logit.item()), float(self.write_residual_scale.item()))
-        return self._gates[1], self._gates[2]
-
     def _scan_params(self, x_conv, x, attention_mask):
         cfg = self.config
         dyn = F.linear(x, self.dyn_proj.weight, self.dyn_proj.bias)
         rw = F.linear(x_conv, self.rw_proj.weight)
-        read_logit, write_logit = self._gate_logits()
         return compute_params_from_projections(
-            dyn, rw, x_conv, attention_mask, self.dt_bias, read_logit, write_logit, self.base_log_tau,
+            dyn, rw, x_conv, attention_mask, self.dt_bias, self.read_residual_logit, self.write_residual_scale,
+            self.base_log_tau,
             self.num_heads, self.head_dim, self.num_modes, self.read_temp, cfg.frac_dt_min, cfg.frac_dt_max,
             cfg.frac_alpha_min, cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max,
             coeff_dtype=torch.float32 if self.coeff_dtype is None else self.coeff_dtype)

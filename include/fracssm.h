@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define FRACSSM_ABI_VERSION 1
+#define FRACSSM_ABI_VERSION 2
 
 /* element types */
 #define FRACSSM_F32 0
@@ -184,7 +184,9 @@ int fracssm_frac_scan_noalloc_status(void *stream);
  * Elementwise scan-parameter prep after the two projections.
  * dyn [Bt, L, 3H] (dt, alpha, lambda logits), rw [Bt, L, 2*H*M] (read then write residuals),
  * x_conv [Bt, L, H*R]; mask [Bt, L] f32 or NULL; dt_bias [H], base_log_tau [M] f32;
- * read_gate_logit, write_gate_logit: the two scalar parameters (sigmoid is applied here).
+ * read_gate_logit, write_gate_logit: the two scalar parameters as DEVICE pointers to one float32 each,
+ * as the reference passes them (frac_ssm/layers/compute_params.py:199-202): no host read of a
+ * parameter, hence no synchronisation in the forward; the sigmoid is applied in the kernel.
  * Outputs head-major: u [Bt*H, L, R] (x dtype), rho [Bt*H, L, M] f32, c and kappa [Bt*H, L, M] in
  * ck_dtype (f32 is what the reference emits; bf16 halves the scan's coefficient traffic).
  * Replaces the kernel behind frac_ssm/layers/compute_params.py:583
@@ -194,8 +196,8 @@ int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dyn_sb, int64
                            const void *rw, int rw_dtype, int64_t rw_sb, int64_t rw_sl,
                            const void *x_conv, int x_dtype, int64_t x_sb, int64_t x_sl,
                            const float *mask, int64_t m_sb, int64_t m_sl, const float *dt_bias,
-                           const float *base_log_tau, float read_gate_logit,
-                           float write_gate_logit, float read_temp, float dt_min, float dt_max,
+                           const float *base_log_tau, const float *read_gate_logit,
+                           const float *write_gate_logit, float read_temp, float dt_min, float dt_max,
                            float alpha_min, float alpha_max, float lambda_min, float lambda_max,
                            void *u, void *c, void *kappa, int ck_dtype, float *rho, int64_t Bt,
                            int64_t L, int64_t H, int64_t R, int64_t M, void *stream);

@@ -38,7 +38,7 @@ def test_binding_covers_every_declared_symbol():
 
 def test_abi_version_and_error_text():
     lib = _cabi.lib()
-    assert lib.fracssm_abi_version() == 1
+    assert lib.fracssm_abi_version() == _cabi.ABI_VERSION == 2
     # argument validation happens before any CUDA call, so this runs without a GPU
     rc = lib.fracssm_chunk_cumsum(None, 0, 0, 0, None, None, 1, 8, 0, 4, None)
     assert rc == 1

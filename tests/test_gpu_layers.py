@@ -297,3 +297,29 @@ def test_fused_layer_path_head_sharded_emulation(shards):
     for gated, ss, cols in parts:
         y = scan_layer_norm(gated, ss, w[cols], R, 1e-6, sumsq=total, norm_width=H * R)
         torch.testing.assert_close(y.float(), y_full[..., cols].float(), rtol=1e-2, atol=1e-3)
+
+
+def test_frac_compute_scan_params_does_not_synchronise():
+    """The drop-in entry point takes the two scalar gate parameters as device tensors, like the
+    reference (its layers/compute_params.py:199-202): no host read, so no synchronisation."""
+    from frac_ssm_b200.layers import frac_compute_scan_params
+    H, R, M, hidden = 2, 64, 128, 96
+    torch.manual_seed(5)
+    cfg = types.SimpleNamespace(frac_dt_min=1e-4, frac_dt_max=1.0, frac_alpha_min=0.2, frac_alpha_max=0.95,
+                                frac_lambda_min=0.25, frac_lambda_max=4.0)
+    mixer = types.SimpleNamespace(
+        dyn_proj=torch.nn.Linear(hidden, 3 * H).cuda().bfloat16(), rw_proj=torch.nn.Linear(H * R, 2 * H * M, bias=False).cuda().bfloat16(),
+        dt_bias=torch.randn(H, device="cuda") - 2.0, read_residual_logit=torch.nn.Parameter(torch.tensor([-2.0], device="cuda")),
+        write_residual_scale=torch.nn.Parameter(torch.tensor([-1.1], device="cuda")),
+        base_log_tau=torch.linspace(0.0, 11.09, M, device="cuda"), num_heads=H, head_dim=R, num_modes=M, read_temp=1.0, config=cfg)
+    x = torch.randn(2, 40, hidden, device="cuda").bfloat16()
+    x_conv = torch.randn(2, 40, H * R, device="cuda").bfloat16()
+    with torch.no_grad():
+        frac_compute_scan_params(mixer, x_conv, x)            # warm-up: library load, cuBLAS handles
+        torch.cuda.synchronize()
+        torch.cuda.set_sync_debug_mode("error")
+        try:
+            u, c, kappa, rho = frac_compute_scan_params(mixer, x_conv, x)
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+    assert u.shape == (2 * H, 40, R) and rho.dtype == torch.float32 and torch.isfinite(c).all()
