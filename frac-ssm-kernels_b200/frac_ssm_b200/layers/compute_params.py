@@ -4,12 +4,13 @@ Interface of `frac_ssm/layers/compute_params.py:583-596`: the two projections st
 GEMMs (`F.linear`), everything after them is one kernel.  Forward only.
 """
 
-from __future__ import annotations
+from typing import Optional, Tuple
 
 import torch
 import torch.nn.functional as F
 
 from .. import _cabi as C
+from ..ops.b200.stages import _op
 
 
 def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, read_residual_logit,
@@ -29,25 +30,41 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
     assert rw.shape == (B, L, 2 * H * M), "rw shape must be (B, L, 2*H*M)"
     assert x_conv.shape == (B, L, H * R), "x_conv shape must be (B, L, H*R)"
     dev = x_conv.device
-    dyn, rw, x_conv = C.rows(dyn), C.rows(rw), C.rows(x_conv)
     mask = None
     if attention_mask is not None:
         assert attention_mask.shape == (B, L), "attention_mask shape must be (B, L)"
         mask = attention_mask.to(device=dev, dtype=torch.float32)
+
+    def scalar(v):
+        if torch.is_tensor(v):
+            return v.detach().to(device=dev, dtype=torch.float32).reshape(-1)[:1].contiguous()
+        return torch.full((1,), float(v), device=dev, dtype=torch.float32)
+
+    u, c, kappa, rho = _compute_params_op(
+        dyn, rw, x_conv, mask, dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous(),
+        scalar(read_residual_logit), scalar(write_residual_scale),
+        base_log_tau.detach().to(device=dev, dtype=torch.float32).contiguous(), H, R, M, float(read_temp),
+        float(dt_min), float(dt_max), float(alpha_min), float(alpha_max), float(lambda_min), float(lambda_max),
+        coeff_dtype)
+    return u, c, kappa, rho
+
+
+# a torch custom op with a shape-only implementation (torch.compile(fullgraph=True)); forward only
+@_op("compute_params")
+def _compute_params_op(dyn: torch.Tensor, rw: torch.Tensor, x_conv: torch.Tensor, mask: Optional[torch.Tensor],
+                       dtb: torch.Tensor, rlog: torch.Tensor, wlog: torch.Tensor, ltau: torch.Tensor, H: int, R: int,
+                       M: int, read_temp: float, dt_min: float, dt_max: float, alpha_min: float, alpha_max: float,
+                       lambda_min: float, lambda_max: float, coeff_dtype: torch.dtype
+                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    B, L, _ = x_conv.shape
+    dev = x_conv.device
+    dyn, rw, x_conv = C.rows(dyn), C.rows(rw), C.rows(x_conv)
     u = torch.empty(B * H, L, R, device=dev, dtype=x_conv.dtype)
     c = torch.empty(B * H, L, M, device=dev, dtype=coeff_dtype)
     kappa = torch.empty_like(c)
     rho = torch.empty(B * H, L, M, device=dev, dtype=torch.float32)
     if B == 0 or L == 0:
         return u, c, kappa, rho
-    def scalar(v):
-        if torch.is_tensor(v):
-            return v.detach().to(device=dev, dtype=torch.float32).reshape(-1)[:1].contiguous()
-        return torch.full((1,), float(v), device=dev, dtype=torch.float32)
-
-    rlog, wlog = scalar(read_residual_logit), scalar(write_residual_scale)
-    dtb = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
-    ltau = base_log_tau.detach().to(device=dev, dtype=torch.float32).contiguous()
     with C.trace("frac_compute_scan_params"), torch.cuda.device(dev):
         C.check(C.lib().fracssm_compute_params(
             C.ptr(dyn), C.dt(dyn), dyn.stride(0), dyn.stride(1), C.ptr(rw), C.dt(rw), rw.stride(0),
@@ -58,6 +75,16 @@ def compute_params_from_projections(dyn, rw, x_conv, attention_mask, dt_bias, re
             float(lambda_min), float(lambda_max), C.ptr(u), C.ptr(c), C.ptr(kappa), C.dt(c), C.ptr(rho),
             B, L, H, R, M, C.stream_of(x_conv)), "compute_params")
     return u, c, kappa, rho
+
+
+@_compute_params_op.register_fake
+def _(dyn, rw, x_conv, mask, dtb, rlog, wlog, ltau, H, R, M, read_temp, dt_min, dt_max, alpha_min, alpha_max,
+      lambda_min, lambda_max, coeff_dtype):
+    B, L, _ = x_conv.shape
+    dev = x_conv.device
+    c = torch.empty(B * H, L, M, device=dev, dtype=coeff_dtype)
+    return (torch.empty(B * H, L, R, device=dev, dtype=x_conv.dtype), c, torch.empty_like(c),
+            torch.empty(B * H, L, M, device=dev, dtype=torch.float32))
 
 
 def frac_compute_scan_params(model, x_conv, x, attention_mask=None):

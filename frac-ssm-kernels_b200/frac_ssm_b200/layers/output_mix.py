@@ -2,11 +2,10 @@
 (interface of `frac_ssm/layers/output_mix.py:232-243`), and the fused epilogue that also
 applies the gated RMSNorm (`frac_ssm/models/modeling_frac.py:213-214`).  Forward only."""
 
-from __future__ import annotations
-
 import torch
 
 from .. import _cabi as C
+from ..ops.b200.stages import _op
 
 
 def skip_mix(mixed_flat, x_conv, D, num_heads, head_dim, out_dtype=None):
@@ -18,8 +17,16 @@ def skip_mix(mixed_flat, x_conv, D, num_heads, head_dim, out_dtype=None):
     assert HR == H * R, "x_conv last dim must be num_heads * head_dim"
     assert mixed_flat.shape == (B * H, L, R), "mixed_flat shape must be (B*H, L, R)"
     out_dtype = x_conv.dtype if out_dtype is None else out_dtype
-    mixed_flat, x_conv = C.rows(mixed_flat), C.rows(x_conv)
     Df = D.detach().to(device=x_conv.device, dtype=torch.float32).contiguous()
+    return _skip_mix_op(mixed_flat, x_conv, Df, H, R, out_dtype)
+
+
+# the launches below are torch custom ops with shape-only implementations (torch.compile(fullgraph=True))
+@_op("skip_mix")
+def _skip_mix_op(mixed_flat: torch.Tensor, x_conv: torch.Tensor, Df: torch.Tensor, H: int, R: int,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    B, L, HR = x_conv.shape
+    mixed_flat, x_conv = C.rows(mixed_flat), C.rows(x_conv)
     out = torch.empty(B, L, HR, device=x_conv.device, dtype=out_dtype)
     if B == 0 or L == 0:
         return out
@@ -29,6 +36,11 @@ def skip_mix(mixed_flat, x_conv, D, num_heads, head_dim, out_dtype=None):
             C.ptr(x_conv), C.dt(x_conv), x_conv.stride(0), x_conv.stride(1), C.ptr(Df), C.ptr(out),
             C.dt(out), B, L, H, R, C.stream_of(x_conv)), "skip_mix")
     return out
+
+
+@_skip_mix_op.register_fake
+def _(mixed_flat, x_conv, Df, H, R, out_dtype):
+    return torch.empty(x_conv.shape, device=x_conv.device, dtype=out_dtype)
 
 
 def frac_skip_mix(model, mixed_flat, x_conv, out_dtype=None):
@@ -44,9 +56,15 @@ def scan_epilogue(h, x_conv, gate, D, weight, num_heads, head_dim, eps=1e-6, gat
     B, L, HR = x_conv.shape
     assert HR == H * R and gate.shape == x_conv.shape and h.shape == (B * H, L, R)
     assert gate.dtype == x_conv.dtype, "gate and x_conv must have the same dtype"
-    h, x_conv, gate = C.rows(h), C.rows(x_conv), C.rows(gate)
     Df = D.detach().to(device=x_conv.device, dtype=torch.float32).contiguous()
-    w = weight.detach().contiguous()
+    return _scan_epilogue_op(h, x_conv, gate, Df, weight.detach().contiguous(), H, R, float(eps), float(gate_bias))
+
+
+@_op("scan_epilogue")
+def _scan_epilogue_op(h: torch.Tensor, x_conv: torch.Tensor, gate: torch.Tensor, Df: torch.Tensor, w: torch.Tensor,
+                      H: int, R: int, eps: float, gate_bias: float) -> torch.Tensor:
+    B, L, HR = x_conv.shape
+    h, x_conv, gate = C.rows(h), C.rows(x_conv), C.rows(gate)
     y = torch.empty(B, L, HR, device=x_conv.device, dtype=x_conv.dtype)
     if B == 0 or L == 0:
         return y
@@ -57,6 +75,11 @@ def scan_epilogue(h, x_conv, gate, D, weight, num_heads, head_dim, eps=1e-6, gat
             C.ptr(w), C.dt(w), float(gate_bias), float(eps), C.ptr(y), B, L, H, R,
             C.stream_of(x_conv)), "scan_epilogue")
     return y
+
+
+@_scan_epilogue_op.register_fake
+def _(h, x_conv, gate, Df, w, H, R, eps, gate_bias):
+    return torch.empty_like(x_conv)
 
 
 def _epilogue_args(h, x_conv, gate, D, num_heads, head_dim):

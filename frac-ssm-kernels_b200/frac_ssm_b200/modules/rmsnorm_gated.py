@@ -1,12 +1,13 @@
 """Gated RMSNorm on the B200 CUDA extension (interface of
 `frac_ssm/modules/rmsnorm_gated.py:65-99,292-299`).  Forward only."""
 
-from __future__ import annotations
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
 
 from .. import _cabi as C
+from ..ops.b200.stages import _op
 
 
 def rmsnorm_gated_fwd(hidden_states, weight, gate=None, eps=1e-6):
@@ -26,7 +27,15 @@ def rmsnorm_gated_fwd(hidden_states, weight, gate=None, eps=1e-6):
             g = g.contiguous()
     w = weight.detach().contiguous()
     assert w.numel() == D, "weight must have hidden_size elements"
-    rows = x.shape[0]
+    y, rstd = _rmsnorm_gated_op(x, g, w, float(eps))
+    return y.reshape(shape), rstd.reshape(shape[:-1])
+
+
+# a torch custom op with a shape-only implementation, so the norm can sit inside torch.compile(fullgraph=True)
+@_op("rmsnorm_gated")
+def _rmsnorm_gated_op(x: torch.Tensor, g: Optional[torch.Tensor], w: torch.Tensor,
+                      eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    rows, D = x.shape
     y = torch.empty(rows, D, device=x.device, dtype=x.dtype)
     rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
     if rows > 0:
@@ -34,7 +43,12 @@ def rmsnorm_gated_fwd(hidden_states, weight, gate=None, eps=1e-6):
             C.check(C.lib().fracssm_rmsnorm_gated(
                 C.ptr(x), x.stride(0), C.ptr(g), 0 if g is None else g.stride(0), C.dt(x), C.ptr(w),
                 C.dt(w), float(eps), C.ptr(y), C.ptr(rstd), rows, D, C.stream_of(x)), "rmsnorm_gated")
-    return y.reshape(shape), rstd.reshape(shape[:-1])
+    return y, rstd
+
+
+@_rmsnorm_gated_op.register_fake
+def _(x, g, w, eps):
+    return torch.empty_like(x), torch.empty(x.shape[0], device=x.device, dtype=torch.float32)
 
 
 class MambaRMSNormGated(nn.Module):

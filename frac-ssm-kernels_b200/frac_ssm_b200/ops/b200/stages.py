@@ -7,12 +7,27 @@ of quorbix/frac-ssm-kernels (`frac_ssm/ops/triton/chunk_cumsum.py:189`,
 outputs are freshly allocated on the input device, kernels run on the current stream.
 """
 
-from __future__ import annotations
-
+from typing import Optional, Tuple
 
 import torch
 
 from ... import _cabi as C
+
+# Every launch below is a torch custom op with a shape-only "fake" implementation, so the stage ops
+# can sit inside torch.compile(fullgraph=True) as the reference's do
+# (frac_ssm/ops/triton/chunk_state.py:243-302).  Forward only: asking for gradients raises.
+
+
+def _no_backward(ctx, *grads):
+    raise NotImplementedError("frac_ssm_b200 implements the forward pass only")
+
+
+def _op(name):
+    def wrap(fn):
+        op = torch.library.custom_op(f"frac_ssm_b200::{name}", mutates_args=())(fn)
+        op.register_autograd(_no_backward)
+        return op
+    return wrap
 
 
 def _nchunks(L: int, T: int) -> int:
@@ -31,6 +46,12 @@ def chunk_cumsum(log_rho, chunk_size):
 
 
 def _cumsum(src, chunk_size, src_is_rho):
+    lcr, cd = _cumsum_op(src, chunk_size, bool(src_is_rho))
+    return lcr, cd
+
+
+@_op("chunk_cumsum")
+def _cumsum_op(src: torch.Tensor, chunk_size: int, src_is_rho: bool) -> Tuple[torch.Tensor, torch.Tensor]:
     B, L, M = src.shape
     N = _nchunks(L, chunk_size)
     src = C.rows(src)
@@ -43,6 +64,13 @@ def _cumsum(src, chunk_size, src_is_rho):
                                              C.ptr(lcr), C.ptr(cd), B, L, M, chunk_size,
                                              C.stream_of(src)), "chunk_cumsum")
     return lcr, cd
+
+
+@_cumsum_op.register_fake
+def _(src, chunk_size, src_is_rho):
+    B, L, M = src.shape
+    return (torch.empty(B, L, M, device=src.device, dtype=torch.float32),
+            torch.empty(B, _nchunks(L, chunk_size), M, device=src.device, dtype=torch.float32))
 
 
 def chunk_state(u, kappa, log_cum_rho, chunk_size, state_fp32=True):
@@ -60,8 +88,17 @@ def chunk_state(u, kappa, log_cum_rho, chunk_size, state_fp32=True):
     N = _nchunks(L, chunk_size)
     sdt = torch.float32 if state_fp32 else u.dtype
     assert sdt in (torch.float32, torch.bfloat16), f"states dtype must be float32 or bfloat16, got {sdt}"
+    return _chunk_state_op(u, kappa, log_cum_rho, chunk_size, sdt == torch.float32)
+
+
+@_op("chunk_state")
+def _chunk_state_op(u: torch.Tensor, kappa: torch.Tensor, log_cum_rho: torch.Tensor, chunk_size: int,
+                    fp32: bool) -> torch.Tensor:
+    B, L, R = u.shape
+    M = kappa.shape[-1]
+    N = _nchunks(L, chunk_size)
     u, kappa, g = C.rows(u), C.rows(kappa), C.rows(log_cum_rho)
-    states = torch.empty(B, N, R, M, device=u.device, dtype=sdt)
+    states = torch.empty(B, N, R, M, device=u.device, dtype=torch.float32 if fp32 else torch.bfloat16)
     if B == 0 or L == 0:
         return states
     with torch.cuda.device(u.device):
@@ -70,6 +107,13 @@ def chunk_state(u, kappa, log_cum_rho, chunk_size, state_fp32=True):
             kappa.stride(1), C.ptr(g), g.stride(0), g.stride(1), C.ptr(states), C.dt(states),
             B, L, R, M, chunk_size, C.stream_of(u)), "chunk_state")
     return states
+
+
+@_chunk_state_op.register_fake
+def _(u, kappa, log_cum_rho, chunk_size, fp32):
+    B, L, R = u.shape
+    return torch.empty(B, _nchunks(L, chunk_size), R, kappa.shape[-1], device=u.device,
+                       dtype=torch.float32 if fp32 else torch.bfloat16)
 
 
 def state_passing(states, chunk_decay, initial_state=None):
@@ -95,6 +139,16 @@ def state_passing(states, chunk_decay, initial_state=None):
 
 
 def _state_passing(states, chunk_decay, initial_state, acc_dtype, final_dtype):
+    acc, fin = _state_passing_op(states, chunk_decay, initial_state, acc_dtype == torch.float32,
+                                 final_dtype == torch.float32)
+    return acc, fin
+
+
+@_op("state_passing")
+def _state_passing_op(states: torch.Tensor, chunk_decay: torch.Tensor, initial_state: Optional[torch.Tensor],
+                      acc_fp32: bool, final_fp32: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    acc_dtype = torch.float32 if acc_fp32 else torch.bfloat16
+    final_dtype = torch.float32 if final_fp32 else torch.bfloat16
     B, N, R, M = states.shape
     states, chunk_decay = states.contiguous(), chunk_decay.contiguous()
     init = None if initial_state is None else initial_state.contiguous()
@@ -108,6 +162,13 @@ def _state_passing(states, chunk_decay, initial_state, acc_dtype, final_dtype):
             C.F32 if init is None else C.dt(init), C.ptr(acc), C.dt(acc), C.ptr(fin), C.dt(fin),
             B, N, R, M, C.stream_of(states)), "state_passing")
     return acc, fin
+
+
+@_state_passing_op.register_fake
+def _(states, chunk_decay, initial_state, acc_fp32, final_fp32):
+    B, N, R, M = states.shape
+    return (torch.empty(B, N, R, M, device=states.device, dtype=torch.float32 if acc_fp32 else torch.bfloat16),
+            torch.empty(B, R, M, device=states.device, dtype=torch.float32 if final_fp32 else torch.bfloat16))
 
 
 def chunk_w(c, kappa, log_cum_rho, chunk_size):
@@ -132,6 +193,12 @@ def chunk_w(c, kappa, log_cum_rho, chunk_size):
     assert chunk_size > 0 and chunk_size % 32 == 0, (
         f"chunk_size must be a positive multiple of 32, got {chunk_size}"
     )
+    return _chunk_w_op(c, kappa, log_cum_rho, chunk_size)
+
+
+@_op("chunk_w")
+def _chunk_w_op(c: torch.Tensor, kappa: torch.Tensor, log_cum_rho: torch.Tensor, chunk_size: int) -> torch.Tensor:
+    M = c.shape[-1]
     B, L, _ = log_cum_rho.shape
     N = _nchunks(L, chunk_size)
     c, kappa, g = C.rows(c), C.rows(kappa), C.rows(log_cum_rho)
@@ -144,6 +211,12 @@ def chunk_w(c, kappa, log_cum_rho, chunk_size):
             kappa.stride(1), C.ptr(g), g.stride(0), g.stride(1), C.ptr(W), B, L, M, chunk_size,
             C.stream_of(c)), "chunk_w")
     return W
+
+
+@_chunk_w_op.register_fake
+def _(c, kappa, log_cum_rho, chunk_size):
+    B, L, _ = log_cum_rho.shape
+    return torch.empty(B, _nchunks(L, chunk_size), chunk_size, chunk_size, device=c.device, dtype=torch.float32)
 
 
 def chunk_readout(u, c, states_acc, W, log_cum_rho, chunk_size):
@@ -173,6 +246,14 @@ def chunk_readout(u, c, states_acc, W, log_cum_rho, chunk_size):
     assert W.shape == (B, N, chunk_size, chunk_size), (
         "W shape must be (B, nchunks, chunk_size, chunk_size)"
     )
+    return _chunk_readout_op(u, c, states_acc, W, log_cum_rho, chunk_size)
+
+
+@_op("chunk_readout")
+def _chunk_readout_op(u: torch.Tensor, c: torch.Tensor, states_acc: torch.Tensor, W: torch.Tensor,
+                      log_cum_rho: torch.Tensor, chunk_size: int) -> torch.Tensor:
+    B, L, R = u.shape
+    M = c.shape[-1]
     u, c, g = C.rows(u), C.rows(c), C.rows(log_cum_rho)
     states_acc, W = states_acc.contiguous(), W.contiguous()
     h = torch.empty(B, L, R, device=u.device, dtype=u.dtype)
@@ -184,6 +265,11 @@ def chunk_readout(u, c, states_acc, W, log_cum_rho, chunk_size):
             C.ptr(states_acc), C.dt(states_acc), C.ptr(W), C.dt(W), C.ptr(g), g.stride(0),
             g.stride(1), C.ptr(h), B, L, R, M, chunk_size, C.stream_of(u)), "chunk_readout")
     return h
+
+
+@_chunk_readout_op.register_fake
+def _(u, c, states_acc, W, log_cum_rho, chunk_size):
+    return torch.empty_like(u)
 
 
 def chunk_fused_readout(u, c, kappa, states_acc, log_cum_rho, chunk_size):
@@ -212,6 +298,14 @@ def chunk_fused_readout(u, c, kappa, states_acc, log_cum_rho, chunk_size):
     assert c.shape == (B, L, M) and kappa.shape == (B, L, M), "c and kappa shapes must match (B, L, M)"
     assert log_cum_rho.shape == (B, L, M), "log_cum_rho shape must match (B, L, M)"
     assert states_acc.shape == (B, N, R, M), "states_acc shape must be (B, nchunks, R, M)"
+    return _chunk_fused_readout_op(u, c, kappa, states_acc, log_cum_rho, chunk_size)
+
+
+@_op("chunk_fused_readout")
+def _chunk_fused_readout_op(u: torch.Tensor, c: torch.Tensor, kappa: torch.Tensor, states_acc: torch.Tensor,
+                            log_cum_rho: torch.Tensor, chunk_size: int) -> torch.Tensor:
+    B, L, R = u.shape
+    M = c.shape[-1]
     u, c, kappa, g = C.rows(u), C.rows(c), C.rows(kappa), C.rows(log_cum_rho)
     states_acc = states_acc.contiguous()
     h = torch.empty(B, L, R, device=u.device, dtype=u.dtype)
@@ -224,6 +318,11 @@ def chunk_fused_readout(u, c, kappa, states_acc, log_cum_rho, chunk_size):
             C.dt(states_acc), C.ptr(g), g.stride(0), g.stride(1), C.ptr(h), B, L, R, M, chunk_size,
             C.stream_of(u)), "chunk_fused_readout")
     return h
+
+
+@_chunk_fused_readout_op.register_fake
+def _(u, c, kappa, states_acc, log_cum_rho, chunk_size):
+    return torch.empty_like(u)
 
 
 __all__ = ["chunk_cumsum", "chunk_state", "state_passing", "chunk_w", "chunk_readout",

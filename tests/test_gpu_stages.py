@@ -171,3 +171,36 @@ def test_zero_batch_shapes(ops):
     assert acc.shape == (0, 2, 8, 16) and fin.shape == (0, 8, 16)
     assert ops.chunk_w(z, z, z, 32).shape == (0, 2, 32, 32)
     assert ops.chunk_fused_readout(u, z.bfloat16(), z.bfloat16(), acc, z, 32).shape == (0, 64, 8)
+
+
+def test_stage_and_layer_ops_inside_torch_compile_fullgraph():
+    """Every stage op, the layer ops and the gated norm are registered custom ops with shape-only
+    implementations, so a graph around them compiles without breaks (the reference checks the same
+    for its ops, tests/test_frac_scan.py:249-262)."""
+    from frac_ssm_b200 import ops
+    from frac_ssm_b200.layers import scan_epilogue, skip_mix
+    from frac_ssm_b200.modules import rmsnorm_gated_fwd
+    B, L, R, M, T, H = 4, 96, 64, 16, 32, 2
+    u, c, kappa, rho, init = (t.cuda() for t in O.scan_inputs(B, L, R, M, dtype=torch.float32, gen="model_like", seed=2))
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(B // H, L, H * R, generator=g).cuda()
+    z = torch.randn(B // H, L, H * R, generator=g).cuda()
+    D = torch.randn(H, R, generator=g).cuda()
+    w = torch.ones(H * R).cuda()
+
+    def fn(u, c, kappa, rho, init, x, z):
+        lcr, cd = ops.chunk_cumsum(torch.log(rho.clamp(min=1e-6)), T)
+        st = ops.chunk_state(u, kappa, lcr, T)
+        acc, fin = ops.state_passing(st, cd, init)
+        W = ops.chunk_w(c, kappa, lcr, T)
+        h1 = ops.chunk_readout(u, c, acc, W, lcr, T)
+        h2 = ops.chunk_fused_readout(u, c, kappa, acc, lcr, T)
+        mixed = skip_mix(h1, x, D, H, R)
+        y1, _ = rmsnorm_gated_fwd(mixed, w, z, 1e-6)
+        y2 = scan_epilogue(h2, x, z, D, w, H, R, 1e-6)
+        return h1 + 0.0, y1 * 1.0, y2 * 1.0, fin + 0.0
+
+    eager = fn(u, c, kappa, rho, init, x, z)
+    compiled = torch.compile(fn, fullgraph=True)(u, c, kappa, rho, init, x, z)
+    for a, b in zip(compiled, eager):
+        torch.testing.assert_close(a, b)
