@@ -560,6 +560,58 @@ def run_model_workload(args, rank, world, dev, dist):
         dist.destroy_process_group()
 
 
+def run_stages_workload(args, rank, world, dev, dist):
+    """Each of the reference's five stage kernels (and the fused W+readout) timed alone on the
+    config-1 scan shape, with the bytes it must move and the fraction of the HBM peak it reaches.
+    The stages are the fallback route of frac_scan; the single-pass kernel replaces them on the hot
+    path, so this line explains the fallback, it is not the benchmark."""
+    from frac_ssm_b200.ops.b200 import stages
+    B, L, R, M, T = CFG["batch"] * CFG["H"], (args.seq_len or CFG["L"]), CFG["R"], CFG["M"], CFG["T"]
+    N = (L + T - 1) // T
+    u, c, kappa, rho, init = scan_inputs_device(B, L, R, M, dev, seed=11 + rank)
+    log_rho = torch.log(rho)
+    lcr, cd = stages.chunk_cumsum(log_rho, T)
+    states = stages.chunk_state(u, kappa, lcr, T)
+    acc, fin = stages.state_passing(states, cd, init)
+    peak, peak_kind = measured_peak_gbs()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    f4, b2 = 4, 2
+    cases = [
+        ("chunk_cumsum", lambda: stages.chunk_cumsum(log_rho, T), B * L * M * f4 * 2 + B * N * M * f4),
+        ("chunk_state", lambda: stages.chunk_state(u, kappa, lcr, T),
+         B * L * (R * b2 + M * b2 + M * f4) + B * N * R * M * f4),
+        ("state_passing", lambda: stages.state_passing(states, cd, init),
+         2 * B * N * R * M * f4 + B * N * M * f4 + 2 * B * R * M * f4),
+        ("chunk_w", lambda: stages.chunk_w(c, kappa, lcr, T), B * L * (2 * M * b2 + M * f4) + B * N * T * T * f4),
+        ("chunk_fused_readout", lambda: stages.chunk_fused_readout(u, c, kappa, acc, lcr, T),
+         B * L * (2 * R * b2 + 2 * M * b2 + M * f4) + B * N * R * M * f4),
+    ]
+    W = stages.chunk_w(c, kappa, lcr, T) if B * N * T * T * 4 <= 16 << 30 else None
+    if W is not None:
+        cases.append(("chunk_readout", lambda: stages.chunk_readout(u, c, acc, W, lcr, T),
+                      B * L * (2 * R * b2 + M * b2 + M * f4) + B * N * (R * M + T * T) * f4))
+    out = {}
+    total_ms = 0.0
+    for name, fn, nbytes in cases:
+        ms = _timed(fn, steps, warmup, dev, dist)
+        out[name] = {"ms": round(ms, 4), "bytes": nbytes, "gbs": round(nbytes / ms / 1e6, 1),
+                     "frac_of_hbm_peak": round(nbytes / ms / 1e6 / peak, 3)}
+        if name in ("chunk_cumsum", "chunk_state", "state_passing", "chunk_fused_readout"):
+            total_ms += ms
+    if rank == 0:
+        print(json.dumps({"metric": "stage kernels, each timed alone", "workload": "stages",
+                          "value": world * B * L / (total_ms * 1e-3), "unit": "tokens/s",
+                          "note": "value = (batch x head) tokens over the sum of the four stages of the staged route "
+                                  "(cumsum, state, passing, fused readout)",
+                          "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(total_ms, 4),
+                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                          "peak_gbs": peak, "peak_kind": peak_kind, "stages": out,
+                          "config": {"workload": f"stage kernels on the config-1 scan shape: {B} (batch, head) rows "
+                                                 f"x L {L}, R {R}, M {M}, chunk {T}"}}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def workload_config(n):
     return {"workload": "config 1: single-layer frac_scan forward + skip-mix/gated-RMSNorm epilogue, "
                         "batch 8 x 24 heads, L 8192, R 64, M 128, chunk 256, per GPU",
@@ -596,7 +648,7 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "staged", "fused"])
     ap.add_argument("--seq-len", type=int, default=None,
                     help="override L (smaller cases for profiler captures; not the benchmark workload)")
-    ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads", "model"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "seq", "heads", "model", "stages"],
                     help="layer: config 1 per GPU (the benchmark); seq: config 3, one sequence of 1,048,576 "
                          "tokens x 24 heads split over the ranks; heads: config 4, one layer's 64 heads spread over the "
                          "ranks; model: config 2, prefill of the 24-layer model, batch 16 x 4096 "
@@ -651,6 +703,9 @@ def main():
         return
     if args.workload == "model":
         run_model_workload(args, rank, world, dev, dist)
+        return
+    if args.workload == "stages":
+        run_stages_workload(args, rank, world, dev, dist)
         return
     if args.workload == "seq":
         run_seq_workload(args, rank, world, dev, dist)

@@ -27,7 +27,8 @@ def _golden(golden_dir, name):
 
 @pytest.mark.parametrize("gen", GENS)
 @pytest.mark.parametrize("B,L,M,T", [(1, 1, 8, 16), (3, 70, 8, 16), (2, 4001, 16, 64),
-                                     (17, 512, 128, 256), (2, 1000, 48, 128), (1, 2048, 5, 1024)])
+                                     (17, 512, 128, 256), (2, 1000, 48, 128), (1, 2048, 5, 1024),
+                                     (2, 700, 200, 256), (1, 300, 132, 32)])
 def test_chunk_cumsum(ops, gen, B, L, M, T):
     lr = O.LOG_RHO_GENS[gen](B, L, M, seed=1)
     lcr, cd = ops.chunk_cumsum(lr.cuda(), T)
@@ -52,6 +53,16 @@ def test_chunk_cumsum_reconstructs_full_sum(ops):
 def test_chunk_cumsum_noncontiguous_rows(ops):
     base = O.uniform_log_rho(2, 100, 24, seed=3).cuda()
     view = base[:, :, :16]          # padded row stride
+    lcr, cd = ops.chunk_cumsum(view, 32)
+    lcr_pt, cd_pt = O.chunk_cumsum(view.cpu().contiguous(), 32)
+    close(lcr, lcr_pt, **TOL_F32)
+    close(cd, cd_pt, **TOL_F32)
+
+
+def test_chunk_cumsum_unaligned_view(ops):
+    """A source that starts 4 bytes off a 16-byte boundary takes the element-wise kernel."""
+    base = O.uniform_log_rho(2, 100, 20, seed=5).cuda()
+    view = base[:, :, 1:17]
     lcr, cd = ops.chunk_cumsum(view, 32)
     lcr_pt, cd_pt = O.chunk_cumsum(view.cpu().contiguous(), 32)
     close(lcr, lcr_pt, **TOL_F32)
