@@ -343,8 +343,11 @@ scan_epilogue_kernel(const void *__restrict__ h, int h_dt, int64_t h_sb, int64_t
 }
 
 // bf16 fast path of the epilogue: one block per (b, l) row, 8 elements (16 bytes) per thread held
-// in registers, so every tensor is read once and written once.
-
+// in registers, so every tensor is read once and written once.  The kernel is bound by its
+// instruction count as much as by memory, hence the fast-math gate (silu(z) = z / (1 + e^-z) with
+// the approximate exponential and division: about 2 ulp, the output is bf16) and the norm weight
+// read as one or two 16-byte pieces (WVEC 1: bf16, 2: f32; 0: element by element, any type).
+template <int WVEC>
 __global__ void __launch_bounds__(1024)
 scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int64_t h_sl,
                           const __nv_bfloat16 *__restrict__ x, int64_t x_sb, int64_t x_sl,
@@ -353,24 +356,25 @@ scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int
                           float gate_bias, float eps, __nv_bfloat16 *__restrict__ y, int64_t L, int64_t H,
                           int64_t R, int mode, float *__restrict__ sumsq, int64_t norm_width) {
   __shared__ float red[32];
-  const int64_t HR = H * R;
-  const int64_t row = blockIdx.x, b = row / L, l = row % L;
-  const int64_t j = (int64_t)threadIdx.x * 8;
+  const int HR = (int)(H * R);
+  const int64_t row = blockIdx.x;   // fewer than 2^31 rows (the grid's x extent), so the row splits in 32 bits
+  const int64_t b = (int)blockIdx.x / (int)L, l = row - b * L;
+  const int j = (int)threadIdx.x * 8;   // < 8192
   float v[8];
   float ss = 0.f;
   const bool live = j < HR;
   if (live) {
-    const int64_t hh = j / R, r = j % R;
+    const int hh = j / (int)R, r = j - hh * (int)R;
     float hv[8], xv[8], zv[8];
     unpack8(__ldcs(reinterpret_cast<const uint4 *>(h + (b * H + hh) * h_sb + l * h_sl + r)), hv);
     unpack8(__ldcs(reinterpret_cast<const uint4 *>(x + b * x_sb + l * x_sl + j)), xv);
     unpack8(__ldcs(reinterpret_cast<const uint4 *>(gate + b * g_sb + l * g_sl + j)), zv);
-    const float4 d0 = *reinterpret_cast<const float4 *>(Dp + j), d1 = *reinterpret_cast<const float4 *>(Dp + j + 4);
+    const float4 d0 = __ldg(reinterpret_cast<const float4 *>(Dp + j)), d1 = __ldg(reinterpret_cast<const float4 *>(Dp + j + 4));
     const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float z = zv[i] + gate_bias;
-      v[i] = (hv[i] + xv[i] * dv[i]) * (z * sigmoidf_(z));
+      v[i] = fmaf(xv[i], dv[i], hv[i]) * __fdividef(z, 1.f + __expf(-z));
       ss = fmaf(v[i], v[i], ss);
     }
   }
@@ -385,11 +389,21 @@ scan_epilogue_bf16_kernel(const __nv_bfloat16 *__restrict__ h, int64_t h_sb, int
   }
   const float rs = rsqrtf(ss / (float)norm_width + eps);
   if (live) {
+    float wv[8];
+    if (WVEC == 1) {
+      unpack8(__ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(w) + j)), wv);
+    } else if (WVEC == 2) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(w) + j));
+      const float4 w1 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(w) + j + 4));
+      wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wv[i] = ld_f32(w, j + i, w_dt);
+    }
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i] * rs * ld_f32(w, j + 2 * i, w_dt),
-                                                     v[2 * i + 1] * rs * ld_f32(w, j + 2 * i + 1, w_dt));
+      const __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i] * rs * wv[2 * i], v[2 * i + 1] * rs * wv[2 * i + 1]);
       o[i] = *reinterpret_cast<const uint32_t *>(&t);
     }
     __stcs(reinterpret_cast<uint4 *>(y + row * HR + j), make_uint4(o[0], o[1], o[2], o[3]));
@@ -546,10 +560,16 @@ int scan_epilogue_launch(const char *who, const void *h, int h_dtype, int64_t h_
       al16(gate) && al16(y) && al16(D) && h_sb % 8 == 0 && h_sl % 8 == 0 && x_sb % 8 == 0 && x_sl % 8 == 0 &&
       g_sb % 8 == 0 && g_sl % 8 == 0) {
     const unsigned threads = (unsigned)(((HR / 8) + 31) / 32 * 32);
-    scan_epilogue_bf16_kernel<<<(unsigned)(Bt * L), threads, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const __nv_bfloat16 *>(h), h_sb, h_sl, reinterpret_cast<const __nv_bfloat16 *>(x_conv),
-        x_sb, x_sl, reinterpret_cast<const __nv_bfloat16 *>(gate), g_sb, g_sl, D, weight, w_dtype, gate_bias,
-        eps, reinterpret_cast<__nv_bfloat16 *>(y), L, H, R, mode, sumsq, norm_width);
+    const int wvec = (mode == kEpiloguePartial || !al16(weight)) ? 0 : w_dtype == FRACSSM_BF16 ? 1 : w_dtype == FRACSSM_F32 ? 2 : 0;
+#define FRACSSM_EPILOGUE(WV)                                                                                       \
+  scan_epilogue_bf16_kernel<WV><<<(unsigned)(Bt * L), threads, 0, (cudaStream_t)stream>>>(                         \
+      reinterpret_cast<const __nv_bfloat16 *>(h), h_sb, h_sl, reinterpret_cast<const __nv_bfloat16 *>(x_conv),     \
+      x_sb, x_sl, reinterpret_cast<const __nv_bfloat16 *>(gate), g_sb, g_sl, D, weight, w_dtype, gate_bias, eps,   \
+      reinterpret_cast<__nv_bfloat16 *>(y), L, H, R, mode, sumsq, norm_width)
+    if (wvec == 1) FRACSSM_EPILOGUE(1);
+    else if (wvec == 2) FRACSSM_EPILOGUE(2);
+    else FRACSSM_EPILOGUE(0);
+#undef FRACSSM_EPILOGUE
     return check_launch(who);
   }
   scan_epilogue_kernel<<<(unsigned)(Bt * L), 256, 0, (cudaStream_t)stream>>>(

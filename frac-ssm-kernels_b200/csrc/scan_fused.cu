@@ -154,6 +154,36 @@ __device__ __forceinline__ void load_tok(RawHalf<CKF32> &raw, const FusedArgs &a
   }
 }
 
+// The same for token rows I and I + 1 of a tile that lies wholly inside the sequence: one element
+// offset for the thread, the rows as immediate byte offsets of the loads.
+template <int OFF>
+__device__ __forceinline__ void ldg_stream_at(f2 &d, const void *p) {
+  asm volatile("ld.global.L1::no_allocate.b64 %0, [%1+%2];" : "=l"(d) : "l"(p), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ void ldg_stream_at(uint32_t &d, const void *p) {
+  asm volatile("ld.global.L1::no_allocate.b32 %0, [%1+%2];" : "=r"(d) : "l"(p), "n"(OFF));
+}
+template <bool CKF32, int I>
+__device__ __forceinline__ void load_tok2(RawHalf<CKF32> &raw, const FusedArgs &a, int bh, int t0, int w, int lane,
+                                          int h) {
+  if (t0 + kTile <= a.L) {
+    constexpr int kCk = CKF32 ? 4 : 2;
+    const int64_t e = (static_cast<int64_t>(bh) * a.L + t0 + 8 * w) * kM + 64 * h + 2 * lane;   // row 0 of the segment
+    const float *rp = a.rho + e;
+    const char *cp = reinterpret_cast<const char *>(a.c) + e * kCk, *kp = reinterpret_cast<const char *>(a.kappa) + e * kCk;
+    ldg_stream_at<I * kM * 4>(raw.r[I], rp);
+    ldg_stream_at<I * kM * kCk>(raw.c[I], cp);
+    ldg_stream_at<I * kM * kCk>(raw.k[I], kp);
+    ldg_stream_at<(I + 1) * kM * 4>(raw.r[I + 1], rp);
+    ldg_stream_at<(I + 1) * kM * kCk>(raw.c[I + 1], cp);
+    ldg_stream_at<(I + 1) * kM * kCk>(raw.k[I + 1], kp);
+    return;
+  }
+  load_tok(raw, a, bh, t0, w, lane, h, I);
+  load_tok(raw, a, bh, t0, w, lane, h, I + 1);
+}
+
 __device__ __forceinline__ f2 floor2(f2 v) {
   float lo, hi;
   un2(v, lo, hi);
@@ -166,7 +196,9 @@ __device__ __forceinline__ void emit_pair(uint32_t rows_s, int i, uint32_t w0) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(w0) : "memory");
 }
 
-template <bool CKF32>
+// CKF32: c and kappa are float32 (else bf16).  LAYER: the output stage applies the skip connection and
+// the gate (its code is kept out of the plain kernel, whose loop is fetched once per tile).
+template <bool CKF32, bool LAYER>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -213,11 +245,19 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
   } else if (w == 17) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+#ifdef FRACSSM_V_PARK_CHAIN
+#define FRACSSM_WAIT(bar, parity)                                  \
+  if (ok) {                                                        \
+    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);      \
+    if (!ok) *failed = 1;                                          \
+  }
+#else
 #define FRACSSM_WAIT(bar, parity)                                  \
   if (ok) {                                                        \
     ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
     if (!ok) *failed = 1;                                          \
   }
+#endif
     // =========================== chain warp ===========================
     // Tickets, the L2 prefetch of the next item, and the hand-over of the state between the tiles of
     // a (batch, head) row: nothing here waits for an MMA, so a row's chain is never held up by them.
@@ -276,11 +316,19 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 #undef FRACSSM_WAIT
   } else if (w == 16) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
+#ifdef FRACSSM_V_PARK_MMA
+#define FRACSSM_WAIT(bar, parity)                                  \
+  if (ok) {                                                        \
+    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);      \
+    if (!ok) *failed = 1;                                          \
+  }
+#else
 #define FRACSSM_WAIT(bar, parity)                                  \
   if (ok) {                                                        \
     ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
     if (!ok) *failed = 1;                                          \
   }
+#endif
     // =========================== MMA warp ===========================
     const uint32_t sb = umma::smem_u32(smem);
     const uint32_t sA0 = sb + kOffA0, sB0 = sb + kOffB0, sY1 = sb + kOffY1, sZ1 = sb + kOffZ1, sY2 = sb + kOffY2,
@@ -293,15 +341,22 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     // Contraction steps s0 .. s1-1 (16 modes or tokens each) of one GEMM piece.  A K-major 128-column
     // tile advances by 32 bytes inside a 64-column atom and by one atom after 4 steps (steps 0..3 are
     // the first half of the modes, 4..7 the second); an MN-major tile by 16 rows (2048 B).
+    // Called by the one elected lane.
+    // The steps run as a real loop (not unrolled): this warp passes through its code once per tile,
+    // so straight-line code would be fetched from beyond the instruction cache every time.
     auto piece = [&](uint32_t d_col, uint32_t a_addr, bool a_mn, uint32_t b_addr, bool b_mn, uint32_t idesc,
                      uint32_t acc_first, uint32_t s0, uint32_t s1) {
-      const uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024);
-      const uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, 1024);
-#pragma unroll
-      for (uint32_t s = s0; s < s1; ++s) {   // s0, s1 are constants at every call: fully unrolled
-        const uint32_t k_step = ((s >> 2) * kAtom + (s & 3) * 32) >> 4, mn_step = (s * 2048) >> 4;
-        umma::mma_ss(tmem + d_col, da + (a_mn ? mn_step : k_step), db + (b_mn ? mn_step : k_step), idesc,
-                     s > s0 ? 1u : acc_first);
+      const uint32_t k0 = ((s0 >> 2) * kAtom + (s0 & 3) * 32) >> 4, mn0 = (s0 * 2048) >> 4;
+      uint64_t da = umma::make_sdesc(a_addr, a_mn ? kAtom : 16, 1024) + (a_mn ? mn0 : k0);
+      uint64_t db = umma::make_sdesc(b_addr, b_mn ? kAtom : 16, 1024) + (b_mn ? mn0 : k0);
+      uint32_t acc = acc_first;
+#pragma unroll 1
+      for (uint32_t s = s0; s < s1; ++s) {
+        umma::mma_ss(tmem + d_col, da, db, idesc, acc);
+        acc = 1u;
+        const uint32_t k_inc = (s & 3) == 3 ? (kAtom - 96) >> 4 : 2u, mn_inc = 2048 >> 4;
+        da += a_mn ? mn_inc : k_inc;
+        db += b_mn ? mn_inc : k_inc;
       }
     };
 
@@ -321,10 +376,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         FRACSSM_WAIT(fA, h);
         FRACSSM_MARK(3, 1 + 4 * h)
         umma::tc_fence_after();
-        if (lane == 0) {
+        if (umma::elect_one()) {
           piece(kColBase, sA0, false, sB0, false, kIdKK128, h, 4 * h, 4 * h + 4);
           umma::mma_commit(cb0);
         }
+        __syncwarp();
         if (h == 0) {
           // the u tile is free once every MMA of the previous tile has finished
           if (n > 0) { FRACSSM_WAIT(barH, n - 1); }
@@ -338,12 +394,13 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         FRACSSM_WAIT(fL, h);
         FRACSSM_MARK(3, 3 + 4 * h)
         umma::tc_fence_after();
-        if (lane == 0) {
+        if (umma::elect_one()) {
           piece(kColL1, sY1, false, sZ1, false, kIdKK128, h, 4 * h, 4 * h + 4);
           umma::mma_commit(cbL);
           piece(kColL2, sY2, false, sZ2, false, kIdKK128, h, 4 * h, 4 * h + 4);
           if (h == 1) umma::mma_commit(cb2);
         }
+        __syncwarp();
         FRACSSM_MARK(3, 4 + 4 * h)
       }
       // Sacc[m,r] = sum_k (Khi + Klo)[k,m] u[k,r]: the tile's own contribution to the state
@@ -355,27 +412,33 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_WAIT(barU, n);
       FRACSSM_MARK(3, 9)
       umma::tc_fence_after();
-      if (lane == 0) {
+      if (umma::elect_one()) {
         piece(kColS, sKhi, true, sU, true, kIdMnMn64, 0u, 0, 8);
         piece(kColS, sKlo, true, sU, true, kIdMnMn64, 1u, 0, 8);
         umma::mma_commit(cbK);
       }
+      __syncwarp();
       FRACSSM_MARK(3, 10)
-      // H = Chat S (both split into bf16 high and low parts, low x low dropped) ...
+      // H = Chat S (both split into bf16 high and low parts, low x low dropped: with single bf16
+      // roundings the output misses its tolerance where large terms cancel) ...
       FRACSSM_WAIT(fS, n);
       FRACSSM_MARK(3, 11)
       umma::tc_fence_after();
-      if (lane == 0) piece(kColH, sChi, false, sS, true, kIdKMn64, 0u, 0, 8);           // Chat(high) S(high)
-      if (lane == 0) piece(kColH, sClo, false, sS, true, kIdKMn64, 1u, 0, 8);           // Chat(low)  S(high)
-      if (lane == 0) piece(kColH, sChi, false, sS + kAtom, true, kIdKMn64, 1u, 0, 8);   // Chat(high) S(low)
+      if (umma::elect_one()) {
+        piece(kColH, sChi, false, sS, true, kIdKMn64, 0u, 0, 8);           // Chat(high) S(high)
+        piece(kColH, sClo, false, sS, true, kIdKMn64, 1u, 0, 8);           // Chat(low)  S(high)
+        piece(kColH, sChi, false, sS + kAtom, true, kIdKMn64, 1u, 0, 8);   // Chat(high) S(low)
+      }
+      __syncwarp();
       // ... + W u
       FRACSSM_WAIT(fW, n);
       FRACSSM_MARK(3, 12)
       umma::tc_fence_after();
-      if (lane == 0) {
+      if (umma::elect_one()) {
         piece(kColH, sW, false, sU, true, kIdKMn64, 1u, 0, 8);
         umma::mma_commit(barH);
       }
+      __syncwarp();
       FRACSSM_MARK(3, 13)
       __syncwarp();
     }
@@ -410,7 +473,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     // the middle of the next tile's first phase, which so overlaps the output MMAs.
     auto write_rows = [&](uint32_t n_done) {
       const int t = prev_t0 + 32 * Q + lane;
-      if (a.gate == nullptr) {
+      if constexpr (!LAYER) {
         FRACSSM_WAIT(barH, n_done);
         umma::tc_fence_after();
         const bool bad = *failed != 0;
@@ -494,7 +557,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       FRACSSM_MARK(pslot, 0)
       float gt_row = 0.f;   // decay of the whole tile for the mode this thread owns in the state update
 
+#ifdef FRACSSM_V_ROLL_H
+#pragma unroll 1
+#else
 #pragma unroll
+#endif
       for (int h = 0; h < 2; ++h) {
         const uint32_t half_off = h * kAtom + th_fix;
         // ---- segment products, the base tiles and the per-token factors cp / ks of this half:
@@ -556,17 +623,23 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         // The other half's inputs (or, in the second pass, nothing: the next item's first half is
         // requested in the tile's last part) are requested now that this half's registers are free.
         // (two token rows at a time, between phases: measured faster than one batch)
-        auto request_other_half = [&](int i) {
-          if (h == 0) {
-            load_tok(raw, a, bh, t0, w, lane, 1, i);
-            load_tok(raw, a, bh, t0, w, lane, 1, i + 1);
+        auto request_other_half = [&](auto i) {
+#ifdef FRACSSM_V_ONEBATCH
+          if (h == 0 && decltype(i)::value == 0) {
+            load_tok2<CKF32, 0>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, 2>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, 4>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, 6>(raw, a, bh, t0, w, lane, 1);
           }
+#else
+          if (h == 0) load_tok2<CKF32, decltype(i)::value>(raw, a, bh, t0, w, lane, 1);
+#endif
         };
-        request_other_half(0);
+        request_other_half(std::integral_constant<int, 0>{});
         umma::named_barrier(1, kWorkers);  // segment products visible to every worker
         FRACSSM_MARK(pslot, 2 + 10 * h)
         if (h == 0 && n > 0) write_rows(n - 1);  // also: every MMA of the previous tile is done, slots 2..5 are free
-        request_other_half(2);
+        request_other_half(std::integral_constant<int, 2>{});
         FRACSSM_MARK(pslot, 3 + 10 * h)
 
         // ---- products of whole segments: back from this segment to the start of its 16 / 32 / 64 /
@@ -594,7 +667,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           if (w & 2) emit_level(sb + kOffY1 + half_off + rg16 * 1024, cp, bk, true);
           else emit_level(sb + kOffZ1 + half_off + rg16 * 1024, ks, fw, true);
         }
-        request_other_half(4);
+        request_other_half(std::integral_constant<int, 4>{});
         // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
         {
           const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
@@ -613,7 +686,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           else emit_level(sb + kOffZ2 + half_off + rg64 * 1024, ks, fw, true);
         }
         warp_arrive(fL, lane);
-        request_other_half(6);
+        request_other_half(std::integral_constant<int, 6>{});
         FRACSSM_MARK(pslot, 4 + 10 * h)
         // to the tile's start (bk becomes E) and end (fw becomes F)
         if (w & 8) {
@@ -676,97 +749,23 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       const bool more = next < a.total;
       const int nj = more ? next / a.BH : 0;
       const int nbh = next - nj * a.BH, nt0 = (nj + a.first_tile) * kTile;
-      auto request_next = [&](int i) {   // two token rows of the next item's first half
+      auto request_next = [&](auto i) {   // two token rows of the next item's first half
         if (more) {
-          load_tok(raw, a, nbh, nt0, w, lane, 0, i);
-          load_tok(raw, a, nbh, nt0, w, lane, 0, i + 1);
-        }
-      };
-      request_next(0);
-
-      // ---- the chain: incoming state -> MMA operand (high | low) -> outgoing state
-      FRACSSM_WAIT(state_bar, n);
-      FRACSSM_WAIT(cb2, n);  // levels 64+32 product done: slots 4 / 5 are free, its accumulators complete
-      FRACSSM_MARK(pslot, 20)
-      const int m_row = 32 * Q + lane;
-      float sj[16];
-      {
-        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
-        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
-                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (jt > 0) {
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const float4 s4 = __ldcg(sp + x * kM);
-            sj[4 * x] = s4.x; sj[4 * x + 1] = s4.y; sj[4 * x + 2] = s4.z; sj[4 * x + 3] = s4.w;
+#ifdef FRACSSM_V_ONEBATCH
+          if (decltype(i)::value == 0) {
+            load_tok2<CKF32, 0>(raw, a, nbh, nt0, w, lane, 0);
+            load_tok2<CKF32, 2>(raw, a, nbh, nt0, w, lane, 0);
+            load_tok2<CKF32, 4>(raw, a, nbh, nt0, w, lane, 0);
+            load_tok2<CKF32, 6>(raw, a, nbh, nt0, w, lane, 0);
           }
-        } else if (a.init) {
-#pragma unroll
-          for (int x = 0; x < 16; ++x)
-            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
-        } else {
-#pragma unroll
-          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
+#else
+          load_tok2<CKF32, decltype(i)::value>(raw, a, nbh, nt0, w, lane, 0);
+#endif
         }
-      }
-      // the incoming state as the MMA operand [high | low] of H = Chat S
-      auto state_operand = [&]() {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ph[4], pl[4];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const float2 sv = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
-            const float2 hi = bf16_round2(sv, ph[x]);
-            pl[x] = pack2(sv.x - hi.x, sv.y - hi.y);
-          }
-          const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
-          *reinterpret_cast<uint4 *>(smem + kOffS + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-          *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-        }
-        warp_arrive(fS, lane);
-        request_next(2);
-        FRACSSM_MARK(pslot, 21)
       };
-      // S_next = Gt * S + Sacc, stored for the next tile of the row (or as the final state)
-      auto state_update = [&]() {
-        FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
-        umma::tc_fence_after();
-        FRACSSM_MARK(pslot, 22)
-        float acc[16];
-        umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
-        umma::tmem_ld_wait();
-        const bool bad = *failed != 0;
-#pragma unroll
-        for (int x = 0; x < 16; ++x) acc[x] = bad ? kNaN : fmaf(gt_row, sj[x], acc[x]);
-        float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (jt + 1 < a.ntiles) {
-#pragma unroll
-          for (int x = 0; x < 4; ++x)
-            __stcg(sp + x * kM, make_float4(acc[4 * x], acc[4 * x + 1], acc[4 * x + 2], acc[4 * x + 3]));
-        } else if (a.fin) {
-#pragma unroll
-          for (int x = 0; x < 16; ++x)
-            st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, acc[x]);
-        }
-        umma::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
-        request_next(4);
-        FRACSSM_MARK(pslot, 23)
-      };
-      // The outgoing state goes first when its own part (Sacc) is already complete: that is the case
-      // when the tile had to wait for the incoming state, i.e. when the row's chain of tiles is what
-      // limits the run; otherwise the operand goes first and the MMA warp gets to work earlier.
-      const bool chain_first = __shfl_sync(0xffffffffu, umma::mbar_test(cbK, n & 1u) ? 1 : 0, 0) != 0;
-      if (chain_first) {
-        state_update();
-        state_operand();
-      } else {
-        state_operand();
-        state_update();
-      }
+      request_next(std::integral_constant<int, 0>{});
 
+      auto w_epilogue = [&]() {
       // ---- W -> slot 4: each block of accumulators goes to its place, 8 columns at a time
       umma::tc_fence_after();
       {
@@ -844,7 +843,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             }
           }
         }
-        request_next(6);
+        request_next(std::integral_constant<int, 6>{});
         // zeros above the diagonal: row t = tid / 4 owns the blocks kc > t / 8, four threads share a row
         {
           const int t = tid >> 2;
@@ -856,6 +855,92 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       }
       warp_arrive(fW, lane);
       FRACSSM_MARK(pslot, 24)
+      };
+      // ---- the chain: incoming state -> MMA operand (high | low) -> outgoing state
+      FRACSSM_WAIT(state_bar, n);
+      FRACSSM_WAIT(cb2, n);  // levels 64+32 product done: slots 4 / 5 are free, its accumulators complete
+      FRACSSM_MARK(pslot, 20)
+      const int m_row = 32 * Q + lane;
+      float sj[16];
+      {
+        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
+        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
+                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
+        if (jt > 0) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float4 s4 = __ldcg(sp + x * kM);
+            sj[4 * x] = s4.x; sj[4 * x + 1] = s4.y; sj[4 * x + 2] = s4.z; sj[4 * x + 3] = s4.w;
+          }
+        } else if (a.init) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
+        }
+      }
+      // the incoming state as the MMA operand [high | low] of H = Chat S
+      auto state_operand = [&]() {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t ph[4], pl[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float2 sv = make_float2(sj[8 * half + 2 * x], sj[8 * half + 2 * x + 1]);
+            const float2 hi = bf16_round2(sv, ph[x]);
+            pl[x] = pack2(sv.x - hi.x, sv.y - hi.y);
+          }
+          const uint32_t off = m_row * 128 + (((2 * P + half) ^ (m_row & 7)) << 4);
+          *reinterpret_cast<uint4 *>(smem + kOffS + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+          *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+        }
+        warp_arrive(fS, lane);
+        request_next(std::integral_constant<int, 2>{});
+        FRACSSM_MARK(pslot, 21)
+      };
+      // S_next = Gt * S + Sacc, stored for the next tile of the row (or as the final state)
+      auto state_update = [&]() {
+        FRACSSM_WAIT(cbK, n);  // Khat(high) and Khat(low) MMAs: Sacc is complete
+        umma::tc_fence_after();
+        FRACSSM_MARK(pslot, 22)
+        float acc[16];
+        umma::tmem_ld16(lane_addr + kColS + 16 * P, acc);
+        umma::tmem_ld_wait();
+        const bool bad = *failed != 0;
+#pragma unroll
+        for (int x = 0; x < 16; ++x) acc[x] = bad ? kNaN : fmaf(gt_row, sj[x], acc[x]);
+        float4 *sp = reinterpret_cast<float4 *>(a.state) + (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
+        if (jt + 1 < a.ntiles) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x)
+            __stcg(sp + x * kM, make_float4(acc[4 * x], acc[4 * x + 1], acc[4 * x + 2], acc[4 * x + 3]));
+        } else if (a.fin) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            st_f32(a.fin, (static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row, a.fin_dt, acc[x]);
+        }
+        umma::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
+        request_next(std::integral_constant<int, 4>{});
+        FRACSSM_MARK(pslot, 23)
+      };
+      // The outgoing state goes first when its own part (Sacc) is already complete: that is the case
+      // when the tile had to wait for the incoming state, i.e. when the row's chain of tiles is what
+      // limits the run; otherwise the operand goes first and the MMA warp gets to work earlier.
+      const bool chain_first = __shfl_sync(0xffffffffu, umma::mbar_test(cbK, n & 1u) ? 1 : 0, 0) != 0;
+      if (chain_first) {
+        state_update();
+        state_operand();
+      } else {
+        state_operand();
+        state_update();
+      }
+
+      w_epilogue();
+
 
       prev_bh = bh;
       prev_t0 = t0;
@@ -917,8 +1002,10 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   {
     std::lock_guard<std::mutex> lock(mu);
     if (sm_count[dev] == 0) {
-      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true>));
+      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, true>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, true>));
       if (prc) return prc;
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -962,8 +1049,13 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
   const cudaStream_t st = (cudaStream_t)stream;
-  if (ckf32) scan_fused_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-  else scan_fused_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  if (a.gate != nullptr) {
+    if (ckf32) scan_fused_kernel<true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    else scan_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  } else {
+    if (ckf32) scan_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    else scan_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+  }
   return check_launch("frac_scan (single-pass kernel)");
 }
 

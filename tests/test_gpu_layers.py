@@ -178,6 +178,23 @@ def test_scan_epilogue_matches_unfused_pair():
     close(y, ref, **TOL_BF16)
 
 
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,L,H,R", [(1, 1, 4, 64), (3, 7, 3, 40), (2, 21, 32, 64), (1, 130, 24, 64), (2, 9, 40, 64)])
+def test_scan_epilogue_row_widths(B, L, H, R, wdtype):
+    """Row widths on either side of each register-resident variant (256, 120, 2048, 1536 columns) and
+    one beyond them (2560), row counts that do not fill the last block, both weight types."""
+    from frac_ssm_b200.layers import scan_epilogue
+    g = torch.Generator().manual_seed(17)
+    h = torch.randn(B * H, L, R, generator=g).bfloat16()
+    x = torch.randn(B, L, H * R, generator=g).bfloat16()
+    z = torch.randn(B, L, H * R, generator=g).bfloat16()
+    D = torch.randn(H, R, generator=g)
+    w = (1 + 0.1 * torch.randn(H * R, generator=g)).to(wdtype)
+    y = scan_epilogue(h.cuda(), x.cuda(), z.cuda(), D.cuda(), w.cuda(), H, R, 1e-6, gate_bias=-0.25)
+    ref = O.rmsnorm_gated(O.skip_mix(h, x, D, H, R, exact=True), w, z.double() - 0.25, 1e-6, exact=True)
+    close(y, ref, **TOL_BF16)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("shards", [2, 3, 8])
 def test_head_sharded_epilogue_two_passes(dtype, shards):
