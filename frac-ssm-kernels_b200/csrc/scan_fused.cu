@@ -15,11 +15,15 @@
 // state from tile to tile of a row (polls and releases the per-row counter); warps 18-19 only pad
 // the register group of those two.  Workers hand a batch of tiles over by arriving on a "full"
 // mbarrier (one arrival per warp, after a proxy fence); the MMA warp hands buffers and accumulators
-// back through tcgen05.commit mbarriers.
+// back through tcgen05.commit mbarriers.  The MMA warp passes through its code once per tile, so that
+// code is kept small (rolled loops over the contraction steps, issued from one elected lane, which
+// keeps the descriptor arithmetic on the uniform datapath): as straight-line code it was fetched from
+// beyond the instruction cache every tile and the kernel ran 10 % slower.
 //
 // A tile is processed in two passes over the modes (64 + 64): a worker thread owns 8 token rows x 2
 // modes per pass, so its per-token factors (32 registers) and the raw inputs of the other pass
-// (32 registers, requested one pass ahead) fit in registers without spilling; each operand tile's two
+// (32 registers, requested one pass ahead in two batches of four token rows; full tiles use one
+// address per thread and immediate row offsets) fit in registers without spilling; each operand tile's two
 // 64-column halves are filled by the two passes and the level / base products are issued per pass
 // (4 of their 8 contraction steps), accumulating in tensor memory.
 //
@@ -211,7 +215,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   uint64_t *cb0 = bars + 0, *cbL = bars + 1, *cb2 = bars + 2, *cbK = bars + 3, *barH = bars + 4, *barU = bars + 5;
   uint64_t *fA = bars + 6, *fL = bars + 7, *fK = bars + 8, *fW = bars + 9, *fS = bars + 10;
   uint64_t *item_bar = bars + 11, *state_bar = bars + 12, *out_bar = bars + 13, *read_bar = bars + 14;
-  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 15);
+  uint64_t *fL1 = bars + 15;    // 16 worker warps, once per half: the rows of the levels 8 + 16 are written
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 16);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_s + 3);  // a wait of this CTA ran out
 
@@ -224,6 +229,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     umma::mbar_init(state_bar, 1);
     umma::mbar_init(out_bar, 16);
     umma::mbar_init(read_bar, 17);   // the 16 worker warps and the MMA warp, once each has read the tile's item
+    umma::mbar_init(fL1, 16);
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
     *failed = 0;
@@ -245,19 +251,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
   } else if (w == 17) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-#ifdef FRACSSM_V_PARK_CHAIN
-#define FRACSSM_WAIT(bar, parity)                                  \
-  if (ok) {                                                        \
-    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);      \
-    if (!ok) *failed = 1;                                          \
-  }
-#else
 #define FRACSSM_WAIT(bar, parity)                                  \
   if (ok) {                                                        \
     ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
     if (!ok) *failed = 1;                                          \
   }
-#endif
     // =========================== chain warp ===========================
     // Tickets, the L2 prefetch of the next item, and the hand-over of the state between the tiles of
     // a (batch, head) row: nothing here waits for an MMA, so a row's chain is never held up by them.
@@ -316,19 +314,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
 #undef FRACSSM_WAIT
   } else if (w == 16) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-#ifdef FRACSSM_V_PARK_MMA
-#define FRACSSM_WAIT(bar, parity)                                  \
-  if (ok) {                                                        \
-    ok = umma::mbar_wait_parked(bar, (parity) & 1u, wait_ns);      \
-    if (!ok) *failed = 1;                                          \
-  }
-#else
 #define FRACSSM_WAIT(bar, parity)                                  \
   if (ok) {                                                        \
     ok = umma::mbar_wait(bar, (parity) & 1u, wait_ns);             \
     if (!ok) *failed = 1;                                          \
   }
-#endif
     // =========================== MMA warp ===========================
     const uint32_t sb = umma::smem_u32(smem);
     const uint32_t sA0 = sb + kOffA0, sB0 = sb + kOffB0, sY1 = sb + kOffY1, sZ1 = sb + kOffZ1, sY2 = sb + kOffY2,
@@ -391,12 +381,17 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           }
         }
         // levels 8 + 16, then 64 + 32: A rows x B rows of the stacked tiles, this half of the modes
-        FRACSSM_WAIT(fL, h);
-        FRACSSM_MARK(3, 3 + 4 * h)
+        FRACSSM_WAIT(fL1, h);
         umma::tc_fence_after();
         if (umma::elect_one()) {
           piece(kColL1, sY1, false, sZ1, false, kIdKK128, h, 4 * h, 4 * h + 4);
           umma::mma_commit(cbL);
+        }
+        __syncwarp();
+        FRACSSM_WAIT(fL, h);
+        FRACSSM_MARK(3, 3 + 4 * h)
+        umma::tc_fence_after();
+        if (umma::elect_one()) {
           piece(kColL2, sY2, false, sZ2, false, kIdKK128, h, 4 * h, 4 * h + 4);
           if (h == 1) umma::mma_commit(cb2);
         }
@@ -556,12 +551,29 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       const int t0 = jt * kTile;
       FRACSSM_MARK(pslot, 0)
       float gt_row = 0.f;   // decay of the whole tile for the mode this thread owns in the state update
-
-#ifdef FRACSSM_V_ROLL_H
-#pragma unroll 1
-#else
+      const int m_row = 32 * Q + lane;
+      float sj[16];         // incoming state: row m_row, columns 16 P .. 16 P + 15
+      auto load_state = [&]() {
+        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
+        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
+                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
+        if (jt > 0) {
 #pragma unroll
-#endif
+          for (int x = 0; x < 4; ++x) {
+            const float4 s4 = __ldcg(sp + x * kM);
+            sj[4 * x] = s4.x; sj[4 * x + 1] = s4.y; sj[4 * x + 2] = s4.z; sj[4 * x + 3] = s4.w;
+          }
+        } else if (a.init) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
+        }
+      };
+
+#pragma unroll
       for (int h = 0; h < 2; ++h) {
         const uint32_t half_off = h * kAtom + th_fix;
         // ---- segment products, the base tiles and the per-token factors cp / ks of this half:
@@ -623,23 +635,18 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         // The other half's inputs (or, in the second pass, nothing: the next item's first half is
         // requested in the tile's last part) are requested now that this half's registers are free.
         // (two token rows at a time, between phases: measured faster than one batch)
+        // (in two batches of four token rows: one batch, and four batches of two, measured slower)
         auto request_other_half = [&](auto i) {
-#ifdef FRACSSM_V_ONEBATCH
-          if (h == 0 && decltype(i)::value == 0) {
-            load_tok2<CKF32, 0>(raw, a, bh, t0, w, lane, 1);
-            load_tok2<CKF32, 2>(raw, a, bh, t0, w, lane, 1);
-            load_tok2<CKF32, 4>(raw, a, bh, t0, w, lane, 1);
-            load_tok2<CKF32, 6>(raw, a, bh, t0, w, lane, 1);
+          if (h == 0) {
+            load_tok2<CKF32, decltype(i)::value>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, decltype(i)::value + 2>(raw, a, bh, t0, w, lane, 1);
           }
-#else
-          if (h == 0) load_tok2<CKF32, decltype(i)::value>(raw, a, bh, t0, w, lane, 1);
-#endif
         };
         request_other_half(std::integral_constant<int, 0>{});
         umma::named_barrier(1, kWorkers);  // segment products visible to every worker
         FRACSSM_MARK(pslot, 2 + 10 * h)
         if (h == 0 && n > 0) write_rows(n - 1);  // also: every MMA of the previous tile is done, slots 2..5 are free
-        request_other_half(std::integral_constant<int, 2>{});
+        request_other_half(std::integral_constant<int, 4>{});
         FRACSSM_MARK(pslot, 3 + 10 * h)
 
         // ---- products of whole segments: back from this segment to the start of its 16 / 32 / 64 /
@@ -667,7 +674,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           if (w & 2) emit_level(sb + kOffY1 + half_off + rg16 * 1024, cp, bk, true);
           else emit_level(sb + kOffZ1 + half_off + rg16 * 1024, ks, fw, true);
         }
-        request_other_half(std::integral_constant<int, 4>{});
+        warp_arrive(fL1, lane);
         // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
         {
           const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
@@ -686,7 +693,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           else emit_level(sb + kOffZ2 + half_off + rg64 * 1024, ks, fw, true);
         }
         warp_arrive(fL, lane);
-        request_other_half(std::integral_constant<int, 6>{});
         FRACSSM_MARK(pslot, 4 + 10 * h)
         // to the tile's start (bk becomes E) and end (fw becomes F)
         if (w & 8) {
@@ -749,18 +755,10 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       const bool more = next < a.total;
       const int nj = more ? next / a.BH : 0;
       const int nbh = next - nj * a.BH, nt0 = (nj + a.first_tile) * kTile;
-      auto request_next = [&](auto i) {   // two token rows of the next item's first half
+      auto request_next = [&](auto i) {   // four token rows of the next item's first half
         if (more) {
-#ifdef FRACSSM_V_ONEBATCH
-          if (decltype(i)::value == 0) {
-            load_tok2<CKF32, 0>(raw, a, nbh, nt0, w, lane, 0);
-            load_tok2<CKF32, 2>(raw, a, nbh, nt0, w, lane, 0);
-            load_tok2<CKF32, 4>(raw, a, nbh, nt0, w, lane, 0);
-            load_tok2<CKF32, 6>(raw, a, nbh, nt0, w, lane, 0);
-          }
-#else
           load_tok2<CKF32, decltype(i)::value>(raw, a, nbh, nt0, w, lane, 0);
-#endif
+          load_tok2<CKF32, decltype(i)::value + 2>(raw, a, nbh, nt0, w, lane, 0);
         }
       };
       request_next(std::integral_constant<int, 0>{});
@@ -843,7 +841,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             }
           }
         }
-        request_next(std::integral_constant<int, 6>{});
+        request_next(std::integral_constant<int, 4>{});
         // zeros above the diagonal: row t = tid / 4 owns the blocks kc > t / 8, four threads share a row
         {
           const int t = tid >> 2;
@@ -858,29 +856,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       };
       // ---- the chain: incoming state -> MMA operand (high | low) -> outgoing state
       FRACSSM_WAIT(state_bar, n);
+      load_state();
       FRACSSM_WAIT(cb2, n);  // levels 64+32 product done: slots 4 / 5 are free, its accumulators complete
       FRACSSM_MARK(pslot, 20)
-      const int m_row = 32 * Q + lane;
-      float sj[16];
-      {
-        // scratch layout [bh][P][x][m][4]: the lanes of a warp touch consecutive 16-byte pieces
-        const float4 *sp = reinterpret_cast<const float4 *>(a.state) +
-                           (static_cast<int64_t>(bh) * 4 + P) * 4 * kM + m_row;
-        if (jt > 0) {
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const float4 s4 = __ldcg(sp + x * kM);
-            sj[4 * x] = s4.x; sj[4 * x + 1] = s4.y; sj[4 * x + 2] = s4.z; sj[4 * x + 3] = s4.w;
-          }
-        } else if (a.init) {
-#pragma unroll
-          for (int x = 0; x < 16; ++x)
-            sj[x] = a.init[(static_cast<int64_t>(bh) * kR + 16 * P + x) * kM + m_row];
-        } else {
-#pragma unroll
-          for (int x = 0; x < 16; ++x) sj[x] = 0.f;
-        }
-      }
       // the incoming state as the MMA operand [high | low] of H = Chat S
       auto state_operand = [&]() {
 #pragma unroll
@@ -897,7 +875,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           *reinterpret_cast<uint4 *>(smem + kOffS + kAtom + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
         }
         warp_arrive(fS, lane);
-        request_next(std::integral_constant<int, 2>{});
         FRACSSM_MARK(pslot, 21)
       };
       // S_next = Gt * S + Sacc, stored for the next tile of the row (or as the final state)
@@ -924,7 +901,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         umma::tc_fence_before();
         __syncwarp();
         if (lane == 0) umma::mbar_arrive(out_bar);  // the chain warp releases the row counter
-        request_next(std::integral_constant<int, 4>{});
         FRACSSM_MARK(pslot, 23)
       };
       // The outgoing state goes first when its own part (Sacc) is already complete: that is the case

@@ -80,6 +80,13 @@ def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32,
     init = None if initial_state is None else initial_state.contiguous()
     h = torch.empty(B, L, R, device=u.device, dtype=u.dtype)
     fin = torch.empty(B, R, M, device=u.device, dtype=final_state_dtype) if want_final else None
+    if L == 0:      # no token: the state passes through unchanged (zeros without an initial state)
+        if want_final:
+            if init is None:
+                fin.zero_()
+            else:
+                fin.copy_(init)
+        return h, fin
     if B > 0:
         lib = C.lib()
         with C.trace("frac_scan"), torch.cuda.device(u.device):

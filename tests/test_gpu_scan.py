@@ -144,6 +144,11 @@ def test_zero_batch_and_determinism(scan):
     a = scan(u, c, kappa, rho, 256, init, True)
     b = scan(u, c, kappa, rho, 256, init, True)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])     # no atomics in the forward
+    # no token at all: the initial state passes through, in the default (bf16) and the f32 state type
+    h0, fin0 = scan(u[:, :0], c[:, :0], kappa[:, :0], rho[:, :0], 256, init, True)
+    assert h0.shape == (5, 0, 64) and fin0.dtype == torch.bfloat16 and torch.equal(fin0, init.bfloat16())
+    _, fin1 = scan(u[:, :0], c[:, :0], kappa[:, :0], rho[:, :0], 256, None, True)
+    assert torch.count_nonzero(fin1) == 0
 
 
 # ---- size-independent properties at the benchmark's full shape ---------------------------------
