@@ -78,9 +78,11 @@ __global__ void __launch_bounds__(128) compute_params_kernel(const ParamArgs a) 
     st_f32(a.kappa, obase + m, a.ck_dt, kap);
     a.rho[obase + m] = rho;
   }
-  const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
-  for (int64_t r = lane; r < R; r += 32)
-    st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+  if (a.u) {   // (no copy when the caller already holds the head-major u, e.g. from the conv kernel)
+    const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
+    for (int64_t r = lane; r < R; r += 32)
+      st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+  }
 }
 
 // The same prep for M = 128 with bf16 projections: one warp walks kPrepTokens tokens of one (b, h);
@@ -180,9 +182,11 @@ __global__ void __launch_bounds__(128) compute_params_m128_kernel(const ParamArg
       __stcs(reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(a.kappa) + obase),
              make_uint2(*reinterpret_cast<const uint32_t *>(&k0), *reinterpret_cast<const uint32_t *>(&k1)));
     }
-    const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
-    for (int64_t r = lane; r < R; r += 32)
-      st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+    if (a.u) {
+      const int64_t xbase = b * a.x_sb + l * a.x_sl + h * R;
+      for (int64_t r = lane; r < R; r += 32)
+        st_f32(a.u, (bh * a.L + l) * R + r, a.x_dt, ld_f32(a.x, xbase + r, a.x_dt));
+    }
   }
 }
 
@@ -474,7 +478,7 @@ extern "C" int fracssm_compute_params(const void *dyn, int dyn_dtype, int64_t dy
   if (!known_dtype(dyn_dtype) || !known_dtype(rw_dtype) || !known_dtype(x_dtype) || !known_dtype(ck_dtype))
     return fail(FRACSSM_ERR_ARG, "compute_params: unsupported dtype");
   if (Bt == 0 || L == 0) return FRACSSM_OK;
-  if (!dyn || !rw || !x_conv || !dt_bias || !base_log_tau || !read_gate_logit || !write_gate_logit || !u || !c ||
+  if (!dyn || !rw || (u && !x_conv) || !dt_bias || !base_log_tau || !read_gate_logit || !write_gate_logit || !c ||
       !kappa || !rho)
     return fail(FRACSSM_ERR_ARG, "compute_params: null pointer");
   if (Bt * H > 65535) return fail(FRACSSM_ERR_UNSUPPORTED, "compute_params: batch*heads too large for one launch");

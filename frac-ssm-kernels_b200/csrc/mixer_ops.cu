@@ -19,9 +19,11 @@ __global__ void __launch_bounds__(128)
 causal_conv_silu_kernel(const void *__restrict__ x, int x_dt, int64_t x_sb, int64_t x_sl,
                         const float *__restrict__ mask, int64_t m_sb, int64_t m_sl,
                         const void *__restrict__ w, int w_dt, const void *__restrict__ bias, int K,
-                        void *__restrict__ y, int y_dt, int64_t L, int64_t C) {
+                        void *__restrict__ y, int y_dt, void *__restrict__ u_heads, int64_t R, int64_t L,
+                        int64_t C) {
   const int64_t ch = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (ch >= C) return;
+  const int64_t H = u_heads ? C / R : 0, hh = u_heads ? ch / R : 0, rr = u_heads ? ch % R : 0;
   const int64_t b = blockIdx.z, l0 = (int64_t)blockIdx.y * kConvTokens;
   float wk[kConvMaxK], win[kConvMaxK];
 #pragma unroll
@@ -45,7 +47,9 @@ causal_conv_silu_kernel(const void *__restrict__ x, int x_dt, int64_t x_sb, int6
       if (k < K - 1) acc = fmaf(wk[k], win[k], acc);
       else if (k == K - 1) acc = fmaf(wk[k], cur, acc);
     }
-    st_f32(y, (b * L + l) * C + ch, y_dt, silu_(acc));
+    const float out = silu_(acc);
+    st_f32(y, (b * L + l) * C + ch, y_dt, out);
+    if (u_heads) st_f32(u_heads, ((b * H + hh) * L + l) * R + rr, y_dt, out);
 #pragma unroll
     for (int k = 0; k < kConvMaxK - 1; ++k) {
       if (k < K - 2) win[k] = win[k + 1];
@@ -54,7 +58,7 @@ causal_conv_silu_kernel(const void *__restrict__ x, int x_dt, int64_t x_sb, int6
   }
 }
 
-// bf16 path for the usual width 4: eight channels (16 bytes) per thread.
+// bf16 path for the usual width 4.
 __device__ __forceinline__ void unpack8(const uint4 &p, float (&f)[8]) {
   const uint32_t wds[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
@@ -64,64 +68,111 @@ __device__ __forceinline__ void unpack8(const uint4 &p, float (&f)[8]) {
   }
 }
 
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void unpack4(const uint2 &p, float (&f)[4]) {
+  f[0] = __uint_as_float(p.x << 16);
+  f[1] = __uint_as_float(p.x & 0xFFFF0000u);
+  f[2] = __uint_as_float(p.y << 16);
+  f[3] = __uint_as_float(p.y & 0xFFFF0000u);
+}
+
+// Four channels (8 bytes) per thread, kConvTokens tokens walked with the window in registers, four
+// tokens' loads in flight at a time; at most 80 registers, so 6 blocks of 128 threads per SM.
+__global__ void __launch_bounds__(128, 6)
 causal_conv4_silu_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_sb, int64_t x_sl,
                               const float *__restrict__ mask, int64_t m_sb, int64_t m_sl,
                               const void *__restrict__ w, int w_dt, const void *__restrict__ bias,
-                              __nv_bfloat16 *__restrict__ y, int64_t L, int64_t C) {
-  const int64_t ch = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+                              __nv_bfloat16 *__restrict__ y, __nv_bfloat16 *__restrict__ u_heads, int64_t R,
+                              int64_t L, int64_t C) {
+  const int64_t ch = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (ch >= C) return;
+  // the same four values also go to the head-major copy [Bt * H, L, R] (R a multiple of 4)
+  __nv_bfloat16 *u_row = nullptr;
+  if (u_heads) u_row = u_heads + ((int64_t)blockIdx.z * (C / R) + ch / R) * L * R + ch % R;
   const int64_t b = blockIdx.z, l0 = (int64_t)blockIdx.y * kConvTokens;
-  float wk[4][8], bv[8], w0[8], w1[8], w2[8];
+  float wk[4][4], bv[4], w0[4], w1[4], w2[4];
+  if (w_dt == FRACSSM_BF16) {   // 4 channels x 4 taps = 32 contiguous bytes (ch is a multiple of 4)
+    const uint4 *wp = reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(w) + ch * 4);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+    for (int q = 0; q < 2; ++q) {   // piece q holds channels 2q, 2q + 1
+      float f[8];
+      unpack8(__ldg(wp + q), f);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) wk[k][i] = ld_f32(w, (ch + i) * 4 + k, w_dt);
-    bv[i] = bias ? ld_f32(bias, ch + i, w_dt) : 0.f;
+      for (int k = 0; k < 4; ++k) { wk[k][2 * q] = f[k]; wk[k][2 * q + 1] = f[4 + k]; }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) wk[k][i] = ld_f32(w, (ch + i) * 4 + k, w_dt);
+    }
   }
-  auto in = [&](int64_t l, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) bv[i] = bias ? ld_f32(bias, ch + i, w_dt) : 0.f;
+  auto in = [&](int64_t l, float (&f)[4]) {
     if (l < 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = 0.f;
+      for (int i = 0; i < 4; ++i) f[i] = 0.f;
       return;
     }
-    unpack8(__ldcs(reinterpret_cast<const uint4 *>(x + b * x_sb + l * x_sl + ch)), f);
+    unpack4(__ldcs(reinterpret_cast<const uint2 *>(x + b * x_sb + l * x_sl + ch)), f);
     if (mask) {
       const float m = mask[b * m_sb + l * m_sl];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] *= m;
+      for (int i = 0; i < 4; ++i) f[i] *= m;
     }
   };
   in(l0 - 3, w0);
   in(l0 - 2, w1);
   in(l0 - 1, w2);
   const int64_t l1 = min(l0 + kConvTokens, L);
-  for (int64_t l = l0; l < l1; ++l) {
-    float cur[8];
-    in(l, cur);
-    uint32_t o[4];
+  for (int64_t lg = l0; lg < l1; lg += 4) {
+    uint2 raw[4];
+    float mk[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float r[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int c = 2 * i + e;
-        float acc = bv[c];
-        acc = fmaf(wk[0][c], w0[c], acc);
-        acc = fmaf(wk[1][c], w1[c], acc);
-        acc = fmaf(wk[2][c], w2[c], acc);
-        acc = fmaf(wk[3][c], cur[c], acc);
-        r[e] = silu_(acc);
+    for (int j = 0; j < 4; ++j) {
+      raw[j] = make_uint2(0u, 0u);
+      mk[j] = 1.f;
+      if (lg + j < l1) {
+        raw[j] = __ldcs(reinterpret_cast<const uint2 *>(x + b * x_sb + (lg + j) * x_sl + ch));
+        if (mask) mk[j] = mask[b * m_sb + (lg + j) * m_sl];
       }
-      const __nv_bfloat162 t = __floats2bfloat162_rn(r[0], r[1]);
-      o[i] = *reinterpret_cast<const uint32_t *>(&t);
     }
-    __stcs(reinterpret_cast<uint4 *>(y + (b * L + l) * C + ch), make_uint4(o[0], o[1], o[2], o[3]));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      w0[i] = w1[i];
-      w1[i] = w2[i];
-      w2[i] = cur[i];
+    for (int j = 0; j < 4; ++j) {
+      if (lg + j < l1) {
+        const int64_t l = lg + j;
+        float cur[4];
+        unpack4(raw[j], cur);
+        if (mask) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) cur[i] *= mk[j];
+        }
+        uint32_t o[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float r[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = 2 * i + e;
+            float acc = bv[c];
+            acc = fmaf(wk[0][c], w0[c], acc);
+            acc = fmaf(wk[1][c], w1[c], acc);
+            acc = fmaf(wk[2][c], w2[c], acc);
+            acc = fmaf(wk[3][c], cur[c], acc);
+            r[e] = __fdividef(acc, 1.f + __expf(-acc));   // silu, about 2 ulp: the output is bf16
+          }
+          const __nv_bfloat162 t = __floats2bfloat162_rn(r[0], r[1]);
+          o[i] = *reinterpret_cast<const uint32_t *>(&t);
+        }
+        __stcs(reinterpret_cast<uint2 *>(y + (b * L + l) * C + ch), make_uint2(o[0], o[1]));
+        if (u_row) __stcs(reinterpret_cast<uint2 *>(u_row + l * R), make_uint2(o[0], o[1]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          w0[i] = w1[i];
+          w1[i] = w2[i];
+          w2[i] = cur[i];
+        }
+      }
     }
   }
 }
@@ -167,7 +218,18 @@ extern "C" int fracssm_causal_conv_silu(const void *x, int x_dtype, int64_t x_sb
                                         const void *weight, const void *bias, int w_dtype, void *y,
                                         int y_dtype, int64_t Bt, int64_t L, int64_t C, int64_t K,
                                         void *stream) {
+  return fracssm_causal_conv_silu_heads(x, x_dtype, x_sb, x_sl, mask, m_sb, m_sl, weight, bias, w_dtype, y, y_dtype,
+                                        nullptr, 0, Bt, L, C, K, stream);
+}
+
+extern "C" int fracssm_causal_conv_silu_heads(const void *x, int x_dtype, int64_t x_sb, int64_t x_sl,
+                                              const float *mask, int64_t m_sb, int64_t m_sl,
+                                              const void *weight, const void *bias, int w_dtype, void *y,
+                                              int y_dtype, void *u_heads, int64_t R, int64_t Bt, int64_t L,
+                                              int64_t C, int64_t K, void *stream) {
   using namespace fracssm;
+  if (u_heads && (R <= 0 || C % R != 0))
+    return fail(FRACSSM_ERR_ARG, "causal_conv_silu: the head width must divide the channel count");
   if (Bt < 0 || L < 0 || C <= 0 || K < 1 || K > kConvMaxK) return fail(FRACSSM_ERR_ARG, "causal_conv_silu: bad sizes (kernel width 1..8)");
   if (!known_dtype(x_dtype) || !known_dtype(w_dtype) || !known_dtype(y_dtype))
     return fail(FRACSSM_ERR_ARG, "causal_conv_silu: unsupported dtype");
@@ -178,16 +240,17 @@ extern "C" int fracssm_causal_conv_silu(const void *x, int x_dtype, int64_t x_sb
   auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const dim3 block(128);
   if (K == 4 && x_dtype == FRACSSM_BF16 && y_dtype == FRACSSM_BF16 && C % 8 == 0 && al16(x) && al16(y) &&
-      x_sb % 8 == 0 && x_sl % 8 == 0) {
-    const dim3 grid((unsigned)ceil_div(C / 8, 128), (unsigned)ceil_div(L, kConvTokens), (unsigned)Bt);
+      x_sb % 8 == 0 && x_sl % 8 == 0 && (!u_heads || (R % 8 == 0 && al16(u_heads))) &&
+      (w_dtype != FRACSSM_BF16 || al16(weight))) {
+    const dim3 grid((unsigned)ceil_div(C / 4, 128), (unsigned)ceil_div(L, kConvTokens), (unsigned)Bt);
     causal_conv4_silu_bf16_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const __nv_bfloat16 *>(x), x_sb, x_sl, mask, m_sb, m_sl, weight, w_dtype, bias,
-        reinterpret_cast<__nv_bfloat16 *>(y), L, C);
+        reinterpret_cast<__nv_bfloat16 *>(y), reinterpret_cast<__nv_bfloat16 *>(u_heads), R, L, C);
     return check_launch("causal_conv_silu");
   }
   const dim3 grid((unsigned)ceil_div(C, 128), (unsigned)ceil_div(L, kConvTokens), (unsigned)Bt);
   causal_conv_silu_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(x, x_dtype, x_sb, x_sl, mask, m_sb, m_sl, weight,
-                                                                 w_dtype, bias, (int)K, y, y_dtype, L, C);
+                                                                 w_dtype, bias, (int)K, y, y_dtype, u_heads, R, L, C);
   return check_launch("causal_conv_silu");
 }
 

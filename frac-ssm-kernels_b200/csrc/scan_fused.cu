@@ -73,6 +73,7 @@ constexpr int kWorkerRegs = 112, kControlRegs = 32;
 constexpr int kLaunchRegsNeeded = (kWorkers * kWorkerRegs + (kThreads - kWorkers) * kControlRegs + kThreads - 1) / kThreads;
 // shared memory map (bytes from the 1024-aligned base)
 constexpr uint32_t kSlot = 32768;
+static_assert(kSlot == 32768, "emit_pair_next_slot stores 32768 bytes further on");
 constexpr uint32_t kOffA0 = 0, kOffB0 = kSlot, kOffY1 = 2 * kSlot, kOffZ1 = 3 * kSlot, kOffY2 = 4 * kSlot,
                    kOffZ2 = 5 * kSlot;
 constexpr uint32_t kOffKhi = kOffA0, kOffKlo = kOffB0, kOffChi = kOffY1, kOffClo = kOffZ1, kOffW = kOffY2,
@@ -200,6 +201,13 @@ __device__ __forceinline__ void emit_pair(uint32_t rows_s, int i, uint32_t w0) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(w0) : "memory");
 }
 
+// The same row of the operand tile one slot further on (slots are 32 KB apart, so the swizzled row
+// address is the same plus a constant, which the store takes as an immediate).
+__device__ __forceinline__ void emit_pair_next_slot(uint32_t rows_s, int i, uint32_t w0) {
+  const uint32_t addr = (rows_s ^ (static_cast<uint32_t>(i) << 4)) + i * 128;
+  asm volatile("st.shared.b32 [%0+32768], %1;" ::"r"(addr), "r"(w0) : "memory");
+}
+
 // CKF32: c and kappa are float32 (else bf16).  LAYER: the output stage applies the skip connection and
 // the gate (its code is kept out of the plain kernel, whose loop is fetched once per tile).
 template <bool CKF32, bool LAYER>
@@ -210,7 +218,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
   // mbarriers.  Completed once per tile: cb2 / cbK / barH (tcgen05.commit), barU (TMA), fS / fW / out_bar
   // (16 worker warps), item_bar / state_bar (chain warp), read_bar (workers + MMA warp).  Completed once per HALF of the modes,
   // i.e. twice per tile, so the phase parity of half h is simply h: cb0 / cbL (tcgen05.commit) and
-  // fA / fL / fK (16 worker warps).
+  // fA / fL1 / fL / fK (16 worker warps).
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffMisc);
   uint64_t *cb0 = bars + 0, *cbL = bars + 1, *cb2 = bars + 2, *cbK = bars + 3, *barH = bars + 4, *barU = bars + 5;
   uint64_t *fA = bars + 6, *fL = bars + 7, *fK = bars + 8, *fW = bars + 9, *fS = bars + 10;
@@ -581,7 +589,7 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         //   ks[i] = kappa[i] * (decay after token i to the segment's end)
         f2 cp[8], ks[8], g8;
         {
-          const uint32_t rowsA = sb + kOffA0 + half_off + w * 1024, rowsB = sb + kOffB0 + half_off + w * 1024;
+          const uint32_t rowsA = sb + kOffA0 + half_off + w * 1024;   // B0 is the next slot
           f2 g4a, g4b;
           {
             // tokens 0..3: reference point just after token 3
@@ -597,10 +605,10 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             emit_pair(rowsA, 1, cvt_bf2(mul2(c1, iq1)));
             emit_pair(rowsA, 2, cvt_bf2(mul2(c2, iq2)));
             emit_pair(rowsA, 3, cvt_bf2(c3));
-            emit_pair(rowsB, 0, cvt_bf2(b0));
-            emit_pair(rowsB, 1, cvt_bf2(b1));
-            emit_pair(rowsB, 2, cvt_bf2(b2));
-            emit_pair(rowsB, 3, cvt_bf2(k3));
+            emit_pair_next_slot(rowsA, 0, cvt_bf2(b0));
+            emit_pair_next_slot(rowsA, 1, cvt_bf2(b1));
+            emit_pair_next_slot(rowsA, 2, cvt_bf2(b2));
+            emit_pair_next_slot(rowsA, 3, cvt_bf2(k3));
             cp[0] = mul2(c0, r0); cp[1] = mul2(c1, p1); cp[2] = mul2(c2, p2); cp[3] = mul2(c3, p3);
             ks[0] = b0; ks[1] = b1; ks[2] = b2; ks[3] = k3;   // times g4b, below
           }
@@ -618,10 +626,10 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             emit_pair(rowsA, 5, cvt_bf2(a5));
             emit_pair(rowsA, 6, cvt_bf2(a6));
             emit_pair(rowsA, 7, cvt_bf2(a7));
-            emit_pair(rowsB, 4, cvt_bf2(mul2(k4, iq4)));
-            emit_pair(rowsB, 5, cvt_bf2(mul2(k5, iq5)));
-            emit_pair(rowsB, 6, cvt_bf2(mul2(k6, iq6)));
-            emit_pair(rowsB, 7, cvt_bf2(mul2(k7, iq7)));
+            emit_pair_next_slot(rowsA, 4, cvt_bf2(mul2(k4, iq4)));
+            emit_pair_next_slot(rowsA, 5, cvt_bf2(mul2(k5, iq5)));
+            emit_pair_next_slot(rowsA, 6, cvt_bf2(mul2(k6, iq6)));
+            emit_pair_next_slot(rowsA, 7, cvt_bf2(mul2(k7, iq7)));
             cp[4] = mul2(a4, g4a); cp[5] = mul2(a5, g4a); cp[6] = mul2(a6, g4a); cp[7] = mul2(a7, g4a);
             ks[4] = mul2(k4, s4); ks[5] = mul2(k5, s5); ks[6] = mul2(k6, r7); ks[7] = k7;
           }
@@ -719,26 +727,26 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         FRACSSM_WAIT(cb0, h);
         FRACSSM_MARK(pslot, 6 + 10 * h)
         {
-          const uint32_t rowsH = sb + kOffKhi + half_off + w * 1024, rowsL = sb + kOffKlo + half_off + w * 1024;
+          const uint32_t rowsH = sb + kOffKhi + half_off + w * 1024;   // the low part is the next slot
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const f2 kf = mul2(ks[i], fw);
             const uint32_t hi = cvt_bf2(kf);
             emit_pair(rowsH, i, hi);
-            emit_pair(rowsL, i, cvt_bf2(sub2(kf, widen_bf2(hi))));
+            emit_pair_next_slot(rowsH, i, cvt_bf2(sub2(kf, widen_bf2(hi))));
           }
         }
         // ---- Chat = cp * (decay from the tile's start) -> slots 2 / 3 (this half's level-8/16 product done)
         FRACSSM_WAIT(cbL, h);
         FRACSSM_MARK(pslot, 7 + 10 * h)
         {
-          const uint32_t rowsH = sb + kOffChi + half_off + w * 1024, rowsL = sb + kOffClo + half_off + w * 1024;
+          const uint32_t rowsH = sb + kOffChi + half_off + w * 1024;   // the low part is the next slot
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const f2 cf = mul2(cp[i], bk);
             const uint32_t hi = cvt_bf2(cf);
             emit_pair(rowsH, i, hi);
-            emit_pair(rowsL, i, cvt_bf2(sub2(cf, widen_bf2(hi))));
+            emit_pair_next_slot(rowsH, i, cvt_bf2(sub2(cf, widen_bf2(hi))));
           }
         }
         warp_arrive(fK, lane);
@@ -776,17 +784,21 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
                        : "memory");
         };
-        // of the warp's 32 accumulator rows, row group g (8 rows) owns the g-th block of 8 columns:
-        // all four blocks are read, each lane keeps its own group's
+        // (each role reads its accumulator columns with ONE tcgen05.ld and one wait)
+        auto slice8 = [&](const float (&v)[32], int e, float (&o)[8]) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) o[x] = v[8 * e + x];
+        };
+        // of the warp's 32 accumulator rows, row group g (8 rows) owns the g-th block of 8 columns
         auto own_block = [&](uint32_t col0, float (&o)[8]) {
           const int grp = lane >> 3;
+          float v[32];
+          umma::tmem_ld32(lane_addr + col0, v);
+          umma::tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float b[8];
-            umma::tmem_ld8(lane_addr + col0 + 8 * g, b);
-            umma::tmem_ld_wait();
-#pragma unroll
-            for (int x = 0; x < 8; ++x) o[x] = (g == 0 || grp == g) ? b[x] : o[x];
+          for (int x = 0; x < 8; ++x) {
+            const float lo = (grp & 1) ? v[8 + x] : v[x], hi = (grp & 1) ? v[24 + x] : v[16 + x];
+            o[x] = (grp & 2) ? hi : lo;
           }
         };
         if (P == 0) {
@@ -805,11 +817,13 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             put8(64 * Q + 16 * (lane >> 3) + 8 + (lane & 7), 8 * Q + 2 * (lane >> 3), o);
           } else {
             // level 64: accumulator row 32 Q + lane is token 64 + 32 Q + lane; columns = tokens 0..63
+            float v[32];
+            umma::tmem_ld32(lane_addr + kColL2 + 32 * (P - 2), v);
+            umma::tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               float b[8];
-              umma::tmem_ld8(lane_addr + kColL2 + 32 * (P - 2) + 8 * e, b);
-              umma::tmem_ld_wait();
+              slice8(v, e, b);
               put8(64 + 32 * Q + lane, 4 * (P - 2) + e, b);
             }
           }
@@ -819,24 +833,27 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
             // level 16: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 (lane / 16) + 16 + lane % 16;
             // its partners are the 16 tokens before its 16-token half
             const int t = 64 * q2 + 32 * (lane >> 4) + 16 + (lane & 15);
+            float v[32];
+            umma::tmem_ld32(lane_addr + kColL1 + 64 + 32 * q2, v);
+            umma::tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              float b0[8], b1[8];
-              umma::tmem_ld8(lane_addr + kColL1 + 64 + 32 * q2 + 8 * e, b0);
-              umma::tmem_ld8(lane_addr + kColL1 + 64 + 32 * q2 + 16 + 8 * e, b1);
-              umma::tmem_ld_wait();
+              float b0[8];
 #pragma unroll
-              for (int x = 0; x < 8; ++x) b0[x] = (lane >> 4) ? b1[x] : b0[x];
+              for (int x = 0; x < 8; ++x) b0[x] = (lane >> 4) ? v[16 + 8 * e + x] : v[8 * e + x];
               put8(t, 8 * q2 + 4 * (lane >> 4) + e, b0);
             }
           } else {
             // level 32: accumulator row 64 + 32 q2 + lane is token 64 q2 + 32 + lane; partners: the 32
             // tokens before its half
+            float v[16];
+            umma::tmem_ld16(lane_addr + kColL2 + 64 + 32 * q2 + 16 * (P - 2), v);
+            umma::tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               float b[8];
-              umma::tmem_ld8(lane_addr + kColL2 + 64 + 32 * q2 + 16 * (P - 2) + 8 * e, b);
-              umma::tmem_ld_wait();
+#pragma unroll
+              for (int x = 0; x < 8; ++x) b[x] = v[8 * e + x];
               put8(64 * q2 + 32 + lane, 8 * q2 + 2 * (P - 2) + e, b);
             }
           }

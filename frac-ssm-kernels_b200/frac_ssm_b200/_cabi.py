@@ -60,6 +60,8 @@ _SIGNATURES = {
     "fracssm_scan_layer_norm": (ci, [vp, vp, vp, vp, ci, cf, i64, vp, i64, i64, i64, i64, vp]),
     "fracssm_causal_conv_silu": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, vp, ci, vp, ci, i64, i64, i64,
                                       i64, vp]),
+    "fracssm_causal_conv_silu_heads": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, vp, ci, vp, ci, vp, i64, i64, i64,
+                                            i64, i64, vp]),
     "fracssm_decode_step": (ci, [vp, ci, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]),
     "fracssm_scan_epilogue_sumsq": (ci, [vp, ci, i64, i64, vp, i64, i64, vp, i64, i64, ci, vp, cf, vp,
                                          i64, i64, i64, i64, vp]),

@@ -28,8 +28,10 @@ from .configuration_frac import FracConfig
 LayerCache = tuple  # (state [B, H, M, R] float32, conv_state [B, C, K-1])
 
 
-def causal_conv_silu(x, weight, bias, attention_mask=None):
-    """silu(depthwise causal conv) over channels-last x [B, L, C]; weight [C, 1, K] or [C, K]."""
+def causal_conv_silu(x, weight, bias, attention_mask=None, head_dim=None):
+    """silu(depthwise causal conv) over channels-last x [B, L, C]; weight [C, 1, K] or [C, K].
+    With `head_dim` R the kernel also writes the result head-major, u [B * C/R, L, R] (the scan's
+    input), and (y, u) is returned."""
     assert x.dim() == 3 and x.is_cuda, "x must be a 3D CUDA tensor"
     B, L, Cn = x.shape
     w = weight.detach().reshape(Cn, -1).contiguous()
@@ -41,14 +43,20 @@ def causal_conv_silu(x, weight, bias, attention_mask=None):
         assert attention_mask.shape == (B, L), "attention_mask shape must be (B, L)"
         mask = attention_mask.to(device=x.device, dtype=torch.float32)
     y = torch.empty(B, L, Cn, device=x.device, dtype=x.dtype)
-    if B == 0 or L == 0:
-        return y
-    with C.trace("causal_conv_silu"), torch.cuda.device(x.device):
-        C.check(C.lib().fracssm_causal_conv_silu(
-            C.ptr(x), C.dt(x), x.stride(0), x.stride(1), C.ptr(mask),
-            0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1), C.ptr(w),
-            C.ptr(b), C.dt(w), C.ptr(y), C.dt(y), B, L, Cn, K, C.stream_of(x)), "causal_conv_silu")
-    return y
+    u = None
+    R = 0
+    if head_dim is not None:
+        R = int(head_dim)
+        assert R > 0 and Cn % R == 0, "head_dim must divide the channel count"
+        u = torch.empty(B * (Cn // R), L, R, device=x.device, dtype=x.dtype)
+    if B > 0 and L > 0:
+        with C.trace("causal_conv_silu"), torch.cuda.device(x.device):
+            C.check(C.lib().fracssm_causal_conv_silu_heads(
+                C.ptr(x), C.dt(x), x.stride(0), x.stride(1), C.ptr(mask),
+                0 if mask is None else mask.stride(0), 0 if mask is None else mask.stride(1), C.ptr(w),
+                C.ptr(b), C.dt(w), C.ptr(y), C.dt(y), C.ptr(u), R, B, L, Cn, K, C.stream_of(x)),
+                "causal_conv_silu")
+    return y if head_dim is None else (y, u)
 
 
 def decode_step(u, c, kappa, rho, D, state):
@@ -110,7 +118,7 @@ class FracMixer(nn.Module):
         # Measured slower than scan + one-pass epilogue at the benchmark shapes, so off by default.
         self.fuse_gate_into_scan = False
 
-    def _scan_params(self, x_conv, x, attention_mask):
+    def _scan_params(self, x_conv, x, attention_mask, u=None):
         cfg = self.config
         dyn = F.linear(x, self.dyn_proj.weight, self.dyn_proj.bias)
         rw = F.linear(x_conv, self.rw_proj.weight)
@@ -119,7 +127,7 @@ class FracMixer(nn.Module):
             self.base_log_tau,
             self.num_heads, self.head_dim, self.num_modes, self.read_temp, cfg.frac_dt_min, cfg.frac_dt_max,
             cfg.frac_alpha_min, cfg.frac_alpha_max, cfg.frac_lambda_min, cfg.frac_lambda_max,
-            coeff_dtype=torch.float32 if self.coeff_dtype is None else self.coeff_dtype)
+            coeff_dtype=torch.float32 if self.coeff_dtype is None else self.coeff_dtype, u=u)
 
     def _conv_state_after(self, x, attention_mask):
         """The last K-1 (masked) inputs, channels first, zero-padded on the left."""
@@ -137,8 +145,9 @@ class FracMixer(nn.Module):
         x, gate = self.in_proj(hidden_states).chunk(2, dim=-1)
         gate_bias = float(self.config.frac_gate_bias_init)
         if layer_past is None and L > 1:
-            x_conv = causal_conv_silu(x, self.conv1d.weight, self.conv1d.bias, attention_mask)
-            u, c, kappa, rho = self._scan_params(x_conv, x, attention_mask)
+            # the convolution writes x_conv and its head-major copy u in one pass
+            x_conv, u = causal_conv_silu(x, self.conv1d.weight, self.conv1d.bias, attention_mask, head_dim=R)
+            u, c, kappa, rho = self._scan_params(x_conv, x, attention_mask, u=u)
             if self.fuse_gate_into_scan and scan_layer_supported(u, c, gate.contiguous()):
                 gate = gate.contiguous()
                 # scan, skip-mix and gated norm with the epilogue fused into the scan's output stage

@@ -187,7 +187,8 @@ int fracssm_frac_scan_noalloc_status(void *stream);
  * read_gate_logit, write_gate_logit: the two scalar parameters as DEVICE pointers to one float32 each,
  * as the reference passes them (frac_ssm/layers/compute_params.py:199-202): no host read of a
  * parameter, hence no synchronisation in the forward; the sigmoid is applied in the kernel.
- * Outputs head-major: u [Bt*H, L, R] (x dtype), rho [Bt*H, L, M] f32, c and kappa [Bt*H, L, M] in
+ * Outputs head-major: u [Bt*H, L, R] (x dtype; NULL when the caller already has it, see
+ * fracssm_causal_conv_silu_heads: x_conv is then not read), rho [Bt*H, L, M] f32, c and kappa [Bt*H, L, M] in
  * ck_dtype (f32 is what the reference emits; bf16 halves the scan's coefficient traffic).
  * Replaces the kernel behind frac_ssm/layers/compute_params.py:583
  * `frac_compute_scan_params(model, x_conv, x, attention_mask)` (:165-213).
@@ -291,6 +292,18 @@ int fracssm_causal_conv_silu(const void *x, int x_dtype, int64_t x_sb, int64_t x
                              int64_t m_sb, int64_t m_sl, const void *weight, const void *bias,
                              int w_dtype, void *y, int y_dtype, int64_t Bt, int64_t L, int64_t C,
                              int64_t K, void *stream);
+
+/*
+ * The same convolution, which also writes its result as the scan's head-major input
+ *   u_heads[(b*H + h), l, r] = y[b, l, h*R + r]   (H = C / R; same dtype as y; NULL: only y is written),
+ * so that fracssm_compute_params can be called with u = NULL and skips its copy of x_conv.
+ * Replaces frac_ssm/models/modeling_frac.py:116-140 together with the head-major copy of
+ * frac_ssm/layers/compute_params.py:154-164.
+ */
+int fracssm_causal_conv_silu_heads(const void *x, int x_dtype, int64_t x_sb, int64_t x_sl, const float *mask,
+                                   int64_t m_sb, int64_t m_sl, const void *weight, const void *bias,
+                                   int w_dtype, void *y, int y_dtype, void *u_heads, int64_t R, int64_t Bt,
+                                   int64_t L, int64_t C, int64_t K, void *stream);
 
 /*
  * One decode token for every (batch, head): state [Bt*H, M, R] float32 is updated in place,

@@ -72,6 +72,26 @@ def test_compute_params_larger(dtype):
         assert_ref_error(a, b, c_, 1e-4)
 
 
+@pytest.mark.parametrize("M", [128, 16])
+def test_compute_params_with_u_from_the_caller(M):
+    """A caller that already holds the head-major u (the convolution writes it) gets the same
+    coefficients, its own u back, and the kernel does not touch x_conv's copy."""
+    from frac_ssm_b200.layers import compute_params_from_projections
+    B, L, H, R = 2, 70, 4, 64
+    g = torch.Generator().manual_seed(9)
+    dyn = torch.randn(B, L, 3 * H, generator=g).bfloat16().cuda()
+    rw = torch.randn(B, L, 2 * H * M, generator=g).bfloat16().cuda()
+    x = torch.randn(B, L, H * R, generator=g).bfloat16().cuda()
+    dt_bias = torch.randn(H, generator=g).cuda()
+    log_tau = torch.linspace(0.0, 11.09, M).cuda()
+    args = (dyn, rw, x, None, dt_bias, -2.0, -1.1, log_tau, H, R, M, 1.0, *CFG.values())
+    u0, c0, k0, r0 = compute_params_from_projections(*args)
+    mine = torch.full((B * H, L, R), 3.0, device="cuda", dtype=torch.bfloat16)
+    u1, c1, k1, r1 = compute_params_from_projections(*args, u=mine)
+    assert u1 is mine and torch.all(mine == 3.0)
+    assert torch.equal(c0, c1) and torch.equal(k0, k1) and torch.equal(r0, r1)
+
+
 @pytest.mark.parametrize("coeff", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("masked", [False, True])
 def test_compute_params_128_modes_one_pass_kernel(coeff, masked):

@@ -95,6 +95,25 @@ def test_causal_conv_silu_matches_conv1d(dtype, C_, K, masked):
     close(y, ref, **tol)
 
 
+@pytest.mark.parametrize("dtype,H,R,K", [(torch.bfloat16, 24, 64, 4), (torch.bfloat16, 3, 24, 4), (torch.float32, 5, 20, 4),
+                                        (torch.bfloat16, 6, 12, 3)])
+def test_causal_conv_silu_also_writes_u_head_major(dtype, H, R, K):
+    """With head_dim the convolution writes its result a second time as the scan's head-major input:
+    exactly the values of y, at [(b*H + h), l, r] (16-byte path, general path and odd widths)."""
+    from frac_ssm_b200.models.modeling_frac import causal_conv_silu
+    B, L, C_ = 2, 77, H * R
+    g = torch.Generator().manual_seed(H + R)
+    x = torch.randn(B, L, C_, generator=g).to(dtype).cuda()
+    w = (0.5 * torch.randn(C_, 1, K, generator=g)).to(dtype).cuda()
+    b = (0.1 * torch.randn(C_, generator=g)).to(dtype).cuda()
+    mask = torch.ones(B, L, dtype=torch.long)
+    mask[1, :10] = 0
+    y, u = causal_conv_silu(x, w, b, mask.cuda(), head_dim=R)
+    assert torch.equal(y, causal_conv_silu(x, w, b, mask.cuda()))
+    assert u.shape == (B * H, L, R)
+    assert torch.equal(u, y.view(B, L, H, R).permute(0, 2, 1, 3).reshape(B * H, L, R))
+
+
 @pytest.mark.parametrize("B,H,R,M", [(2, 24, 64, 128), (3, 2, 32, 16), (1, 5, 20, 7)])
 def test_decode_step_matches_token_recurrence(B, H, R, M):
     from frac_ssm_b200.models.modeling_frac import decode_step
