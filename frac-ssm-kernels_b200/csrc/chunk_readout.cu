@@ -1,8 +1,9 @@
 // Chunk readout on CUDA cores, any shape and dtype (the general path), in two flavours:
 //   plain: h = (c * exp(lcr)) . states_acc^T + W . u with W read from memory
-//   fused: the 32x32 tiles of W are formed in shared memory and never stored
-// One block of 256 threads owns a 32(token) x 64(r) tile of h.  Thread (tx, ty) holds
-// tokens {2ty, 2ty+1} x rows {4tx .. 4tx+3}.
+//          (chunk_readout_kernel: one block of 256 threads owns a 32(token) x 64(r) tile of h, thread
+//          (tx, ty) holds tokens {2ty, 2ty+1} x columns {4tx .. 4tx+3})
+//   fused: the tiles of W are formed in shared memory and never stored
+//          (chunk_fused_readout_kernel, 64-token tiles, described at the kernel)
 #include "common.cuh"
 
 namespace fracssm {
@@ -19,7 +20,6 @@ struct ReadoutArgs {
   int r_tiles;
 };
 
-template <bool FUSED>
 __global__ void __launch_bounds__(256) chunk_readout_kernel(const ReadoutArgs a) {
   const int ti = blockIdx.x / a.r_tiles;
   const int r0 = (blockIdx.x % a.r_tiles) * 64;
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) chunk_readout_kernel(const ReadoutArgs a)
   const int64_t len = min(a.T, a.L - t0);
   const int64_t M = a.M, R = a.R;
 
-  __shared__ float gt[32][33], ct[32][33], gk[32][33], kk[32][33];
+  __shared__ float ct[32][33];
   __shared__ float wt[32][33];
   __shared__ float ss[64][33];
   __shared__ __align__(16) float us[32][64];
@@ -68,47 +68,12 @@ __global__ void __launch_bounds__(256) chunk_readout_kernel(const ReadoutArgs a)
 
   // local part: W . u over the token tiles at or before this one
   for (int kt = 0; kt <= ti; ++kt) {
-    if (FUSED) {
-      float wacc[4] = {0.f, 0.f, 0.f, 0.f};
-      const int kx = tid % 32, tyb = tid / 32;  // entries (t = tyb + 8 i, k = kx)
-      for (int64_t m0 = 0; m0 < M; m0 += 32) {
-        __syncthreads();
-        for (int i = tid; i < 32 * 32; i += 256) {
-          int rr = i / 32, mm = i % 32;
-          int64_t m = m0 + mm;
-          int64_t row_t = (int64_t)ti * 32 + rr, row_k = (int64_t)kt * 32 + rr;
-          const bool mv = m < M;
-          const int64_t rt = min(row_t, len - 1), rk = min(row_k, len - 1);
-          gt[rr][mm] = mv ? a.lcr[b * a.g_sb + (t0 + rt) * a.g_sl + m] * kLog2e : 0.f;
-          gk[rr][mm] = mv ? a.lcr[b * a.g_sb + (t0 + rk) * a.g_sl + m] * kLog2e : 0.f;
-          ct[rr][mm] = (mv && row_t < len) ? ld_f32(a.c, b * a.c_sb + (t0 + row_t) * a.c_sl + m, a.c_dt) : 0.f;
-          kk[rr][mm] = (mv && row_k < len) ? ld_f32(a.kappa, b * a.k_sb + (t0 + row_k) * a.k_sl + m, a.c_dt) : 0.f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int tt = tyb + 8 * i;
-          if (kt < ti || kx <= tt) {
-#pragma unroll 8
-            for (int mm = 0; mm < 32; ++mm)
-              wacc[i] = fmaf(ct[tt][mm] * kk[kx][mm], exp2f(gt[tt][mm] - gk[kx][mm]), wacc[i]);
-          }
-        }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int tt = tyb + 8 * i;
-        wt[tt][kx] = (kt < ti || kx <= tt) ? wacc[i] : 0.f;
-      }
-    } else {
-      __syncthreads();
-      for (int i = tid; i < 32 * 32; i += 256) {
-        int tt = i / 32, kx = i % 32;
-        int64_t t = (int64_t)ti * 32 + tt, k = (int64_t)kt * 32 + kx;
-        wt[tt][kx] = (t < a.T && k < a.T)
-                         ? ld_f32(a.W, ((b * a.N + n) * a.T + t) * a.T + k, a.w_dt) : 0.f;
-      }
+    __syncthreads();
+    for (int i = tid; i < 32 * 32; i += 256) {
+      int tt = i / 32, kx = i % 32;
+      int64_t t = (int64_t)ti * 32 + tt, k = (int64_t)kt * 32 + kx;
+      wt[tt][kx] = (t < a.T && k < a.T)
+                       ? ld_f32(a.W, ((b * a.N + n) * a.T + t) * a.T + k, a.w_dt) : 0.f;
     }
     for (int i = tid; i < 32 * 64; i += 256) {
       int kx = i / 64, rr = i % 64;
@@ -139,13 +104,166 @@ __global__ void __launch_bounds__(256) chunk_readout_kernel(const ReadoutArgs a)
   }
 }
 
+// The fused flavour on 64-token tiles: one block of 256 threads owns a 64(token) x 64(r) tile of h,
+// thread (tx, ty) holds tokens 4ty .. 4ty+3 x columns 4tx .. 4tx+3.  Operands are staged transposed
+// ([mode][token]) so that a thread reads its four tokens with one 16-byte load.  For every 64-token
+// tile of W at or before the block's own: the tile is formed on 4 x 4 register tiles (below the
+// diagonal as a plain product of two factors that are both <= 1, reference point = last token of the
+// k tile, one exponential per staged element; on the diagonal with one exponential per (t, k, m)),
+// written transposed to shared memory, and multiplied with the u tile.  The staging buffers are
+// reused for the W tile (the two exponent arrays) and the u tile (the two value arrays).
+__global__ void __launch_bounds__(256) chunk_fused_readout_kernel(const ReadoutArgs a) {
+  constexpr int kT = 64, kMs = 32, kPad = 68;
+  const int ti = blockIdx.x / a.r_tiles;
+  const int r0 = (blockIdx.x % a.r_tiles) * 64;
+  const int64_t n = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const int64_t t0 = n * a.T;
+  const int64_t len = min(a.T, a.L - t0);
+  const int64_t M = a.M, R = a.R;
+  const int64_t tb = (int64_t)ti * kT;
+
+  __shared__ __align__(16) float sm[4][kMs][kPad];
+  float (*ct)[kPad] = sm[0], (*kk)[kPad] = sm[1], (*gt)[kPad] = sm[2], (*gk)[kPad] = sm[3];
+  float (*wT)[kPad] = sm[2];                                      // [k][t], 64 rows: spans sm[2] and sm[3]
+  float (*us)[kT] = reinterpret_cast<float (*)[kT]>(&sm[0][0][0]);  // [k][r], 64 x 64 floats inside sm[0..1]
+
+  float acc[4][4] = {};
+
+  // carried part: (c * exp(lcr)) . states_acc^T
+  for (int64_t m0 = 0; m0 < M; m0 += kMs) {
+    __syncthreads();
+    for (int i = tid; i < kT * kMs; i += 256) {
+      // a warp takes 8 modes x 4 rows: 32-byte pieces of four rows from memory, 32 distinct banks in the
+      // transposed shared-memory arrays (row stride 68 floats)
+      const int blk = i >> 5, ln = i & 31;
+      const int mm = 8 * (blk & 3) + (ln & 7), rr = 4 * (blk >> 2) + (ln >> 3);
+      const int64_t t = tb + rr, m = m0 + mm, r = r0 + rr;
+      float v = 0.f;
+      if (t < len && m < M)
+        v = ld_f32(a.c, b * a.c_sb + (t0 + t) * a.c_sl + m, a.c_dt) * __expf(a.lcr[b * a.g_sb + (t0 + t) * a.g_sl + m]);
+      ct[mm][rr] = v;
+      kk[mm][rr] = (r < R && m < M) ? ld_f32(a.acc, ((b * a.N + n) * R + r) * M + m, a.a_dt) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int mm = 0; mm < kMs; ++mm) {
+      const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
+      const float4 b4 = *reinterpret_cast<const float4 *>(&kk[mm][4 * tx]);
+      const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+  }
+
+  // local part: W . u over the 64-token tiles at or before this one
+  for (int kt = 0; kt <= ti; ++kt) {
+    const int64_t kb = (int64_t)kt * kT;
+    const bool below = kt < ti;
+    const int64_t rref = min(kb + kT - 1, len - 1);
+    float wacc[4][4] = {};   // W[t = 4ty + i][k = 4tx + j] of this tile
+    for (int64_t m0 = 0; m0 < M; m0 += kMs) {
+      __syncthreads();
+      for (int i = tid; i < kT * kMs; i += 256) {
+        // a warp takes 8 modes x 4 rows: 32-byte pieces of four rows from memory, 32 distinct banks in the
+      // transposed shared-memory arrays (row stride 68 floats)
+      const int blk = i >> 5, ln = i & 31;
+      const int mm = 8 * (blk & 3) + (ln & 7), rr = 4 * (blk >> 2) + (ln >> 3);
+        const int64_t m = m0 + mm;
+        const bool mv = m < M;
+        const int64_t row_t = tb + rr, row_k = kb + rr;
+        const int64_t rt = min(row_t, len - 1), rk = min(row_k, len - 1);
+        const float g_t = mv ? a.lcr[b * a.g_sb + (t0 + rt) * a.g_sl + m] * kLog2e : 0.f;
+        const float g_k = mv ? a.lcr[b * a.g_sb + (t0 + rk) * a.g_sl + m] * kLog2e : 0.f;
+        float c_v = (mv && row_t < len) ? ld_f32(a.c, b * a.c_sb + (t0 + row_t) * a.c_sl + m, a.c_dt) : 0.f;
+        float k_v = (mv && row_k < len) ? ld_f32(a.kappa, b * a.k_sb + (t0 + row_k) * a.k_sl + m, a.c_dt) : 0.f;
+        if (below) {
+          const float g_r = mv ? a.lcr[b * a.g_sb + (t0 + rref) * a.g_sl + m] * kLog2e : 0.f;
+          c_v *= exp2f(g_t - g_r);
+          k_v *= exp2f(g_r - g_k);
+        } else {
+          gt[mm][rr] = g_t;
+          gk[mm][rr] = g_k;
+        }
+        ct[mm][rr] = c_v;
+        kk[mm][rr] = k_v;
+      }
+      __syncthreads();
+      if (below) {
+#pragma unroll 8
+        for (int mm = 0; mm < kMs; ++mm) {
+          const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
+          const float4 b4 = *reinterpret_cast<const float4 *>(&kk[mm][4 * tx]);
+          const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wacc[i][j] = fmaf(av[i], bv[j], wacc[i][j]);
+        }
+      } else if (tx <= ty) {   // (a 4 x 4 register tile wholly above the diagonal stays zero)
+#pragma unroll 4
+        for (int mm = 0; mm < kMs; ++mm) {
+          const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
+          const float4 b4 = *reinterpret_cast<const float4 *>(&kk[mm][4 * tx]);
+          const float4 p4 = *reinterpret_cast<const float4 *>(&gt[mm][4 * ty]);
+          const float4 q4 = *reinterpret_cast<const float4 *>(&gk[mm][4 * tx]);
+          const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+          const float pv[4] = {p4.x, p4.y, p4.z, p4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              wacc[i][j] = fmaf(av[i] * bv[j], exp2f(fminf(pv[i] - qv[j], 0.f)), wacc[i][j]);
+        }
+      }
+    }
+    __syncthreads();   // every thread is done with the staging buffers: they become the W and u tiles
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = 4 * tx + j, t = 4 * ty;
+      *reinterpret_cast<float4 *>(&wT[k][t]) =
+          make_float4((below || k <= t) ? wacc[0][j] : 0.f, (below || k <= t + 1) ? wacc[1][j] : 0.f,
+                      (below || k <= t + 2) ? wacc[2][j] : 0.f, (below || k <= t + 3) ? wacc[3][j] : 0.f);
+    }
+    for (int i = tid; i < kT * 64; i += 256) {
+      const int kx = i / 64, rr = i % 64;
+      const int64_t k = kb + kx, r = r0 + rr;
+      us[kx][rr] = (k < len && r < R) ? ld_f32(a.u, b * a.u_sb + (t0 + k) * a.u_sl + r, a.u_dt) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kx = 0; kx < kT; ++kx) {
+      const float4 w4 = *reinterpret_cast<const float4 *>(&wT[kx][4 * ty]);
+      const float4 x = *reinterpret_cast<const float4 *>(&us[kx][4 * tx]);
+      const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(wv[i], xv[j], acc[i][j]);
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t t = tb + 4 * ty + i;
+    if (t >= len) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t r = r0 + 4 * tx + j;
+      if (r < R) st_f32(a.h, (b * a.L + t0 + t) * R + r, a.u_dt, acc[i][j]);
+    }
+  }
+}
+
 static int launch_readout(bool fused, const ReadoutArgs &a, int64_t B, void *stream) {
-  const int tiles = (int)ceil_div(a.T, 32);
+  const int tiles = (int)ceil_div(a.T, fused ? 64 : 32);
   if (B > 65535 || a.N > 65535)
     return fail(FRACSSM_ERR_UNSUPPORTED, "chunk_readout: B or N too large for one launch");
   dim3 grid((unsigned)(tiles * a.r_tiles), (unsigned)a.N, (unsigned)B);
-  if (fused) chunk_readout_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
-  else chunk_readout_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  if (fused) chunk_fused_readout_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  else chunk_readout_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
   return check_launch(fused ? "chunk_fused_readout" : "chunk_readout");
 }
 

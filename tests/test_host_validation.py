@@ -92,3 +92,19 @@ def test_misaligned_pointers_are_refused_before_any_launch():
         rc = lib.fracssm_segment_summary(ptrs[0], ptrs[1], C.BF16, ptrs[2], None, ok, ok, ws, need,
                                          2, 256, 64, 128, None)
         assert rc == 1 and b"16-byte aligned" in lib.fracssm_last_error()
+
+
+def test_conv_head_width_and_missing_pointers_are_argument_errors():
+    """fracssm_causal_conv_silu_heads: a head width that does not divide the channels is refused, and
+    fracssm_compute_params may leave out u but nothing else (made-up addresses: nothing runs)."""
+    import ctypes
+    from frac_ssm_b200 import _cabi as C
+    lib = C.lib()
+    ok = ctypes.c_void_p(0x10000)
+    rc = lib.fracssm_causal_conv_silu_heads(ok, C.BF16, 1536, 1536, None, 0, 0, ok, None, C.BF16, ok, C.BF16,
+                                            ok, 100, 1, 16, 1536, 4, None)
+    assert rc == 1 and b"head width" in lib.fracssm_last_error()
+    rc = lib.fracssm_compute_params(ok, C.BF16, 72, 72, ok, C.BF16, 6144, 6144, None, C.BF16, 0, 0, None, 0, 0,
+                                    ok, ok, ok, ok, 1.0, 1e-3, 0.1, 0.3, 0.9, 0.25, 4.0, None, None, ok, C.BF16,
+                                    ok, 1, 16, 24, 64, 128, None)
+    assert rc == 1 and b"null pointer" in lib.fracssm_last_error()
