@@ -123,8 +123,8 @@ __global__ void __launch_bounds__(256) chunk_fused_readout_kernel(const ReadoutA
   const int64_t M = a.M, R = a.R;
   const int64_t tb = (int64_t)ti * kT;
 
-  __shared__ __align__(16) float sm[4][kMs][kPad];
-  float (*ct)[kPad] = sm[0], (*kk)[kPad] = sm[1], (*gt)[kPad] = sm[2], (*gk)[kPad] = sm[3];
+  __shared__ __align__(16) float sm[5][kMs][kPad];
+  float (*ct)[kPad] = sm[0], (*kk)[kPad] = sm[1], (*gt)[kPad] = sm[2], (*gk)[kPad] = sm[3], (*kk2)[kPad] = sm[4];
   float (*wT)[kPad] = sm[2];                                      // [k][t], 64 rows: spans sm[2] and sm[3]
   float (*us)[kT] = reinterpret_cast<float (*)[kT]>(&sm[0][0][0]);  // [k][r], 64 x 64 floats inside sm[0..1]
 
@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(256) chunk_fused_readout_kernel(const ReadoutA
     const bool below = kt < ti;
     const int64_t rref = min(kb + kT - 1, len - 1);
     float wacc[4][4] = {};   // W[t = 4ty + i][k = 4tx + j] of this tile
+    float dacc = 0.f;        // diagonal tile: entry (4d + i, 4d + j), d = tid / 16, of the register tiles on the diagonal
     for (int64_t m0 = 0; m0 < M; m0 += kMs) {
       __syncthreads();
       for (int i = tid; i < kT * kMs; i += 256) {
@@ -186,6 +187,9 @@ __global__ void __launch_bounds__(256) chunk_fused_readout_kernel(const ReadoutA
         } else {
           gt[mm][rr] = g_t;
           gk[mm][rr] = g_k;
+          // kappa taken to the last token of its group of four rows (in lanes 24..31 of this warp)
+          const float g_4 = __shfl_sync(0xffffffffu, g_k, 24 + (ln & 7));
+          kk2[mm][rr] = k_v * exp2f(fminf(g_4 - g_k, 0.f));
         }
         ct[mm][rr] = c_v;
         kk[mm][rr] = k_v;
@@ -202,30 +206,45 @@ __global__ void __launch_bounds__(256) chunk_fused_readout_kernel(const ReadoutA
 #pragma unroll
             for (int j = 0; j < 4; ++j) wacc[i][j] = fmaf(av[i], bv[j], wacc[i][j]);
         }
-      } else if (tx <= ty) {   // (a 4 x 4 register tile wholly above the diagonal stays zero)
+      } else {
+        // the diagonal tile, as in chunk_w.cu: register tiles strictly below the diagonal with the
+        // last k of their group as reference point, the 16 register tiles on the diagonal one entry
+        // per thread
+        if (tx < ty) {
 #pragma unroll 4
-        for (int mm = 0; mm < kMs; ++mm) {
-          const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
-          const float4 b4 = *reinterpret_cast<const float4 *>(&kk[mm][4 * tx]);
-          const float4 p4 = *reinterpret_cast<const float4 *>(&gt[mm][4 * ty]);
-          const float4 q4 = *reinterpret_cast<const float4 *>(&gk[mm][4 * tx]);
-          const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
-          const float pv[4] = {p4.x, p4.y, p4.z, p4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+          for (int mm = 0; mm < kMs; ++mm) {
+            const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
+            const float4 p4 = *reinterpret_cast<const float4 *>(&gt[mm][4 * ty]);
+            const float4 b4 = *reinterpret_cast<const float4 *>(&kk2[mm][4 * tx]);
+            const float g_r = gk[mm][4 * tx + 3];
+            const float av[4] = {a4.x * exp2f(fminf(p4.x - g_r, 0.f)), a4.y * exp2f(fminf(p4.y - g_r, 0.f)),
+                                 a4.z * exp2f(fminf(p4.z - g_r, 0.f)), a4.w * exp2f(fminf(p4.w - g_r, 0.f))};
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              wacc[i][j] = fmaf(av[i] * bv[j], exp2f(fminf(pv[i] - qv[j], 0.f)), wacc[i][j]);
+              for (int j = 0; j < 4; ++j) wacc[i][j] = fmaf(av[i], bv[j], wacc[i][j]);
+          }
+        }
+        {
+          const int d = tid >> 4, i = (tid >> 2) & 3, j = tid & 3;
+          if (j <= i) {
+#pragma unroll 8
+            for (int mm = 0; mm < kMs; ++mm)
+              dacc = fmaf(ct[mm][4 * d + i] * kk[mm][4 * d + j], exp2f(gt[mm][4 * d + i] - gk[mm][4 * d + j]), dacc);
+          }
         }
       }
     }
     __syncthreads();   // every thread is done with the staging buffers: they become the W and u tiles
+    if (below || tx != ty) {   // (register tiles above the diagonal hold zeros)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int k = 4 * tx + j, t = 4 * ty;
-      *reinterpret_cast<float4 *>(&wT[k][t]) =
-          make_float4((below || k <= t) ? wacc[0][j] : 0.f, (below || k <= t + 1) ? wacc[1][j] : 0.f,
-                      (below || k <= t + 2) ? wacc[2][j] : 0.f, (below || k <= t + 3) ? wacc[3][j] : 0.f);
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<float4 *>(&wT[4 * tx + j][4 * ty]) = make_float4(wacc[0][j], wacc[1][j], wacc[2][j], wacc[3][j]);
+    }
+    if (!below) {
+      const int d = tid >> 4, i = (tid >> 2) & 3, j = tid & 3;
+      wT[4 * d + j][4 * d + i] = (j <= i) ? dacc : 0.f;
     }
     for (int i = tid; i < kT * 64; i += 256) {
       const int kx = i / 64, rr = i % 64;

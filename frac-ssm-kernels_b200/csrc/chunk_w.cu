@@ -29,8 +29,10 @@ chunk_w_kernel(const void *__restrict__ c, const void *__restrict__ kappa, int c
   float *out = W + ((b * N + n) * T) * T;
   const int64_t tb = (int64_t)ti * kWt, kb = (int64_t)tk * kWt;
   float acc[4][4] = {};
+  float dacc = 0.f;   // diagonal tile: the entry (t, k) = (4d + i, 4d + j), d = tid / 16, of the register tiles on the diagonal
   if (tk <= ti) {
-    __shared__ __align__(16) float ct[kWm][kWt + 4], kk[kWm][kWt + 4], gt[kWm][kWt + 4], gk[kWm][kWt + 4];
+    __shared__ __align__(16) float ct[kWm][kWt + 4], kk[kWm][kWt + 4], gt[kWm][kWt + 4], gk[kWm][kWt + 4],
+        kk2[kWm][kWt + 4];
     const int64_t t0 = n * T;
     const int64_t len = min(T, L - t0);
     const bool below = tk < ti;
@@ -57,6 +59,10 @@ chunk_w_kernel(const void *__restrict__ c, const void *__restrict__ kappa, int c
         } else {
           gt[mm][rr] = g_t;
           gk[mm][rr] = g_k;
+          // kappa taken to the last token of its group of four rows (the warp holds the four rows of
+          // a group for 8 modes: the group's last row is in lanes 24..31)
+          const float g_4 = __shfl_sync(0xffffffffu, g_k, 24 + (ln & 7));
+          kk2[mm][rr] = k_v * exp2f(fminf(g_4 - g_k, 0.f));
         }
         ct[mm][rr] = c_v;
         kk[mm][rr] = k_v;
@@ -73,33 +79,54 @@ chunk_w_kernel(const void *__restrict__ c, const void *__restrict__ kappa, int c
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
-      } else if (tx <= ty) {   // (a 4 x 4 register tile wholly above the diagonal is skipped)
+      } else {
+        // On the diagonal tile: a 4 x 4 register tile strictly below the diagonal (all its k before
+        // all its t) takes the last k of its group as reference point: four exponentials per mode for
+        // the thread's t rows, the k side comes scaled from the staging.  The 16 register tiles ON the
+        // diagonal are done afterwards, one entry per thread, with one exponential per (t, k, m).
+        if (tx < ty) {
 #pragma unroll 4
-        for (int mm = 0; mm < kWm; ++mm) {
-          const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
-          const float4 b4 = *reinterpret_cast<const float4 *>(&kk[mm][4 * tx]);
-          const float4 p4 = *reinterpret_cast<const float4 *>(&gt[mm][4 * ty]);
-          const float4 q4 = *reinterpret_cast<const float4 *>(&gk[mm][4 * tx]);
-          const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
-          const float pv[4] = {p4.x, p4.y, p4.z, p4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+          for (int mm = 0; mm < kWm; ++mm) {
+            const float4 a4 = *reinterpret_cast<const float4 *>(&ct[mm][4 * ty]);
+            const float4 p4 = *reinterpret_cast<const float4 *>(&gt[mm][4 * ty]);
+            const float4 b4 = *reinterpret_cast<const float4 *>(&kk2[mm][4 * tx]);
+            const float g_r = gk[mm][4 * tx + 3];
+            const float av[4] = {a4.x * exp2f(fminf(p4.x - g_r, 0.f)), a4.y * exp2f(fminf(p4.y - g_r, 0.f)),
+                                 a4.z * exp2f(fminf(p4.z - g_r, 0.f)), a4.w * exp2f(fminf(p4.w - g_r, 0.f))};
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              acc[i][j] = fmaf(av[i] * bv[j], exp2f(fminf(pv[i] - qv[j], 0.f)), acc[i][j]);
+              for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+          }
+        }
+        {
+          const int d = tid >> 4, i = (tid >> 2) & 3, j = tid & 3;
+          if (j <= i) {
+#pragma unroll 8
+            for (int mm = 0; mm < kWm; ++mm)
+              dacc = fmaf(ct[mm][4 * d + i] * kk[mm][4 * d + j], exp2f(gt[mm][4 * d + i] - gk[mm][4 * d + j]), dacc);
+          }
         }
       }
     }
   }
+  if (tk != ti || tx != ty) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t t = tb + 4 * ty + i;
-    if (t >= T) continue;
+    for (int i = 0; i < 4; ++i) {
+      const int64_t t = tb + 4 * ty + i;
+      if (t >= T) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int64_t k = kb + 4 * tx + j;
-      if (k < T) out[t * T + k] = (k <= t) ? acc[i][j] : 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const int64_t k = kb + 4 * tx + j;
+        if (k < T) out[t * T + k] = (k <= t) ? acc[i][j] : 0.f;
+      }
     }
+  }
+  if (tk == ti) {
+    const int d = tid >> 4, i = (tid >> 2) & 3, j = tid & 3;
+    const int64_t t = tb + 4 * d + i, k = kb + 4 * d + j;
+    if (t < T && k < T) out[t * T + k] = (j <= i) ? dacc : 0.f;
   }
 }
 
