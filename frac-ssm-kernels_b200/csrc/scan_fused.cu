@@ -169,10 +169,10 @@ template <int OFF>
 __device__ __forceinline__ void ldg_stream_at(uint32_t &d, const void *p) {
   asm volatile("ld.global.L1::no_allocate.b32 %0, [%1+%2];" : "=r"(d) : "l"(p), "n"(OFF));
 }
-template <bool CKF32, int I>
+template <bool CKF32, bool RAGGED, int I>
 __device__ __forceinline__ void load_tok2(RawHalf<CKF32> &raw, const FusedArgs &a, int bh, int t0, int w, int lane,
                                           int h) {
-  if (t0 + kTile <= a.L) {
+  if (!RAGGED || t0 + kTile <= a.L) {
     constexpr int kCk = CKF32 ? 4 : 2;
     const int64_t e = (static_cast<int64_t>(bh) * a.L + t0 + 8 * w) * kM + 64 * h + 2 * lane;   // row 0 of the segment
     const float *rp = a.rho + e;
@@ -185,8 +185,10 @@ __device__ __forceinline__ void load_tok2(RawHalf<CKF32> &raw, const FusedArgs &
     ldg_stream_at<(I + 1) * kM * kCk>(raw.k[I + 1], kp);
     return;
   }
-  load_tok(raw, a, bh, t0, w, lane, h, I);
-  load_tok(raw, a, bh, t0, w, lane, h, I + 1);
+  if constexpr (RAGGED) {
+    load_tok(raw, a, bh, t0, w, lane, h, I);
+    load_tok(raw, a, bh, t0, w, lane, h, I + 1);
+  }
 }
 
 __device__ __forceinline__ f2 floor2(f2 v) {
@@ -210,7 +212,9 @@ __device__ __forceinline__ void emit_pair_next_slot(uint32_t rows_s, int i, uint
 
 // CKF32: c and kappa are float32 (else bf16).  LAYER: the output stage applies the skip connection and
 // the gate (its code is kept out of the plain kernel, whose loop is fetched once per tile).
-template <bool CKF32, bool LAYER>
+// RAGGED: L is not a multiple of the tile, so a row's last tile takes the row-by-row, predicated loads
+// (kept out of the other instances: the loop's code is fetched once per tile and its size counts).
+template <bool CKF32, bool LAYER, bool RAGGED>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -646,8 +650,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         // (in two batches of four token rows: one batch, and four batches of two, measured slower)
         auto request_other_half = [&](auto i) {
           if (h == 0) {
-            load_tok2<CKF32, decltype(i)::value>(raw, a, bh, t0, w, lane, 1);
-            load_tok2<CKF32, decltype(i)::value + 2>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, RAGGED, decltype(i)::value>(raw, a, bh, t0, w, lane, 1);
+            load_tok2<CKF32, RAGGED, decltype(i)::value + 2>(raw, a, bh, t0, w, lane, 1);
           }
         };
         request_other_half(std::integral_constant<int, 0>{});
@@ -765,8 +769,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
       const int nbh = next - nj * a.BH, nt0 = (nj + a.first_tile) * kTile;
       auto request_next = [&](auto i) {   // four token rows of the next item's first half
         if (more) {
-          load_tok2<CKF32, decltype(i)::value>(raw, a, nbh, nt0, w, lane, 0);
-          load_tok2<CKF32, decltype(i)::value + 2>(raw, a, nbh, nt0, w, lane, 0);
+          load_tok2<CKF32, RAGGED, decltype(i)::value>(raw, a, nbh, nt0, w, lane, 0);
+          load_tok2<CKF32, RAGGED, decltype(i)::value + 2>(raw, a, nbh, nt0, w, lane, 0);
         }
       };
       request_next(std::integral_constant<int, 0>{});
@@ -995,10 +999,12 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   {
     std::lock_guard<std::mutex> lock(mu);
     if (sm_count[dev] == 0) {
-      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, true>));
-      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, true>));
+      int prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false, false>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, false, true>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, false, true>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<false, true, true>));
+      if (prc == FRACSSM_OK) prc = prepare(reinterpret_cast<const void *>(&scan_fused_kernel<true, true, true>));
       if (prc) return prc;
       int n = 0;
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -1043,11 +1049,17 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
   const int grid = a.total < sms ? a.total : sms;
   const cudaStream_t st = (cudaStream_t)stream;
   if (a.gate != nullptr) {
-    if (ckf32) scan_fused_kernel<true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-    else scan_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    if (ckf32) scan_fused_kernel<true, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    else scan_fused_kernel<false, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
   } else {
-    if (ckf32) scan_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
-    else scan_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    const bool ragged = a.L % kTile != 0;
+    if (ragged) {
+      if (ckf32) scan_fused_kernel<true, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+      else scan_fused_kernel<false, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    } else {
+      if (ckf32) scan_fused_kernel<true, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+      else scan_fused_kernel<false, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    }
   }
   return check_launch("frac_scan (single-pass kernel)");
 }
