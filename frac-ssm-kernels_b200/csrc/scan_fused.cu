@@ -12,9 +12,8 @@
 // One CTA per SM, 20 warps.  Warps 0-15 ("workers") turn the raw inputs into bf16 operand tiles in
 // shared memory and run the epilogues; warp 16 ("MMA warp") issues the TMA load of u and every
 // tcgen05.mma; warp 17 ("chain warp") takes the tickets, pulls the next item into L2 and hands the
-// state from tile to tile of a row (polls and releases the per-row counter); warp 18 ("store warp")
-// writes a tile's output rows, which the workers stage in shared memory, with one TMA tile store;
-// warp 19 only pads the register group of the service warps.  Workers hand a batch of tiles over by arriving on a "full"
+// state from tile to tile of a row (polls and releases the per-row counter); warps 18-19 only pad
+// the register group of those two.  Workers hand a batch of tiles over by arriving on a "full"
 // mbarrier (one arrival per warp, after a proxy fence); the MMA warp hands buffers and accumulators
 // back through tcgen05.commit mbarriers.  The MMA warp passes through its code once per tile, so that
 // code is kept small (rolled loops over the contraction steps, issued from one elected lane, which
@@ -50,8 +49,6 @@
 //   slot 0 / 1: base A / B factors        -> Khat high / low   (after the base product)
 //   slot 2 / 3: levels 8+16, A / B rows   -> Chat high / low   (after the level-8/16 product)
 //   slot 4 / 5: levels 64+32, A / B rows  -> W / incoming state high|low (after that product)
-// plus a third use of slot 4's second half: the previous tile's output rows wait there for the TMA
-// store from the end of that tile's products until the second pass writes the half again.
 // Tensor memory (fp32 columns): base 0..127, tile's own state contribution 128..191, levels 8+16
 // 192..319, levels 64+32 320..447, output accumulator H 448..511.
 #include <cstdlib>
@@ -81,8 +78,6 @@ constexpr uint32_t kOffA0 = 0, kOffB0 = kSlot, kOffY1 = 2 * kSlot, kOffZ1 = 3 * 
                    kOffZ2 = 5 * kSlot;
 constexpr uint32_t kOffKhi = kOffA0, kOffKlo = kOffB0, kOffChi = kOffY1, kOffClo = kOffZ1, kOffW = kOffY2,
                    kOffS = kOffZ2;              // second use of each slot
-constexpr uint32_t kOffStage = kOffY2 + 16384;  // output rows of the previous tile (the second half of slot 4, which
-                                                // is next written in the tile's second pass)
 constexpr uint32_t kOffU = 6 * kSlot;           // u tile, 128 tokens x 64 bf16
 constexpr uint32_t kOffSeg = kOffU + 16384;     // float [16][128]: decay product of each 8-token segment
 constexpr uint32_t kOffMisc = kOffSeg + 8192;   // mbarriers, TMEM base, tickets, failure flag
@@ -221,8 +216,7 @@ __device__ __forceinline__ void emit_pair_next_slot(uint32_t rows_s, int i, uint
 // (kept out of the other instances: the loop's code is fetched once per tile and its size counts).
 template <bool CKF32, bool LAYER, bool RAGGED>
 __global__ void __launch_bounds__(kThreads, 1)
-scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
-                  const __grid_constant__ CUtensorMap h_map) {
+scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // mbarriers.  Completed once per tile: cb2 / cbK / barH (tcgen05.commit), barU (TMA), fS / fW / out_bar
@@ -234,12 +228,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
   uint64_t *fA = bars + 6, *fL = bars + 7, *fK = bars + 8, *fW = bars + 9, *fS = bars + 10;
   uint64_t *item_bar = bars + 11, *state_bar = bars + 12, *out_bar = bars + 13, *read_bar = bars + 14;
   uint64_t *fL1 = bars + 15;    // 16 worker warps, once per half: the rows of the levels 8 + 16 are written
-  uint64_t *fH = bars + 16;     // 16 worker warps, once per tile: its output rows are staged in shared memory
-  uint64_t *hFree = bars + 17;  // store warp, once per tile: the staged rows have been read by the TMA store
-  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 18);
+  uint32_t *tmem_s = reinterpret_cast<uint32_t *>(bars + 16);
   volatile int *items = reinterpret_cast<volatile int *>(tmem_s + 1);  // [2], by tile parity
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_s + 3);  // a wait of this CTA ran out
-  volatile int *out_box = reinterpret_cast<volatile int *>(tmem_s + 4);  // [2][2]: (bh, t0) of the staged rows, bh < 0: no more
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
 
@@ -251,11 +242,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
     umma::mbar_init(out_bar, 16);
     umma::mbar_init(read_bar, 17);   // the 16 worker warps and the MMA warp, once each has read the tile's item
     umma::mbar_init(fL1, 16);
-    umma::mbar_init(fH, 16);
-    umma::mbar_init(hFree, 1);
     umma::fence_mbar_init();
     umma::prefetch_tmap(&u_map);
-    if (!LAYER) umma::prefetch_tmap(&h_map);
     *failed = 0;
   }
   if (w == 0) umma::tmem_alloc(tmem_s, 512);
@@ -270,33 +258,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
   // warps park, which leaves the issue slots to the warps that have work.  A wait that runs
   // out marks the CTA as failed: its remaining outputs are written as NaN and the error word is set.
   // (each setmaxnreg sits inside its role's branch: the register limit must not merge across roles)
-  if (w > 18 || (LAYER && w == 18)) {
-    // spare warps of the service warps' register group: give the registers back, nothing else
+  if (w > 17) {
+    // spare warps of the two service warps' register group: give the registers back, nothing else
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-  } else if (w == 18) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
-    // =========================== store warp ===========================
-    // The workers stage a tile's output rows (bf16, 128-byte swizzle) in shared memory; this warp
-    // writes them to h with ONE TMA tile store per tile (16 KB, rows beyond L dropped by the tensor
-    // map) and tells the workers when the staging buffer may be reused.  Done by the workers with
-    // 16-byte global stores, every store instruction touched 32 different 128-byte lines.
-#pragma unroll 1
-    for (uint32_t k = 0;; ++k) {
-      if (ok) {
-        ok = umma::mbar_wait_parked(fH, k & 1u, wait_ns);
-        if (!ok) *failed = 1;
-      }
-      if (!ok) break;
-      const int obh = out_box[2 * (k & 1)], ot0 = out_box[2 * (k & 1) + 1];
-      if (obh < 0) break;
-      if (lane == 0) {
-        umma::tma_store_3d(smem + kOffStage, &h_map, 0, ot0, obh);
-        umma::tma_store_wait_read();
-        umma::mbar_arrive(hFree);
-      }
-      __syncwarp();
-    }
-    if (lane == 0) umma::tma_store_wait_all();
   } else if (w == 17) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
 #define FRACSSM_WAIT(bar, parity)                                  \
@@ -520,10 +484,11 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
         FRACSSM_WAIT(barH, n_done);
         umma::tc_fence_after();
         const bool bad = *failed != 0;
+        uint4 *dst = reinterpret_cast<uint4 *>(a.h + (static_cast<int64_t>(prev_bh) * a.L + t) * kR + 16 * P);
         float acc[16];
         umma::tmem_ld16(lane_addr + kColH + 16 * P, acc);
         umma::tmem_ld_wait();
-        {
+        if (t < a.L) {
           uint4 o0, o1;
           if (bad) {
 #pragma unroll
@@ -531,16 +496,8 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
           }
           o0.x = pack2(acc[0], acc[1]); o0.y = pack2(acc[2], acc[3]); o0.z = pack2(acc[4], acc[5]); o0.w = pack2(acc[6], acc[7]);
           o1.x = pack2(acc[8], acc[9]); o1.y = pack2(acc[10], acc[11]); o1.z = pack2(acc[12], acc[13]); o1.w = pack2(acc[14], acc[15]);
-          // row 32 Q + lane of the staged tile, 16-byte chunks 2P and 2P + 1 at their swizzled places
-          const uint32_t row = 32 * Q + lane;
-          uint8_t *rp = smem + kOffStage + row * 128;
-          *reinterpret_cast<uint4 *>(rp + (((2 * P) ^ (row & 7)) << 4)) = o0;
-          *reinterpret_cast<uint4 *>(rp + (((2 * P + 1) ^ (row & 7)) << 4)) = o1;
-          if (w == 0 && lane == 0) {
-            out_box[2 * (n_done & 1)] = prev_bh;
-            out_box[2 * (n_done & 1) + 1] = prev_t0;
-          }
-          warp_arrive(fH, lane);
+          __stcs(dst, o0);
+          __stcs(dst + 1, o1);
         }
       } else {
         // layer mode: skip connection, gate and the partial sum of squares, 8 columns at a time; the
@@ -730,11 +687,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
           else emit_level(sb + kOffZ1 + half_off + rg16 * 1024, ks, fw, true);
         }
         warp_arrive(fL1, lane);
-        // (the second half of slot 4 held the previous tile's output rows: the store warp has read them)
-        // (waited for even after a failed wait elsewhere: the NaN rows of a failed tile must reach h intact)
-        if (!LAYER && h == 1 && n > 0) {
-          if (!umma::mbar_wait_parked(hFree, (n - 1) & 1u, wait_ns)) { ok = false; *failed = 1; }
-        }
         // ---- levels 32 (rows 64..127) and 64 (rows 0..63) -> slots 4 / 5
         {
           const uint32_t rg64 = w & 7, rg32 = 8 + (((w >> 3) << 2) | (w & 3));
@@ -992,16 +944,6 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map,
       item = next;
     }
     if (n_tiles_done > 0) write_rows(n_tiles_done - 1);
-    if constexpr (!LAYER) {
-      // tell the store warp that no more rows will come (the buffer of the tile before the last one
-      // has been handed back: hFree is waited for in every tile's second pass)
-      // (the store warp must have seen the last tile's arrival before the next phase of fH completes)
-      if (n_tiles_done > 0) {
-        if (!umma::mbar_wait_parked(hFree, (n_tiles_done - 1) & 1u, wait_ns)) { ok = false; *failed = 1; }
-      }
-      if (w == 0 && lane == 0) out_box[2 * (n_tiles_done & 1)] = -1;
-      warp_arrive(fH, lane);
-    }
   }
 
   if (!ok) atomicExch(&a.ctrl[1], 1);
@@ -1099,27 +1041,24 @@ int scan_fused_launch_ex(const void *u, const void *c, const void *kappa, int ck
     a.gate_bias = layer->gate_bias;
     a.H = (int)layer->H;
   }
-  CUtensorMap map, hmap;
+  CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
-  if (rc) return rc;
-  // the output rows leave through a tile store with the same geometry (layer mode writes elsewhere)
-  rc = make_tmap_bf16_3d(&hmap, a.gate != nullptr ? u : h, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
   if (rc) return rc;
   cudaError_t e = cudaMemsetAsync(ws, 0, kCtrlBytes + align256((size_t)B * 4), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(FRACSSM_ERR_CUDA, "frac_scan: %s", cudaGetErrorString(e));
   const int grid = a.total < sms ? a.total : sms;
   const cudaStream_t st = (cudaStream_t)stream;
   if (a.gate != nullptr) {
-    if (ckf32) scan_fused_kernel<true, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
-    else scan_fused_kernel<false, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
+    if (ckf32) scan_fused_kernel<true, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+    else scan_fused_kernel<false, true, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
   } else {
     const bool ragged = a.L % kTile != 0;
     if (ragged) {
-      if (ckf32) scan_fused_kernel<true, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
-      else scan_fused_kernel<false, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
+      if (ckf32) scan_fused_kernel<true, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+      else scan_fused_kernel<false, false, true><<<grid, kThreads, kSmemBytes, st>>>(a, map);
     } else {
-      if (ckf32) scan_fused_kernel<true, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
-      else scan_fused_kernel<false, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map, hmap);
+      if (ckf32) scan_fused_kernel<true, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
+      else scan_fused_kernel<false, false, false><<<grid, kThreads, kSmemBytes, st>>>(a, map);
     }
   }
   return check_launch("frac_scan (single-pass kernel)");

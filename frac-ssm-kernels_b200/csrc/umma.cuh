@@ -111,22 +111,6 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// Tile store shared -> global through the same kind of tensor map (rows outside the tensor are
-// dropped); completion is tracked by the issuing thread's bulk-copy group.
-__device__ __forceinline__ void tma_store_3d(const void *src, const CUtensorMap *map, int x, int y, int z) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
-               : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// the issuing thread's stores have finished READING shared memory (the source may be reused)
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-// the issuing thread's stores are complete
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
