@@ -169,6 +169,15 @@ template <int OFF>
 __device__ __forceinline__ void ldg_stream_at(uint32_t &d, const void *p) {
   asm volatile("ld.global.L1::no_allocate.b32 %0, [%1+%2];" : "=r"(d) : "l"(p), "n"(OFF));
 }
+// 32 bytes per lane in one instruction (sm_100: 256-bit global accesses); the address must be 32-byte aligned
+__device__ __forceinline__ void stg_stream_32B(void *p, const uint4 &a, const uint4 &b) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+__device__ __forceinline__ void ldg_stream_32B(const void *p, uint4 &a, uint4 &b) {
+  asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w),
+               "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+}
 template <bool CKF32, bool RAGGED, int I>
 __device__ __forceinline__ void load_tok2(RawHalf<CKF32> &raw, const FusedArgs &a, int bh, int t0, int w, int lane,
                                           int h) {
@@ -476,6 +485,9 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
     __syncwarp();
     if (lane == 0) umma::mbar_arrive(read_bar);
     int prev_bh = 0, prev_t0 = 0;
+    // 32-byte accesses of the output stage need 32-byte aligned rows (a row is 128 bytes: the bases decide)
+    const bool io32 = ((LAYER ? (reinterpret_cast<uintptr_t>(a.u) | reinterpret_cast<uintptr_t>(a.gate))
+                              : reinterpret_cast<uintptr_t>(a.h)) & 31) == 0;
     // Output rows of the previous tile (its H accumulator is complete when barH fires).  It runs in
     // the middle of the next tile's first phase, which so overlaps the output MMAs.
     auto write_rows = [&](uint32_t n_done) {
@@ -496,8 +508,14 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
           }
           o0.x = pack2(acc[0], acc[1]); o0.y = pack2(acc[2], acc[3]); o0.z = pack2(acc[4], acc[5]); o0.w = pack2(acc[6], acc[7]);
           o1.x = pack2(acc[8], acc[9]); o1.y = pack2(acc[10], acc[11]); o1.z = pack2(acc[12], acc[13]); o1.w = pack2(acc[14], acc[15]);
-          __stcs(dst, o0);
-          __stcs(dst + 1, o1);
+          // one 32-byte store per row where the rows are 32-byte aligned: a lane's 32 bytes are one
+          // sector, and two 16-byte stores made the warp touch its 32 lines twice
+          if (io32) {
+            stg_stream_32B(dst, o0, o1);
+          } else {
+            __stcs(dst, o0);
+            __stcs(dst + 1, o1);
+          }
         }
       } else {
         // layer mode: skip connection, gate and the partial sum of squares, 8 columns at a time; the
@@ -509,8 +527,13 @@ scan_fused_kernel(const FusedArgs a, const __grid_constant__ CUtensorMap u_map) 
         uint4 uv[2] = {}, gv[2] = {};
         if (live) {
           const uint4 *up = reinterpret_cast<const uint4 *>(a.u + urow), *gp = reinterpret_cast<const uint4 *>(a.gate + grow);
-          uv[0] = __ldcs(up); uv[1] = __ldcs(up + 1);
-          gv[0] = __ldcs(gp); gv[1] = __ldcs(gp + 1);
+          if (io32) {
+            ldg_stream_32B(up, uv[0], uv[1]);
+            ldg_stream_32B(gp, gv[0], gv[1]);
+          } else {
+            uv[0] = __ldcs(up); uv[1] = __ldcs(up + 1);
+            gv[0] = __ldcs(gp); gv[1] = __ldcs(gp + 1);
+          }
         }
         FRACSSM_WAIT(barH, n_done);
         umma::tc_fence_after();

@@ -16,11 +16,11 @@ from tests.helpers import TOL_BF16, TOL_F32
 pytestmark = pytest.mark.gpu
 
 
-def _noalloc(u, c, kappa, rho, init):
+def _noalloc(u, c, kappa, rho, init, h=None):
     from frac_ssm_b200 import _cabi as C
     B, L, R = u.shape
     M = c.shape[-1]
-    h = torch.empty_like(u)
+    h = torch.empty_like(u) if h is None else h
     fin = torch.empty(B, R, M, device=u.device, dtype=torch.float32)
     C.check(C.lib().fracssm_frac_scan_fwd_noalloc(
         C.ptr(u), C.ptr(c), C.ptr(kappa), C.ptr(rho), C.ptr(init), C.ptr(h), C.ptr(fin), C.F32,
@@ -48,6 +48,22 @@ def test_noalloc_matches_workspace_entry_twice_in_a_row():
             torch.testing.assert_close(fin, f_ref, **TOL_F32)
             torch.testing.assert_close(h.float().cpu(), h_orc.float(), **TOL_BF16)
             torch.testing.assert_close(fin.cpu(), f_orc.float(), **TOL_F32)
+
+
+def test_output_rows_that_are_only_16_byte_aligned():
+    """The kernel writes a row's 32 bytes per lane with one store when h is 32-byte aligned and with two
+    16-byte stores otherwise: both give the same bits."""
+    from frac_ssm_b200 import _cabi as C
+    u, c, kappa, rho, _ = (t.cuda() for t in O.scan_inputs(5, 333, 64, 128, gen="model_like", seed=33))
+    h_even, f_even = _noalloc(u, c, kappa, rho, None)
+    assert C.ptr(h_even).value % 32 == 0
+    buf = torch.full((u.numel() + 16,), float("nan"), device=u.device, dtype=u.dtype)
+    h_odd = buf[8:8 + u.numel()].view_as(u)
+    assert C.ptr(h_odd).value % 32 == 16
+    h_odd, f_odd = _noalloc(u, c, kappa, rho, None, h=h_odd)
+    assert C.lib().fracssm_frac_scan_noalloc_status(C.stream_of(u)) == 0
+    assert torch.equal(h_odd, h_even) and torch.equal(f_odd, f_even)
+    assert torch.isnan(buf[:8]).all() and torch.isnan(buf[8 + u.numel():]).all()
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
