@@ -28,7 +28,11 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
         return_final_state: also return the state after the last token.
         final_state_dtype: dtype of the returned state; default follows the reference
             (bfloat16 when u is bfloat16, else float32).  The state is always carried in float32.
-        path: "auto", "staged" or "fused".
+        path: "auto", "staged" or "fused".  "auto" takes the single-pass kernel when it covers the
+            shape, and for few rows with many tokens (at most 28 rows, at least 32768 tokens) cuts
+            every row into sub-segments first, because a row is one chain of tiles and 148 SMs want
+            more chains than that: one summary pass over u, kappa and rho gives every sub-segment its
+            incoming state, then all sub-segments are scanned as rows (`parallel.seq_parallel_scan`).
         check: after the launch, synchronise and raise if a bounded device-side wait of the
             single-pass kernel ran out (debugging aid; the default stays asynchronous).
     Returns:
@@ -61,6 +65,13 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
     assert final_state_dtype in (torch.float32, torch.bfloat16)
 
     path_code = _PATHS[path]
+    if path == "auto" and not check and not torch.compiler.is_compiling():
+        splits = _row_splits(u, c, chunk_size)
+        if splits > 1:
+            from ... import parallel
+            h, fin = parallel.seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state, True,
+                                                local_splits=splits, process_local=True)
+            return (h, fin.to(final_state_dtype)) if return_final_state else h
     if check:      # the status read-back bypasses the registered op (it needs the scratch)
         h, fin = _launch(u, c, kappa, rho, chunk_size, initial_state, return_final_state,
                          final_state_dtype == torch.float32, path_code, check)
@@ -70,6 +81,20 @@ def frac_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_sta
     if return_final_state:
         return h, fin
     return h
+
+
+def _row_splits(u, c, chunk_size):
+    """Sub-segments per row for the "auto" path: more than 1 only where the single-pass kernel covers
+    both the call and the cut-up call, the tensors are dense, and the rows are few and long."""
+    from ... import parallel
+    B, L, R = u.shape
+    if B < 1 or not (u.is_contiguous() and c.is_contiguous()) or u.dtype != torch.bfloat16:
+        return 1
+    splits = parallel._auto_local_splits(B, L, chunk_size, 1, u.device)
+    if splits > 1 and not C.lib().fracssm_scan_fused_supported(B * splits, L // splits, R, c.shape[-1],
+                                                               chunk_size, C.dt(u), C.dt(c)):
+        return 1
+    return splits
 
 
 def _launch(u, c, kappa, rho, chunk_size, initial_state, want_final, final_fp32, path_code, check=False):

@@ -100,25 +100,31 @@ def _auto_local_splits(B, L_local, chunk_size, world, device, group=None):
 
     The scan kernels hand the state from tile to tile of a row, so few rows mean few independent
     chains; sub-segments are extra rows.  Splitting costs one more read of u, kappa and rho, so a
-    single rank does not split.  Each rank can only judge its own segment (segments differ by a chunk
+    single rank splits only where the chains are what limits the plain scan by a wide margin: at most
+    28 rows (one tile step of a chain takes about 2.8 us, a CTA needs about 7.6 us per tile, so
+    148 SMs are busy from some 54 rows on, and the extra read costs about 60 % of a scan) and at
+    least 32768 tokens (measured on 24 rows x 1,048,576 tokens: 22.7 ms plain, 16.9 ms cut in 8).
+    Each rank can only judge its own segment (segments differ by a chunk
     when the chunk count does not divide by the world size, and the last one may be ragged), so the
     ranks agree on the smallest of their candidates with one MIN all-reduce of a single integer;
     candidates are powers of two and a segment that can be cut into S whole-chunk pieces can also be
     cut into any smaller power of two.  Reading the agreed value synchronises the host with the
     device; callers that must not synchronise pass `local_splits` themselves.
     """
-    if world == 1:
+    if world == 1 and (B > 28 or L_local < 32768):
         return 1
     s = 1
     while B * s < 148 and L_local % (2 * s * chunk_size) == 0 and L_local // (2 * s) >= 1024:
         s *= 2
+    if world == 1:
+        return s
     agreed = torch.tensor([s], dtype=torch.int64, device=device)
     dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
     return int(agreed.item())
 
 
 def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_final_state=False,
-                      group=None, ops=None, local_splits=None):
+                      group=None, ops=None, local_splits=None, process_local=False):
     """Scan a sequence whose tokens are split across the ranks of `group` (in rank order).
 
     Every rank passes ITS segment (`[B, L_local, ...]`; all segments but the last must be a
@@ -130,9 +136,12 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     segment into that many sub-segments which are scanned as extra rows: with few (batch x head)
     rows this is what keeps all SMs busy.  By default the ranks agree on a value among themselves
     (one small all-reduce and a host synchronisation, see `_auto_local_splits`).
+
+    `process_local=True` ignores the process group: the tensors are the whole sequence and only the
+    sub-segment composition runs (what `frac_scan` does by itself for few rows and many tokens).
     """
     ops = CudaStageOps if ops is None else ops
-    if dist.is_available() and dist.is_initialized():
+    if not process_local and dist.is_available() and dist.is_initialized():
         world, rank = dist.get_world_size(group), dist.get_rank(group)
     else:                       # a single process: the same composition without any exchange
         world, rank = 1, 0

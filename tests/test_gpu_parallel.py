@@ -51,6 +51,32 @@ def test_segment_summary_kernel(kdtype, B, L):
     close(decay, torch.exp(cd.double().sum(1)).float(), **TOL_F32)
 
 
+def test_single_process_default_split_matches_plain_scan():
+    """Few rows and a long sequence: one process cuts the sequence into sub-segments by default
+    (summary pass, state composition, one scan of all sub-segments as rows)."""
+    from frac_ssm_b200 import parallel
+    B, L, T = 3, 32768, 256
+    assert parallel._auto_local_splits(B, L, T, 1, torch.device("cuda")) == 32
+    u, c, kappa, rho, init = (t.cuda() for t in O.scan_inputs(B, L, 64, 128, gen="model_like", seed=77))
+    from frac_ssm_b200.ops.b200 import frac_scan
+    h_ref, f_ref = frac_scan(u, c, kappa, rho, T, init, True, final_state_dtype=torch.float32, path="fused")
+    h, fin = parallel.seq_parallel_scan(u, c, kappa, rho, T, init, True)
+    close(h, h_ref.cpu(), **TOL_BF16)
+    close(fin, f_ref.cpu(), **TOL_F32)
+    # the scan's own "auto" path takes the same route for such a shape
+    h_auto, f_auto = frac_scan(u, c, kappa, rho, T, init, True)
+    assert f_auto.dtype == torch.bfloat16 and torch.equal(h_auto, h)
+    close(f_auto, f_ref.cpu(), rtol=2e-2, atol=2e-2)
+    h_only = frac_scan(u, c, kappa, rho, T)
+    close(h_only, frac_scan(u, c, kappa, rho, T, path="fused").cpu(), **TOL_BF16)
+    # the oracle on one row, token by token in float64
+    uc, cc, kc, rc = (t[1:2].cpu() for t in (u, c, kappa, rho))
+    h_orc, f_orc = O.frac_scan_slabs(uc.float(), cc.float(), kc.float(), rc, T, init[1:2].cpu(), True,
+                                     exact=True, slab=1)
+    close(h[1:2], h_orc, **TOL_BF16)
+    close(fin[1:2], f_orc, **TOL_F32)
+
+
 def _nccl_worker(rank, world, port, out):
     import torch.distributed as dist
     from frac_ssm_b200 import parallel

@@ -165,6 +165,17 @@ def test_shard_helpers():
         parallel.shard_rows(4, 4, 4)
 
 
+def test_single_rank_split_policy():
+    """One rank cuts only few-row, long sequences (the extra read must pay for itself); no exchange,
+    no host synchronisation."""
+    f = lambda B, L: parallel._auto_local_splits(B, L, 256, 1, torch.device("cpu"))
+    assert f(24, 1048576) == 8          # 24 rows -> 192 chains
+    assert f(29, 1048576) == 1          # enough rows: the plain scan is within reach of the split one
+    assert f(24, 16384) == 1            # too short to pay for two more launches
+    assert f(3, 32768) == 32            # sub-segments of at least 1024 tokens
+    assert f(3, 32768 + 256) == 1       # 129 chunks cannot be halved
+
+
 def test_incoming_state_composition():
     g = torch.Generator().manual_seed(0)
     D = torch.rand(3, 2, 4, generator=g)
