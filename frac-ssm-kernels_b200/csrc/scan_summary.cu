@@ -38,9 +38,15 @@ struct SummaryArgs {
   float *state;  // running state per row (worker access order)
   float *dec;    // running decay product per row [BH, 128]
   int BH, L, ntiles, total;
+  int rows, group;             // rows the launch works on; group > 1: the last row of every `group` rows is left out
   int first_tile;              // tile index of the first ticket (0 except in the wait-limit self-test)
   unsigned long long wait_ns;  // limit of every device-side wait
 };
+
+// Row of the q-th row that the launch works on (rows come in groups of a.group; the last of each is skipped).
+__device__ __forceinline__ int summary_row(const SummaryArgs &a, int q) {
+  return a.group > 1 ? q + q / (a.group - 1) : q;
+}
 
 template <bool KF32>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -99,7 +105,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
     item = __shfl_sync(0xffffffffu, item, 0);
 #pragma unroll 1
     for (uint32_t n = 0; item < a.total; ++n) {
-      const int j = item / a.BH + a.first_tile, bh = item % a.BH;
+      const int j = item / a.rows + a.first_tile, bh = summary_row(a, item % a.rows);
       // The next ticket is taken a tile ahead and published through item_bar.  For the first tile it
       // has to wait until the workers have read the first item (their arrival on `full`): two
       // completions of item_bar in a row would flip its parity twice, and a worker that had not
@@ -114,7 +120,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
         }
         next = __shfl_sync(0xffffffffu, next, 0);
         if (lane == 1 && next < a.total) {  // pull the next item's inputs into L2 a whole tile ahead
-          const int nj = next / a.BH + a.first_tile, nb = next % a.BH;
+          const int nj = next / a.rows + a.first_tile, nb = summary_row(a, next % a.rows);
           const int ntok = min(kTile, a.L - nj * kTile);
           const int64_t tok = static_cast<int64_t>(nb) * a.L + nj * kTile;
           constexpr int kKb = KF32 ? 4 : 2;
@@ -172,7 +178,7 @@ scan_summary_kernel(const SummaryArgs a, const __grid_constant__ CUtensorMap u_m
     FRACSSM_WAIT(item_bar, 0);
     int item = items[0];
     for (uint32_t n = 0; item < a.total; ++n) {
-      const int j = item / a.BH + a.first_tile, bh = item % a.BH;
+      const int j = item / a.rows + a.first_tile, bh = summary_row(a, item % a.rows);
       const int t0 = j * kTile + 8 * w;
       const int64_t tok0 = static_cast<int64_t>(bh) * a.L + t0;
       float4 rr[8];
@@ -308,8 +314,10 @@ namespace fracssm {
 int segment_summary_launch_ex(const void *u, const void *kappa, int k_dtype, const float *rho,
                               const float *initial_state, float *final_state, float *decay, void *workspace,
                               size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M, void *stream,
-                              int first_tile, unsigned long long wait_ns) {
+                              int first_tile, unsigned long long wait_ns, int64_t group) {
   if (B < 0 || L < 0) return fail(FRACSSM_ERR_ARG, "segment_summary: bad sizes");
+  if (group < 0 || (group > 1 && B % group != 0))
+    return fail(FRACSSM_ERR_ARG, "segment_summary: the row count must be a multiple of the group size");
   if (R != kR || M != kM || (k_dtype != FRACSSM_BF16 && k_dtype != FRACSSM_F32))
     return fail(FRACSSM_ERR_UNSUPPORTED, "segment_summary: needs R = 64, M = 128, bfloat16 u and bfloat16 or float32 kappa");
   if (B == 0) return FRACSSM_OK;
@@ -360,7 +368,9 @@ int segment_summary_launch_ex(const void *u, const void *kappa, int k_dtype, con
   a.L = (int)L;
   a.ntiles = (int)ceil_div(L, kTile);
   a.first_tile = first_tile;
-  a.total = (a.ntiles - first_tile) * a.BH;
+  a.group = group > 1 ? (int)group : 1;
+  a.rows = group > 1 ? (int)(B / group * (group - 1)) : (int)B;
+  a.total = (a.ntiles - first_tile) * a.rows;
   a.wait_ns = wait_ns;
   CUtensorMap map;
   int rc = make_tmap_bf16_3d(&map, u, kR, (uint64_t)L, (uint64_t)B, kR, kTile);
@@ -379,5 +389,13 @@ extern "C" int fracssm_segment_summary(const void *u, const void *kappa, int k_d
                                        void *workspace, size_t workspace_bytes, int64_t B, int64_t L,
                                        int64_t R, int64_t M, void *stream) {
   return fracssm::segment_summary_launch_ex(u, kappa, k_dtype, rho, initial_state, final_state, decay, workspace,
-                                            workspace_bytes, B, L, R, M, stream, 0, fracssm::tile::kWaitNs);
+                                            workspace_bytes, B, L, R, M, stream, 0, fracssm::tile::kWaitNs, 1);
+}
+
+extern "C" int fracssm_segment_summary_grouped(const void *u, const void *kappa, int k_dtype, const float *rho,
+                                               float *final_state, float *decay, void *workspace,
+                                               size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M,
+                                               int64_t group, void *stream) {
+  return fracssm::segment_summary_launch_ex(u, kappa, k_dtype, rho, nullptr, final_state, decay, workspace,
+                                            workspace_bytes, B, L, R, M, stream, 0, fracssm::tile::kWaitNs, group);
 }

@@ -9,7 +9,7 @@ namespace fracssm {
 int segment_summary_launch_ex(const void *u, const void *kappa, int k_dtype, const float *rho,
                               const float *initial_state, float *final_state, float *decay, void *workspace,
                               size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M, void *stream,
-                              int first_tile, unsigned long long wait_ns);
+                              int first_tile, unsigned long long wait_ns, int64_t group);
 }  // namespace fracssm
 
 extern "C" int fracssm_selftest_scan_wait_limit(const void *u, const void *c, const void *kappa, const float *rho,
@@ -29,5 +29,5 @@ extern "C" int fracssm_selftest_summary_wait_limit(const void *u, const void *ka
   using namespace fracssm;
   if (L <= 128 || B < 1) return fail(FRACSSM_ERR_ARG, "selftest_summary_wait_limit: needs at least two tiles");
   return segment_summary_launch_ex(u, kappa, FRACSSM_BF16, rho, nullptr, final_state, decay, workspace,
-                                   workspace_bytes, B, L, 64, 128, stream, /*first_tile=*/1, wait_ns);
+                                   workspace_bytes, B, L, 64, 128, stream, /*first_tile=*/1, wait_ns, /*group=*/1);
 }

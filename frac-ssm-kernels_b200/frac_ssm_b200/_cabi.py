@@ -44,6 +44,7 @@ _SIGNATURES = {
     "fracssm_frac_scan_fwd_noalloc": (ci, [vp, vp, vp, vp, vp, vp, vp, ci, i64, i64, i64, i64, vp]),
     "fracssm_segment_summary_workspace_bytes": (sz, [i64, i64, i64]),
     "fracssm_segment_summary": (ci, [vp, vp, ci, vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, vp]),
+    "fracssm_segment_summary_grouped": (ci, [vp, vp, ci, vp, vp, vp, vp, sz, i64, i64, i64, i64, i64, vp]),
     "fracssm_scan_fused_status": (ci, [vp, vp]),
     "fracssm_frac_scan_noalloc_status": (ci, [vp]),
     "fracssm_compute_params": (ci, [vp, ci, i64, i64, vp, ci, i64, i64, vp, ci, i64, i64,

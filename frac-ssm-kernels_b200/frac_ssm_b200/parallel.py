@@ -46,11 +46,14 @@ class CudaStageOps:
     """Stage functions on the CUDA extension (the product path)."""
 
     @staticmethod
-    def segment_summary(u, kappa, rho, chunk_size):
+    def segment_summary(u, kappa, rho, chunk_size, skip_last_of=1):
         """(decay product [B, M], final state from a zero state [B, R, M]) of a segment, float32.
 
         One kernel that reads u, kappa and rho once when the shape is covered (R = 64, M = 128,
         bfloat16 u, dense); otherwise the staged kernels (cumsum -> chunk_state -> state_passing).
+        `skip_last_of = S > 1`: the rows are groups of S sub-segments of one sequence each and nobody
+        needs the summary of a group's last row; the one-kernel path then leaves those rows out
+        (their entries are zero), the staged path computes them anyway.
         """
         from . import _cabi as C
         B, L, R = u.shape
@@ -58,15 +61,22 @@ class CudaStageOps:
         if (R == 64 and M == 128 and u.dtype == torch.bfloat16 and L > 0 and B > 0
                 and kappa.dtype in (torch.bfloat16, torch.float32)):
             u, kappa, rho = u.contiguous(), kappa.contiguous(), rho.contiguous()
-            fin = torch.empty(B, R, M, device=u.device, dtype=torch.float32)
-            decay = torch.empty(B, M, device=u.device, dtype=torch.float32)
+            grouped = skip_last_of > 1
+            alloc = torch.zeros if grouped else torch.empty
+            fin = alloc(B, R, M, device=u.device, dtype=torch.float32)
+            decay = alloc(B, M, device=u.device, dtype=torch.float32)
             lib = C.lib()
             with torch.cuda.device(u.device):
                 ws = torch.empty(lib.fracssm_segment_summary_workspace_bytes(B, R, M), device=u.device,
                                  dtype=torch.uint8)
-                C.check(lib.fracssm_segment_summary(
-                    C.ptr(u), C.ptr(kappa), C.dt(kappa), C.ptr(rho), None, C.ptr(fin), C.ptr(decay),
-                    C.ptr(ws), ws.numel(), B, L, R, M, C.stream_of(u)), "segment_summary")
+                if grouped:
+                    C.check(lib.fracssm_segment_summary_grouped(
+                        C.ptr(u), C.ptr(kappa), C.dt(kappa), C.ptr(rho), C.ptr(fin), C.ptr(decay),
+                        C.ptr(ws), ws.numel(), B, L, R, M, skip_last_of, C.stream_of(u)), "segment_summary")
+                else:
+                    C.check(lib.fracssm_segment_summary(
+                        C.ptr(u), C.ptr(kappa), C.dt(kappa), C.ptr(rho), None, C.ptr(fin), C.ptr(decay),
+                        C.ptr(ws), ws.numel(), B, L, R, M, C.stream_of(u)), "segment_summary")
             return decay, fin
         from .ops.b200 import stages
         lcr, cd = stages._cumsum(rho, chunk_size, True)
@@ -161,7 +171,12 @@ def seq_parallel_scan(u, c, kappa, rho, chunk_size, initial_state=None, return_f
     Ls = L_local // S
     rows = lambda t: t.contiguous().view(B * S, Ls, t.shape[-1])   # (b, s) becomes the row index
     u_r, c_r, k_r, rho_r = rows(u), rows(c), rows(kappa), rows(rho)
-    decay, fin0 = ops.segment_summary(u_r, k_r, rho_r, chunk_size)
+    if rank == world - 1 and ops is CudaStageOps:
+        # nobody reads the summary of the whole sequence's last sub-segment(s): the last rank leaves out
+        # the last sub-segment of each of its rows
+        decay, fin0 = ops.segment_summary(u_r, k_r, rho_r, chunk_size, skip_last_of=S)
+    else:
+        decay, fin0 = ops.segment_summary(u_r, k_r, rho_r, chunk_size)
     packed = torch.cat([fin0.reshape(B, S, R * M), decay.reshape(B, S, M)], dim=2).float().contiguous()
     if world > 1:
         gathered = torch.empty(world * B, S, R * M + M, dtype=packed.dtype, device=packed.device)

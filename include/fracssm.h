@@ -165,6 +165,18 @@ int fracssm_segment_summary(const void *u, const void *kappa, int k_dtype, const
                             int64_t M, void *stream);
 
 /*
+ * The same for rows that come in groups of `group` consecutive rows (the sub-segments of one
+ * sequence, in order): the last row of every group is left out and its final_state and decay entries
+ * are not written.  A process that cuts its own sequence into sub-segments needs the summaries of all
+ * but the last one.  group <= 1: every row; otherwise B must be a multiple of group.  The state starts
+ * from zero.  Same workspace as fracssm_segment_summary.  New with respect to the reference.
+ */
+int fracssm_segment_summary_grouped(const void *u, const void *kappa, int k_dtype, const float *rho,
+                                    float *final_state, float *decay, void *workspace,
+                                    size_t workspace_bytes, int64_t B, int64_t L, int64_t R, int64_t M,
+                                    int64_t group, void *stream);
+
+/*
  * Reads back the error word of the last single-pass launch that used `workspace` (this call
  * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
  * (for a predecessor tile's state, a TMA load or an MMA) ran out; the outputs of the affected rows

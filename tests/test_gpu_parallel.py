@@ -51,6 +51,19 @@ def test_segment_summary_kernel(kdtype, B, L):
     close(decay, torch.exp(cd.double().sum(1)).float(), **TOL_F32)
 
 
+def test_grouped_summary_leaves_out_the_last_row_of_every_group():
+    from frac_ssm_b200 import parallel
+    u, c, kappa, rho, _ = (t.cuda() for t in O.scan_inputs(12, 600, 64, 128, gen="model_like", seed=5))
+    decay, fin = parallel.CudaStageOps.segment_summary(u, kappa, rho, 256)
+    d4, f4 = parallel.CudaStageOps.segment_summary(u, kappa, rho, 256, skip_last_of=4)
+    keep = torch.arange(12, device="cuda") % 4 != 3
+    assert torch.equal(d4[keep], decay[keep]) and torch.equal(f4[keep], fin[keep])
+    assert not d4[~keep].any() and not f4[~keep].any()
+    from frac_ssm_b200 import _cabi as C
+    with pytest.raises(C.FracSsmError, match="multiple of the group size"):
+        parallel.CudaStageOps.segment_summary(u, kappa, rho, 256, skip_last_of=5)
+
+
 def test_single_process_default_split_matches_plain_scan():
     """Few rows and a long sequence: one process cuts the sequence into sub-segments by default
     (summary pass, state composition, one scan of all sub-segments as rows)."""
