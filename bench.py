@@ -502,18 +502,46 @@ def run_model_workload(args, rank, world, dev, dist):
     ids = torch.randint(0, cfg.vocab_size, (batch // world, L), device=dev, generator=g)
 
     def step():
-        return model(ids, use_cache=False)[0]
+        with torch.no_grad():
+            return model(ids, use_cache=False)[0]
+
+    launch = {"kind": "plain launches"}
 
     def timed():
         for _ in range(max(args.warmup, 3)):
             step()
+        # one prefill captured as a CUDA graph and replayed K times, as for config 1: a step is about 700
+        # launches from Python, and a busy host (other jobs on the box) then starves the GPU between them
+        graph = None
+        if not args.no_graph:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step()
+                torch.cuda.current_stream().wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                graph.replay()
+                torch.cuda.synchronize()
+                launch["kind"] = "CUDA graph of one prefill, replayed once per step"
+            except Exception as exc:      # noqa: BLE001 - any capture problem falls back to plain launches
+                print(f"bench: CUDA graph capture of the model step failed ({exc}); timing plain launches",
+                      file=sys.stderr)
+                graph = None
+                launch["kind"] = "plain launches"
+                torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            step()
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
         e1.record()
         if dist is not None:
             dist.barrier()
@@ -553,6 +581,7 @@ def run_model_workload(args, rank, world, dev, dist):
                           "config": {"workload": f"config 2: 24-layer model prefill, batch {batch} x L {L}, hidden 768, "
                                                  "24 heads x 64, 128 modes, chunk 256, vocabulary 50280",
                                      "parameters": nparam, "scan_coefficients": "bf16",
+                                     "timed_launch": launch["kind"],
                                      "ms_per_step_with_f32_scan_coefficients": ms_f32,
                                      "decode_ms_per_token_step_rank0": dec_ms,
                                      "decode_batch_per_gpu": batch // world,
