@@ -396,7 +396,10 @@ rmsnorm_gated_kernel(const void *__restrict__ x, int64_t x_srow, const void *__r
 }
 
 // bf16 fast path: one warp per row, the row (up to 2048 elements) held in registers as 16-byte
-// pieces, so x and the gate are read once; four rows per block.
+// pieces, so x and the gate are read once; four rows per block.  The weight is read as one or two
+// 16-byte pieces per chunk (WVEC 1: bf16, 2: f32; 0: element by element, any type): eight 2-byte loads
+// with a run-time type switch per chunk made the kernel instruction-bound.
+template <int WVEC>
 __global__ void __launch_bounds__(128)
 rmsnorm_gated_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_srow,
                           const __nv_bfloat16 *__restrict__ gate, int64_t g_srow, const void *__restrict__ w,
@@ -430,11 +433,21 @@ rmsnorm_gated_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_srow,
   for (int i = 0; i < 8; ++i) {
     const int ch = lane + 32 * i;
     if (ch < chunks) {
+      float wv[8];
+      if (WVEC == 1) {
+        unpack8(__ldg(reinterpret_cast<const uint4 *>(w) + ch), wv);
+      } else if (WVEC == 2) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * ch);
+        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * ch + 1);
+        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wv[e] = ld_f32(w, 8 * ch + e, w_dt);
+      }
       uint32_t o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const __nv_bfloat162 t = __floats2bfloat162_rn(v[i][2 * e] * rs * ld_f32(w, 8 * ch + 2 * e, w_dt),
-                                                       v[i][2 * e + 1] * rs * ld_f32(w, 8 * ch + 2 * e + 1, w_dt));
+        const __nv_bfloat162 t = __floats2bfloat162_rn(v[i][2 * e] * rs * wv[2 * e], v[i][2 * e + 1] * rs * wv[2 * e + 1]);
         o[e] = *reinterpret_cast<const uint32_t *>(&t);
       }
       __stcs(reinterpret_cast<uint4 *>(y + row * D) + ch, make_uint4(o[0], o[1], o[2], o[3]));
@@ -680,9 +693,15 @@ extern "C" int fracssm_rmsnorm_gated(const void *x, int64_t x_srow, const void *
   auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (xg_dtype == FRACSSM_BF16 && D % 8 == 0 && D <= 2048 && al16(x) && al16(y) && x_srow % 8 == 0 &&
       (!gate || (al16(gate) && g_srow % 8 == 0))) {
-    rmsnorm_gated_bf16_kernel<<<(unsigned)ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const __nv_bfloat16 *>(x), x_srow, reinterpret_cast<const __nv_bfloat16 *>(gate), g_srow,
-        weight, w_dtype, eps, reinterpret_cast<__nv_bfloat16 *>(y), rstd, rows, D);
+    const int wvec = !al16(weight) ? 0 : w_dtype == FRACSSM_BF16 ? 1 : w_dtype == FRACSSM_F32 ? 2 : 0;
+#define FRACSSM_RMSNORM(WV)                                                                                        \
+  rmsnorm_gated_bf16_kernel<WV><<<(unsigned)ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(                    \
+      reinterpret_cast<const __nv_bfloat16 *>(x), x_srow, reinterpret_cast<const __nv_bfloat16 *>(gate), g_srow,   \
+      weight, w_dtype, eps, reinterpret_cast<__nv_bfloat16 *>(y), rstd, rows, D)
+    if (wvec == 1) FRACSSM_RMSNORM(1);
+    else if (wvec == 2) FRACSSM_RMSNORM(2);
+    else FRACSSM_RMSNORM(0);
+#undef FRACSSM_RMSNORM
     return check_launch("rmsnorm_gated");
   }
   rmsnorm_gated_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(

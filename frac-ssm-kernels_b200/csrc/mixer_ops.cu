@@ -12,7 +12,7 @@ namespace {
 __device__ __forceinline__ float silu_(float x) { return x / (1.f + __expf(-x)); }
 
 constexpr int kConvMaxK = 8;     // kernel widths 1..8
-constexpr int kConvTokens = 16;  // tokens per thread: the window slides in registers
+constexpr int kConvTokens = 32;  // tokens per thread: the window slides in registers
 
 // General path: one channel per thread, any dtype.  grid (ceil(C/128), ceil(L/kConvTokens), B).
 __global__ void __launch_bounds__(128)
@@ -75,8 +75,11 @@ __device__ __forceinline__ void unpack4(const uint2 &p, float (&f)[4]) {
   f[3] = __uint_as_float(p.y & 0xFFFF0000u);
 }
 
-// Four channels (8 bytes) per thread, kConvTokens tokens walked with the window in registers, four
-// tokens' loads in flight at a time; at most 80 registers, so 6 blocks of 128 threads per SM.
+// Four channels (8 bytes) per thread, kConvTokens tokens walked with the window in registers, the next
+// four tokens requested before the current four are worked on; at most 80 registers, so 6 blocks of
+// 128 threads per SM.  At batch 16 x 4096 tokens x 1536 channels: 0.154 ms with 16 tokens per thread and
+// the loads of a group issued right before their use, 0.143 ms with 32 tokens (the three window tokens and
+// the weights are read once per 32), 0.125 ms with the loads one group ahead.
 __global__ void __launch_bounds__(128, 6)
 causal_conv4_silu_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_sb, int64_t x_sl,
                               const float *__restrict__ mask, int64_t m_sb, int64_t m_sl,
@@ -125,18 +128,27 @@ causal_conv4_silu_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_sb,
   in(l0 - 2, w1);
   in(l0 - 1, w2);
   const int64_t l1 = min(l0 + kConvTokens, L);
+  // the next four tokens are requested before the current four are worked on
+  uint2 nraw[4];
+  float nmk[4];
+  auto request = [&](int64_t lg) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      nraw[j] = make_uint2(0u, 0u);
+      nmk[j] = 1.f;
+      if (lg + j < l1) {
+        nraw[j] = __ldcs(reinterpret_cast<const uint2 *>(x + b * x_sb + (lg + j) * x_sl + ch));
+        if (mask) nmk[j] = mask[b * m_sb + (lg + j) * m_sl];
+      }
+    }
+  };
+  request(l0);
   for (int64_t lg = l0; lg < l1; lg += 4) {
     uint2 raw[4];
     float mk[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      raw[j] = make_uint2(0u, 0u);
-      mk[j] = 1.f;
-      if (lg + j < l1) {
-        raw[j] = __ldcs(reinterpret_cast<const uint2 *>(x + b * x_sb + (lg + j) * x_sl + ch));
-        if (mask) mk[j] = mask[b * m_sb + (lg + j) * m_sl];
-      }
-    }
+    for (int j = 0; j < 4; ++j) { raw[j] = nraw[j]; mk[j] = nmk[j]; }
+    if (lg + 4 < l1) request(lg + 4);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (lg + j < l1) {
