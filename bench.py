@@ -512,8 +512,10 @@ def run_model_workload(args, rank, world, dev, dist):
             step()
         # one prefill captured as a CUDA graph and replayed K times, as for config 1: a step is about 700
         # launches from Python, and a busy host (other jobs on the box) then starves the GPU between them
+        # (single process only: under torchrun the captured step did not get through its first barrier
+        # in one 2-GPU run, so ranks of a multi-process run launch the step plainly)
         graph = None
-        if not args.no_graph:
+        if not args.no_graph and dist is None:
             try:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
