@@ -179,8 +179,9 @@ int fracssm_segment_summary_grouped(const void *u, const void *kappa, int k_dtyp
 /*
  * Reads back the error word of the last single-pass launch that used `workspace` (this call
  * synchronises the stream).  Returns 0, or FRACSSM_ERR_WAIT when a bounded device-side wait
- * (for a predecessor tile's state, a TMA load or an MMA) ran out; the outputs of the affected rows
- * are then NaN from that point on.
+ * (for a predecessor tile's state, a TMA load or an MMA) ran out; the outputs the launch still wrote
+ * for the affected rows are NaN, and tiles it no longer got to are left unwritten: after this status
+ * the outputs of the whole launch are to be discarded.
  * No counterpart in the reference (its kernels have no cross-CTA waits).
  */
 int fracssm_scan_fused_status(const void *workspace, void *stream);
