@@ -99,6 +99,18 @@ def _worker(rank, world, port, mode, out):
                                                 Dk[hs], wk[cols], nloc, Rh, H, 1e-6, 0.0,
                                                 ops=OracleEpilogueOps)
             ok = torch.allclose(y.double(), y_ref[..., cols], rtol=1e-5, atol=1e-5)
+        elif mode == "local":
+            # inside an initialised group, process_local=True cuts THIS process's whole sequence and
+            # takes part in no exchange (only rank 1 calls it: a collective would hang and time out)
+            ok = True
+            if rank == 1:
+                L = 256
+                u, c, kappa, rho, init = O.scan_inputs(B, L, R, M, dtype=torch.float32, gen="model_like", seed=8)
+                h_ref, f_ref = O.frac_scan(u, c, kappa, rho, T, init, True, exact=True)
+                h, fin = parallel.seq_parallel_scan(u, c, kappa, rho, T, init, True, ops=OracleStageOps,
+                                                    local_splits=4, process_local=True)
+                ok = torch.allclose(h, h_ref, rtol=1e-4, atol=1e-4) and \
+                    torch.allclose(fin, f_ref, rtol=1e-4, atol=1e-4)
         elif mode == "rows":
             rows = parallel.shard_rows(B, rank, world)
             h, fin = OracleStageOps.scan(u[rows], c[rows], kappa[rows], rho[rows], T, init[rows])
@@ -145,6 +157,10 @@ def test_sequence_sharding_with_unequal_segments_and_default_splits(L):
 
 def test_row_sharding_matches_single_scan():
     _run(2, "rows")
+
+
+def test_process_local_split_ignores_the_group():
+    _run(2, "local")
 
 
 @pytest.mark.parametrize("world", [2, 3])
